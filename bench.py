@@ -1,0 +1,298 @@
+"""Benchmark: prefill tokens/s per decoder layer (device-timed) on N B200s.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+A step is one pass of the MoE decoder layer (`kernel_fn`) over one batch of seeded synthetic
+input.  At N = 1 the workload is the largest single-GPU benchmark configuration: the full
+decoder layer at mid prefill (4 sequences x 4096 new tokens, hidden 4096, 32 q / 8 kv heads x
+128, paged FP8 K/V cache with 64-token pages, 128 NVFP4 experts top-8 with intermediate 1536, a
+BF16 shared expert of intermediate 4096).  At N > 1 every rank runs its own 4 x 4096-token
+requests (weak scaling) and the 128 experts are sharded across ranks with all-to-all dispatch and
+combine over NCCL.  Prints one JSON line (rank 0).
+
+`value` is device-timed with inputs resident in HBM; `e2e` is the same metric through the public
+`kernel_fn` call with HOST buffers (pinned), host<->device copies inside the timed region.
+`--impl reference` times the CPU restatement of the reference's layer (oracle/) on the host
+cores, on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "prefill tokens/s per decoder layer"
+UNIT = "tokens/s"
+SEQS, SEQ_LEN = 4, 4096
+CPU_SAMPLE_TOKENS = 512
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"hbm_gbs": p["hbm_gbs"], "tflops": p.get("bf16_tflops_sustained", p["bf16_tflops"]),
+                "source": "measured (sustained bf16)"}
+    return {"hbm_gbs": 6650.0, "tflops": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons every 200 ms while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        rows = [r for r in self.rows if len(r) >= 6 and r[0].isdigit()]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        mhz = sorted(int(r[0]) for r in rows)
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in rows)]
+        return {"sm_mhz": mhz[len(mhz) // 2], "sm_max_mhz": int(rows[0][1]), "reasons": reasons, "samples": len(rows)}
+
+
+def make_workload(device, seqs=SEQS, seq_len=SEQ_LEN, seed=0, local_experts=None, local_start=0):
+    from muse_spark_open_challenge_b200 import synth
+    import dataclasses
+    shape = synth.MID
+    if local_experts is not None:
+        shape = dataclasses.replace(shape, local_experts=local_experts)
+    weights = synth.make_weights(shape, seed=seed, device=device)
+    data = synth.make_input(shape, [seq_len] * seqs, [0] * seqs, seed=seed + 1, page=64, kv_scale=1.0,
+                            local_start=local_start, device=device, fill_cache=False)
+    return shape, weights, data
+
+
+def layer_flops(shape, seqs, seq_len, routes):
+    t = seqs * seq_len
+    h = shape.hidden
+    dense = 2.0 * t * h * (shape.qkv_size + shape.q_size + shape.n_experts)
+    attn = 4.0 * shape.hq * shape.head_dim * seqs * (seq_len * (seq_len + 1) / 2)
+    routed = 2.0 * routes * 3 * shape.moe_width * shape.inter
+    shared = 2.0 * t * 3 * shape.moe_width * shape.shared_inter
+    return dense + attn + routed + shared
+
+
+def run_reference(args):
+    """CPU arm: the oracle's restatement of the reference layer on the host cores, all threads, on
+    a bounded sample (one request of CPU_SAMPLE_TOKENS tokens) of the workload's architecture."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    from oracle import layer_ref as L
+    torch.set_num_threads(os.cpu_count())
+    shape, weights, data = make_workload("cpu", seqs=1, seq_len=CPU_SAMPLE_TOKENS)
+    times = []
+    for i in range(args.warmup + args.steps):
+        t0 = time.perf_counter()
+        L.ref_kernel(data, weights)
+        if i >= args.warmup:
+            times.append(time.perf_counter() - t0)
+    sec = sum(times) / len(times)
+    value = CPU_SAMPLE_TOKENS / sec
+    sample = f"1 request x {CPU_SAMPLE_TOKENS} tokens of the same layer (all 128 experts resident), fp32 torch on CPU"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "full decoder layer, mid prefill (BASELINE config 3)", "sample": sample},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": os.cpu_count(), "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def cpu_baseline_leg():
+    from oracle import layer_ref as L
+    torch.set_num_threads(os.cpu_count())
+    shape, weights, data = make_workload("cpu", seqs=1, seq_len=CPU_SAMPLE_TOKENS)
+    t0 = time.perf_counter()
+    L.ref_kernel(data, weights)
+    sec = time.perf_counter() - t0
+    return {"value": CPU_SAMPLE_TOKENS / sec, "unit": UNIT, "cores": os.cpu_count(), "kind": "port",
+            "sample": f"1 request x {CPU_SAMPLE_TOKENS} tokens of the same layer, one timed call, fp32 torch on "
+                      f"{os.cpu_count()} threads"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+
+    from muse_spark_open_challenge_b200 import _lib, layer
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the product path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+        from muse_spark_open_challenge_b200 import ep
+    else:
+        dist = None
+
+    n_exp = 128
+    if world > 1:
+        shape, weights, data = make_workload(dev, seed=100 * rank, local_experts=n_exp // world,
+                                             local_start=rank * (n_exp // world))
+        # dense weights and the router are replicated: take rank 0's
+        for k, v in weights.items():
+            if not k.startswith(("w13", "w2")):
+                dist.broadcast(v, 0)
+        st = layer.prepare(weights)
+        ctx = ep.ExpertParallel(st, world, rank, shape.n_experts)
+        step = lambda d: ep.kernel_fn(d, st, ctx)  # noqa: E731
+    else:
+        shape, weights, data = make_workload(dev)
+        st = layer.prepare(weights)
+        step = lambda d: layer.kernel_fn(d, st)  # noqa: E731
+    del weights
+    tokens = data["config"]["tokens"]
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        out = step(data)
+    barrier()
+    layer.check_status(st)
+    ids = out[2]
+    routes_local = int(st["offsets"][-1].item())
+
+    # ---- device-timed region: K steps, inputs resident in HBM (per-step working set >> L2)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    launches0 = _lib.LAUNCHES
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step(data)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1) / args.steps
+    launches = _lib.LAUNCHES - launches0
+    clocks = sampler.stop()
+
+    # ---- per-kernel times of the same steps (events between launches), for the roofline
+    st["marks"] = []
+    per_stage = {}
+    for _ in range(min(args.steps, 5)):
+        st["marks"].clear()
+        step(data)
+        torch.cuda.synchronize()
+        for name, t in layer.stage_times_ms(st["marks"]):
+            per_stage.setdefault(name, []).append(t)
+    st["marks"] = None
+    stage_ms = {k: sum(v) / len(v) for k, v in per_stage.items()}
+
+    # ---- end to end through kernel_fn with host buffers
+    host_in = {k: data[k].cpu().pin_memory() for k in ("stream", "attn_input", "positions", "cache_loc", "seq_lens",
+                                                       "cu_seqlens_q", "page_table", "cache_seqlens")}
+    h2d = sum(v.numel() * v.element_size() for v in host_in.values())
+    host_out = [torch.empty_like(o, device="cpu").pin_memory() for o in out]
+    d2h = sum(v.numel() * v.element_size() for v in host_out)
+    dev_in = dict(data)
+
+    def e2e_step():
+        for k, v in host_in.items():
+            dev_in[k] = v.to(dev, non_blocking=True)
+        o = step(dev_in)
+        for dst, src in zip(host_out, o):
+            dst.copy_(src, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    t0e, t1e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0e.record()
+    for _ in range(args.steps):
+        e2e_step()
+    t1e.record()
+    barrier()
+    e2e_ms = t0e.elapsed_time(t1e) / args.steps
+    layer.check_status(st)
+
+    times = torch.tensor([ms, e2e_ms], device=dev)
+    if dist is not None:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = times.tolist()
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    pk = peaks()
+    routes = tokens * shape.top_k               # every route is computed somewhere
+    gate_up_flops = 2.0 * routes_local * (2 * shape.inter) * shape.moe_width
+    gu_ms = stage_ms.get("experts_gate_up")
+    roof = None
+    if gu_ms:
+        achieved = gate_up_flops / (gu_ms * 1e-3) / 1e12
+        roof = {"kernel": "grouped_nvfp4_kernel (experts gate/up + SiLU*up)", "bound": "tensor", "achieved": achieved,
+                "peak": pk["tflops"], "unit": "TFLOP/s", "frac": achieved / pk["tflops"], "traffic": None,
+                "peak_source": pk["source"], "launch_ms": gu_ms}
+    total_flops = layer_flops(shape, SEQS, SEQ_LEN, routes)
+    line = {
+        "metric": METRIC, "value": tokens * world / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16 activations, NVFP4 expert weights (W4A16), fp8 e4m3 attention",
+        "data": "synthetic",
+        "config": {"workload": "full decoder layer, mid prefill (BASELINE config 3): 4 x 4096 tokens per GPU, hidden "
+                               "4096, 32q/8kv x 128, page 64, 128 experts top-8 x 1536 NVFP4 + shared 4096",
+                   "tokens_per_gpu": tokens, "expert_parallel": world, "l2": "per-step working set (weights 2.6 GB) "
+                   "exceeds the 126 MB L2; no explicit flush"},
+        "layer_tflops": total_flops / (ms * 1e-3) / 1e12,
+        "stage_ms": {k: round(v, 4) for k, v in stage_ms.items()},
+        "roofline": roof,
+        "e2e": {"value": tokens * world / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches,
+        "clocks": clocks,
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline_leg()
+    print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

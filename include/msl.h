@@ -1,0 +1,148 @@
+/* C ABI of libmsl: the B200 (sm_100a) kernels of one MoE decoder layer at prefill.
+ *
+ * Every entry point takes raw device pointers, sizes and a CUDA stream (cudaStream_t passed as
+ * void*), launches asynchronously on that stream, allocates nothing, never synchronises and
+ * returns an int status (0 = launched; negative = rejected on the host before any launch).
+ * Kernels that wait on hardware barriers bound every wait; a wait that runs out stores
+ * MSL_ERR_DEVICE_TIMEOUT into the caller-provided `status` word (device memory, may be NULL),
+ * which the caller reads after the stream has drained.
+ *
+ * The reference (nvbkdw/muse-spark-open-challenge) has no C interface for this path: its layer is
+ * a Python `kernel_fn(data, state)` that launches Triton / NVRTC / library kernels.  Each entry
+ * below names the launch site in muse_prefill_layer/submission.py that it replaces.
+ */
+#ifndef MSL_H_
+#define MSL_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MSL_ABI_VERSION 1
+
+enum {
+  MSL_OK = 0,
+  MSL_ERR_ARG = -1,
+  MSL_ERR_ALIGN = -2,
+  MSL_ERR_CUDA = -3,
+  MSL_ERR_TENSORMAP = -4,
+  MSL_ERR_DEVICE_TIMEOUT = -5,
+  MSL_ERR_CAPACITY = -6,
+  MSL_ERR_UNSUPPORTED = -7
+};
+
+/* Output modes of the GEMMs. */
+enum {
+  MSL_OUT_BF16 = 0,        /* c: bf16 [m, n] */
+  MSL_OUT_F32 = 1,         /* c: fp32 [m, n] */
+  MSL_OUT_SWIGLU_BF16 = 2  /* b rows come in blocks of 256 = 128 gate rows then their 128 up rows;
+                              c: bf16 [m, n/2] = silu(gate) * up */
+};
+
+int msl_abi_version(void);
+const char* msl_status_string(int code);
+
+/* Dense BF16 GEMM, fp32 accumulate: c[m, n] = alpha * sum_{s < segs} A_s * B_s^T with
+ * A_s = a[:, s*a_seg_stride : s*a_seg_stride + k] and B_s = b[:, s*b_seg_stride : ... + k];
+ * a is bf16 [m, lda] row-major, b is bf16 [n, ldb] row-major (a weight matrix as stored).
+ * Two segments with a_seg_stride = 0 give the router's "BF16 hi + lo" product.
+ * Replaces torch.mm at submission.py:1082 (QKV+gate), :1096 (O), :1113 (router, fp32 out),
+ * :1116 (pooler), :1135 (unpooler).  lda, ldb, k, strides: multiples of 8; a, b: 16-byte aligned. */
+int msl_gemm_bf16(const void* a, int64_t lda, const void* b, int64_t ldb, void* c, int64_t ldc, int m, int n,
+                  int k, int segs, int a_seg_stride, int b_seg_stride, int out_mode, float alpha, int* status,
+                  void* stream);
+
+/* Per-head RMS norm (eps 1e-5, no weight) of q and k, interleaved RoPE when inv_freq != NULL
+ * (pairs (2i, 2i+1) rotate by positions[t] * inv_freq[i]), q -> E4M3 [tokens, hq, head_dim],
+ * k / *k_scale and v / *v_scale -> E4M3 written to row cache_loc[t] of the paged caches
+ * ([cache_rows, hkv, head_dim]).  qkv is the bf16 projection output, q heads then k heads then v
+ * heads in each row of pitch ld.  A cache_loc outside [0, cache_rows) is skipped and reported in
+ * *status.  Replaces _qk_rope_store_kernel (submission.py:740-785, launch :1086-1089).
+ * head_dim 64 or 128. */
+int msl_qk_rope_store(const void* qkv, int64_t ld, const int64_t* positions, const int64_t* cache_loc,
+                      const float* inv_freq, const float* k_scale, const float* v_scale, void* q8, void* k_cache,
+                      void* v_cache, int tokens, int hq, int hkv, int head_dim, int64_t cache_rows, int* status,
+                      void* stream);
+
+/* Residual boundary: b = branch * branch_scale (branch_scale may be NULL);
+ * stream_out = alpha * stream_in + beta * rms(b, eps_branch);
+ * hidden_out = bf16(rms(stream_out, eps_out) * norm_w).  alpha, beta, norm_w, branch_scale: fp32
+ * [hidden], prepared once from the gate / norm weights.  Replaces _attn_boundary_kernel and
+ * _ffn_boundary_kernel (submission.py:806-855, launches :1101, :1138). */
+int msl_boundary(const void* branch, int64_t ld_branch, const float* branch_scale, const float* stream_in,
+                 const float* alpha, const float* beta, const float* norm_w, float* stream_out, void* hidden_out,
+                 int64_t ld_hidden, int tokens, int hidden, float eps_branch, float eps_out, void* stream);
+
+/* Router top-k with slot assignment.  logits fp32 [tokens, ld]: columns [0, n_experts) and, when
+ * hilo != 0, a second half [n_experts, 2 n_experts) that is added (BF16 hi + lo router product).
+ * score = sigmoid(multiplier * logit); top_k of score + bias, lowest index first among ties;
+ * weights = score / (sum of the picked scores + 1e-15).  Experts [*local_start, *local_start +
+ * n_local) modulo n_experts are local: local_ids holds id - local_start (or -1) and slots the
+ * route's index among its expert's routes, drawn from counts[n_local] (zeroed by the caller).
+ * Replaces _routing_kernel (submission.py:859-886, launch :1114). */
+int msl_route_topk(const float* logits, int64_t ld, int hilo, const float* bias, float multiplier,
+                   const int* local_start, int tokens, int n_experts, int top_k, int n_local, int* ids,
+                   float* weights, int* local_ids, int* slots, int* counts, void* stream);
+
+/* Token dispatch: copies row t of x (bf16 [tokens, ldx], `width` columns) to slab row
+ * offsets[e] + slot for every local route, offsets being the exclusive prefix sum of counts
+ * (written to offsets_out[n_local + 1] when not NULL); rowmap[tokens, top_k] receives the slab row
+ * or -1.  With norm_w (fp32 [width]) the row is first RMS-normalised (eps 1e-5) and scaled.
+ * Replaces _dispatch_kernel (submission.py:890-899, launch :1123) with a compact slab instead of
+ * one token-count-sized slab per expert. */
+int msl_dispatch(const void* x, int64_t ldx, const float* norm_w, const int* local_ids, const int* slots,
+                 const int* counts, int tokens, int n_local, int top_k, int width, void* slab, int64_t slab_rows,
+                 int* rowmap, int* offsets_out, int* status, void* stream);
+
+/* Weighted combine: out[t] = sum_j weights[t, j] * rms(y[rowmap[t, j]] * post_w, eps 1e-8)
+ * (+ addend[t] when not NULL); rowmap < 0 contributes nothing.  y: bf16 [slab rows, width].
+ * Replaces _combine_kernel (submission.py:917-928, launch :1132). */
+int msl_combine(const void* y, const int* rowmap, const float* weights, const float* post_w, const void* addend,
+                int64_t ld_addend, void* out, int64_t ld_out, int tokens, int top_k, int width, void* stream);
+
+/* Rows of a re-tiled NVFP4 bank: `rows` padded to whole 256-row tiles (for a gate/up bank,
+ * interleave != 0, each half padded to whole 128-row blocks). */
+int64_t msl_nvfp4_padded_rows(int rows, int interleave);
+
+/* Load-time, lossless re-tiling of an NVFP4 expert bank (weights w13 / w2 of the reference,
+ * baseline.py:74-79): codes uint8 [experts, rows, k/2], scales e4m3 [experts, rows, k/16] ->
+ * tiles [experts, n_padded/256, k/64, 256, 32] and [.., 256, 4] consumed by
+ * msl_grouped_gemm_nvfp4.  With interleave != 0 the bank is gate rows then up rows and tile j
+ * holds gate rows [128 j, 128 j + 128) followed by their up rows.  A permutation of the input
+ * bytes and nibbles; padding rows are zero.  Takes the place of the reference's load-time
+ * weight repack (submission.py:934-950).  k: multiple of 64. */
+int msl_nvfp4_repack(const void* src_codes, const void* src_scales, void* dst_codes, void* dst_scales, int experts,
+                     int rows, int k, int interleave, void* stream);
+
+/* Grouped expert GEMM, NVFP4 weights x BF16 activations, fp32 accumulate:
+ * out[r, :] = global_scales[e] * x[r, :] * dq(W_e)^T for slab rows offsets[e] <= r < offsets[e+1];
+ * x bf16 [slab_rows, k]; out bf16 [slab_rows, ld_out] with n_out valid columns; with swiglu != 0
+ * the bank is an interleaved gate/up bank and out = silu(gate) * up (n_out = intermediate size).
+ * offsets is device memory [experts + 1]; no host synchronisation.  Replaces the two grouped GEMM
+ * launches and _silu_mul_kernel (submission.py:956-1002, 903-913; launches :1128-1130). */
+int msl_grouped_gemm_nvfp4(const void* x, int64_t slab_rows, const void* codes, const void* scales,
+                           const float* global_scales, const int* offsets, void* out, int64_t ld_out, int experts,
+                           int n_padded, int k, int n_out, int swiglu, int* status, void* stream);
+
+/* Causal attention of the new tokens over the paged FP8 cache (which already holds the new
+ * tokens' K/V rows): q8 e4m3 [tokens, hq, head_dim]; caches e4m3 [cache_rows, hkv, head_dim];
+ * request b owns query rows cu_seqlens_q[b] .. cu_seqlens_q[b+1] at positions seq_lens[b] + i and
+ * sees keys 0 .. position (the last `window` of them when window > 0) through
+ * page_table[b, pos / page_size].  softmax_scale = sm_scale * qk_scale_factor; *k_scale and
+ * *v_scale dequantise the cache.  out bf16 [tokens, ld_out], column h * head_dim + d.  With gate
+ * != NULL (bf16, pitch ld_gate, same columns) the epilogue applies the per-head RMS norm (eps
+ * 1e-5) and multiplies by sigmoid(gate).  Replaces submission.py:639-721 (gather, attn_fwd,
+ * combine, library fallback) and _onorm_gate_kernel (:789-802).  head_dim 64 or 128; hq / hkv a
+ * power of two <= 128. */
+int msl_attention_fp8(const void* q8, const void* k_cache, const void* v_cache, const int* page_table,
+                      int max_pages, const int* seq_lens, const int* cu_seqlens_q, const float* k_scale,
+                      const float* v_scale, float softmax_scale, int batch, int max_q_len, int tokens, int hq,
+                      int hkv, int head_dim, int page_size, int window, int64_t cache_rows, void* out,
+                      int64_t ld_out, const void* gate, int64_t ld_gate, int* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MSL_H_ */

@@ -1,0 +1,542 @@
+// The bandwidth-bound kernels of the layer: QK-norm + RoPE + FP8 quantise + paged cache store,
+// the two residual boundaries, the router's top-k with slot assignment, token dispatch and the
+// weighted combine.  All use 128-bit global accesses and keep a row in registers so each tensor
+// crosses HBM once.
+#include "msl_common.cuh"
+#include "msl_host.h"
+
+namespace msl {
+
+__device__ __forceinline__ void unpack8(const uint4& q, float (&v)[8]) {
+  v[0] = bf16_bits_to_f32(q.x & 0xffffu); v[1] = bf16_bits_to_f32(q.x >> 16);
+  v[2] = bf16_bits_to_f32(q.y & 0xffffu); v[3] = bf16_bits_to_f32(q.y >> 16);
+  v[4] = bf16_bits_to_f32(q.z & 0xffffu); v[5] = bf16_bits_to_f32(q.z >> 16);
+  v[6] = bf16_bits_to_f32(q.w & 0xffffu); v[7] = bf16_bits_to_f32(q.w >> 16);
+}
+__device__ __forceinline__ uint4 pack8(const float (&v)[8]) {
+  return make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
+                    pack_bf16x2(v[6], v[7]));
+}
+__device__ __forceinline__ uint32_t fp8x4(float a, float b, float c, float d) {
+  const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+  const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+  return lo | (hi << 16);
+}
+
+// Sum over all threads of a block; `scratch` holds one float per warp (+1).  Every thread
+// receives the total.  `n` values are reduced at once.
+template <int N>
+__device__ __forceinline__ void block_sum(float (&v)[N], float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+#pragma unroll
+  for (int i = 0; i < N; ++i) v[i] = warp_sum(v[i]);
+  __syncthreads();   // scratch may still be read from a previous use
+  if (lane == 0) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) scratch[warp * N + i] = v[i];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < N; ++i) {
+    float s = 0.f;
+    for (int w = 0; w < nwarp; ++w) s += scratch[w * N + i];
+    v[i] = s;
+  }
+}
+
+// ============================================================================ QK-norm + RoPE + FP8 + cache store
+// One group of D/8 lanes per (token, head); each lane owns 8 consecutive channels (one 16-byte load).
+// Heads 0..HQ-1 are queries, the next HKV keys, the next HKV values (the row layout of the QKV+gate
+// projection; the gate columns after them are not read).
+template <int D>
+__global__ void __launch_bounds__(256)
+qk_rope_store_kernel(const __nv_bfloat16* __restrict__ qkv, int64_t ld, const int64_t* __restrict__ positions,
+                     const int64_t* __restrict__ cache_loc, const float* __restrict__ inv_freq,
+                     const float* __restrict__ k_scale_p, const float* __restrict__ v_scale_p,
+                     uint8_t* __restrict__ q8, uint8_t* __restrict__ k_cache, uint8_t* __restrict__ v_cache,
+                     int tokens, int hq, int hkv, int64_t cache_rows, int* status) {
+  constexpr int LPH = D / 8;   // lanes per head
+  const int nh = hq + 2 * hkv;
+  const int64_t item = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) / LPH;
+  const int sub = threadIdx.x % LPH;
+  const bool live = item < static_cast<int64_t>(tokens) * nh;
+  const int t = live ? static_cast<int>(item / nh) : 0;
+  const int h = live ? static_cast<int>(item % nh) : 0;
+  float v[8];
+  {
+    const uint4 raw = live ? *reinterpret_cast<const uint4*>(qkv + t * ld + h * D + sub * 8) : make_uint4(0, 0, 0, 0);
+    unpack8(raw, v);
+  }
+  const bool is_v = h >= hq + hkv;
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) ss += v[i] * v[i];
+#pragma unroll
+  for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if (!live) return;
+  if (!is_v) {
+    const float r = 1.0f / sqrtf(ss / D + 1e-5f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] *= r;
+    if (inv_freq != nullptr) {
+      const float pos = static_cast<float>(positions[t]);
+#pragma unroll
+      for (int i = 0; i < 8; i += 2) {
+        const float ang = pos * inv_freq[sub * 4 + i / 2];
+        float sn, cs;
+        sincosf(ang, &sn, &cs);
+        const float e = v[i], o = v[i + 1];
+        v[i] = e * cs - o * sn;
+        v[i + 1] = e * sn + o * cs;
+      }
+    }
+  }
+  uint8_t* dst;
+  if (h < hq) {
+    dst = q8 + (static_cast<int64_t>(t) * hq + h) * D + sub * 8;
+  } else {
+    const float scale = is_v ? *v_scale_p : *k_scale_p;
+    // x / scale as the reference divides (reference.py:181-182); a reciprocal multiply would
+    // round differently when the scale is not a power of two.
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = v[i] / scale;
+    const int64_t row = cache_loc[t];
+    if (row < 0 || row >= cache_rows) {
+      report_error(status, MSL_ERR_CAPACITY);
+      return;
+    }
+    const int kvh = is_v ? h - hq - hkv : h - hq;
+    dst = (is_v ? v_cache : k_cache) + (row * hkv + kvh) * D + sub * 8;
+  }
+  *reinterpret_cast<uint2*>(dst) = make_uint2(fp8x4(v[0], v[1], v[2], v[3]), fp8x4(v[4], v[5], v[6], v[7]));
+}
+
+// ============================================================================ residual boundary
+// branch' = branch * branch_scale (optional); s_out = alpha * s_in + beta * rms(branch', eps_branch);
+// h_out = rms(s_out, eps_out) * norm_w.  One block per token row; the row stays in registers.
+template <int MAXC>
+__global__ void __launch_bounds__(256)
+boundary_kernel(const __nv_bfloat16* __restrict__ branch, int64_t ld_branch, const float* __restrict__ branch_scale,
+                const float* __restrict__ s_in, const float* __restrict__ alpha, const float* __restrict__ beta,
+                const float* __restrict__ norm_w, float* __restrict__ s_out, __nv_bfloat16* __restrict__ h_out,
+                int64_t ld_h, int hidden, float eps_branch, float eps_out) {
+  __shared__ float scratch[32];
+  const int64_t row = blockIdx.x;
+  const int chunks = hidden / 8;
+  float b[MAXC][8], s[MAXC][8];
+  float ss[1] = {0.f};
+#pragma unroll
+  for (int c = 0; c < MAXC; ++c) {
+    const int ch = threadIdx.x + c * blockDim.x;
+    if (ch < chunks) {
+      unpack8(*reinterpret_cast<const uint4*>(branch + row * ld_branch + ch * 8), b[c]);
+      if (branch_scale != nullptr) {
+        const float4 w0 = *reinterpret_cast<const float4*>(branch_scale + ch * 8);
+        const float4 w1 = *reinterpret_cast<const float4*>(branch_scale + ch * 8 + 4);
+        b[c][0] *= w0.x; b[c][1] *= w0.y; b[c][2] *= w0.z; b[c][3] *= w0.w;
+        b[c][4] *= w1.x; b[c][5] *= w1.y; b[c][6] *= w1.z; b[c][7] *= w1.w;
+      }
+      const float4 s0 = *reinterpret_cast<const float4*>(s_in + row * hidden + ch * 8);
+      const float4 s1 = *reinterpret_cast<const float4*>(s_in + row * hidden + ch * 8 + 4);
+      s[c][0] = s0.x; s[c][1] = s0.y; s[c][2] = s0.z; s[c][3] = s0.w;
+      s[c][4] = s1.x; s[c][5] = s1.y; s[c][6] = s1.z; s[c][7] = s1.w;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss[0] += b[c][i] * b[c][i];
+    }
+  }
+  block_sum<1>(ss, scratch);
+  const float rb = 1.0f / sqrtf(ss[0] / hidden + eps_branch);
+  float s2[1] = {0.f};
+#pragma unroll
+  for (int c = 0; c < MAXC; ++c) {
+    const int ch = threadIdx.x + c * blockDim.x;
+    if (ch < chunks) {
+      const float4 a0 = *reinterpret_cast<const float4*>(alpha + ch * 8);
+      const float4 a1 = *reinterpret_cast<const float4*>(alpha + ch * 8 + 4);
+      const float4 b0 = *reinterpret_cast<const float4*>(beta + ch * 8);
+      const float4 b1 = *reinterpret_cast<const float4*>(beta + ch * 8 + 4);
+      const float al[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+      const float be[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        s[c][i] = al[i] * s[c][i] + be[i] * (b[c][i] * rb);
+        s2[0] += s[c][i] * s[c][i];
+      }
+      float* dst = s_out + row * hidden + ch * 8;
+      *reinterpret_cast<float4*>(dst) = make_float4(s[c][0], s[c][1], s[c][2], s[c][3]);
+      *reinterpret_cast<float4*>(dst + 4) = make_float4(s[c][4], s[c][5], s[c][6], s[c][7]);
+    }
+  }
+  block_sum<1>(s2, scratch);
+  const float rs = 1.0f / sqrtf(s2[0] / hidden + eps_out);
+#pragma unroll
+  for (int c = 0; c < MAXC; ++c) {
+    const int ch = threadIdx.x + c * blockDim.x;
+    if (ch < chunks) {
+      const float4 w0 = *reinterpret_cast<const float4*>(norm_w + ch * 8);
+      const float4 w1 = *reinterpret_cast<const float4*>(norm_w + ch * 8 + 4);
+      const float w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+      float o[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = s[c][i] * rs * w[i];
+      *reinterpret_cast<uint4*>(h_out + row * ld_h + ch * 8) = pack8(o);
+    }
+  }
+}
+
+// ============================================================================ router top-k + slots
+// One warp per token.  score = sigmoid(multiplier * logit) in fp64 rounded to fp32 (the reference
+// forms the logits and the sigmoid in fp64, reference.py:422-423); biased = score + bias chooses,
+// lowest index winning exact ties; weights = score / (sum of picked + 1e-15).  Routes to experts
+// [local_start, local_start + n_local) (modulo n_experts) get a slot from a per-expert counter:
+// a shared-memory histogram per block, then one global atomic per (block, expert).
+template <int MAXPL>   // experts per lane, n_experts <= 32 * MAXPL
+__global__ void __launch_bounds__(256)
+route_topk_kernel(const float* __restrict__ logits, int64_t ld, int hilo, const float* __restrict__ bias,
+                  float multiplier, const int* __restrict__ local_start_p, int tokens, int n_experts, int top_k,
+                  int n_local, int* __restrict__ ids, float* __restrict__ weights, int* __restrict__ local_ids,
+                  int* __restrict__ slots, int* __restrict__ counts) {
+  extern __shared__ int hist[];          // [n_local] counts, then [n_local] global bases
+  int* base = hist + n_local;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+  for (int i = threadIdx.x; i < n_local; i += blockDim.x) hist[i] = 0;
+  __syncthreads();
+
+  float score[MAXPL], biased[MAXPL];
+  int my_e = -1, my_rank = 0;           // lane j < top_k owns route j
+  float my_w = 0.f;
+  int my_id = 0;
+  if (t < tokens) {
+#pragma unroll
+    for (int i = 0; i < MAXPL; ++i) {
+      const int e = lane + 32 * i;
+      if (e < n_experts) {
+        float x = logits[t * ld + e];
+        if (hilo) x += logits[t * ld + n_experts + e];
+        const double z = static_cast<double>(x) * static_cast<double>(multiplier);
+        score[i] = static_cast<float>(1.0 / (1.0 + exp(-z)));
+        biased[i] = score[i] + bias[e];
+      } else {
+        score[i] = 0.f;
+        biased[i] = -INFINITY;
+      }
+    }
+    float sum = 0.f;
+    const int ls = *local_start_p;
+    for (int j = 0; j < top_k; ++j) {
+      float best = -INFINITY;
+      int best_e = 0x7fffffff;
+#pragma unroll
+      for (int i = 0; i < MAXPL; ++i) {
+        const int e = lane + 32 * i;
+        if (biased[i] > best) { best = biased[i]; best_e = e; }   // ascending e: first hit is the lowest index
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+        if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+      }
+      // the owner removes the winner and broadcasts its unbiased score
+      float sc = 0.f;
+#pragma unroll
+      for (int i = 0; i < MAXPL; ++i) {
+        if (lane + 32 * i == best_e) { sc = score[i]; biased[i] = -INFINITY; }
+      }
+      sc = __shfl_sync(0xffffffffu, sc, best_e & 31);
+      sum += sc;
+      if (lane == j) { my_id = best_e; my_w = sc; }
+    }
+    if (lane < top_k) {
+      my_w = my_w / (sum + 1e-15f);
+      int le = (my_id - ls) % n_experts;
+      if (le < 0) le += n_experts;
+      my_e = le < n_local ? le : -1;
+      if (my_e >= 0) my_rank = atomicAdd(&hist[my_e], 1);
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_local; i += blockDim.x) base[i] = hist[i] ? atomicAdd(&counts[i], hist[i]) : 0;
+  __syncthreads();
+  if (t < tokens && lane < top_k) {
+    const int64_t o = static_cast<int64_t>(t) * top_k + lane;
+    ids[o] = my_id;
+    weights[o] = my_w;
+    local_ids[o] = my_e;
+    slots[o] = my_e >= 0 ? base[my_e] + my_rank : -1;
+  }
+}
+
+// ============================================================================ dispatch
+// Copies each token's row to one slab row per local route: row = offset[expert] + slot, offsets
+// being the exclusive prefix sum of the per-expert counts (recomputed per block; block 0 also
+// publishes it for the grouped GEMM).  With norm_w the row is RMS-normalised (eps 1e-5) and
+// scaled first (the pooled layer's pre-expert norm, submission.py:890-899).
+__global__ void __launch_bounds__(256)
+dispatch_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, const float* __restrict__ norm_w,
+                const int* __restrict__ local_ids, const int* __restrict__ slots, const int* __restrict__ counts,
+                int n_local, int top_k, int width, __nv_bfloat16* __restrict__ slab, int64_t slab_rows,
+                int* __restrict__ rowmap, int* __restrict__ offsets_out, int* status) {
+  extern __shared__ int offs[];          // [n_local + 1]
+  __shared__ float scratch[32];
+  const int t = blockIdx.x;
+  if (threadIdx.x < 32) {
+    // exclusive scan by one warp, n_local <= 1024
+    int carry = 0;
+    for (int b0 = 0; b0 < n_local; b0 += 32) {
+      const int i = b0 + threadIdx.x;
+      const int c = i < n_local ? counts[i] : 0;
+      int inc = c;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int n = __shfl_up_sync(0xffffffffu, inc, o);
+        if (threadIdx.x >= o) inc += n;
+      }
+      if (i < n_local) offs[i] = carry + inc - c;
+      carry += __shfl_sync(0xffffffffu, inc, 31);
+    }
+    if (threadIdx.x == 0) offs[n_local] = carry;
+  }
+  __syncthreads();
+  if (t == 0 && offsets_out != nullptr)
+    for (int i = threadIdx.x; i <= n_local; i += blockDim.x) offsets_out[i] = offs[i];
+
+  const int chunks = width / 8;
+  float ss[1] = {0.f};
+  if (norm_w != nullptr) {
+    for (int ch = threadIdx.x; ch < chunks; ch += blockDim.x) {
+      float v[8];
+      unpack8(*reinterpret_cast<const uint4*>(x + t * ldx + ch * 8), v);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss[0] += v[i] * v[i];
+    }
+    block_sum<1>(ss, scratch);
+  }
+  const float r = norm_w != nullptr ? 1.0f / sqrtf(ss[0] / width + 1e-5f) : 1.0f;
+  int rows[16];
+  int nr = 0;
+  for (int j = 0; j < top_k && j < 16; ++j) {
+    const int le = local_ids[t * top_k + j];
+    int row = -1;
+    if (le >= 0) {
+      row = offs[le] + slots[t * top_k + j];
+      if (row >= slab_rows) {
+        if (threadIdx.x == 0) report_error(status, MSL_ERR_CAPACITY);
+        row = -1;
+      }
+    }
+    if (threadIdx.x == 0) rowmap[t * top_k + j] = row;
+    if (row >= 0) rows[nr++] = row;
+  }
+  if (nr == 0) return;
+  for (int ch = threadIdx.x; ch < chunks; ch += blockDim.x) {
+    uint4 raw = *reinterpret_cast<const uint4*>(x + t * ldx + ch * 8);
+    if (norm_w != nullptr) {
+      float v[8];
+      unpack8(raw, v);
+      const float4 w0 = *reinterpret_cast<const float4*>(norm_w + ch * 8);
+      const float4 w1 = *reinterpret_cast<const float4*>(norm_w + ch * 8 + 4);
+      v[0] *= r * w0.x; v[1] *= r * w0.y; v[2] *= r * w0.z; v[3] *= r * w0.w;
+      v[4] *= r * w1.x; v[5] *= r * w1.y; v[6] *= r * w1.z; v[7] *= r * w1.w;
+      raw = pack8(v);
+    }
+    for (int j = 0; j < nr; ++j)
+      *reinterpret_cast<uint4*>(slab + static_cast<int64_t>(rows[j]) * width + ch * 8) = raw;
+  }
+}
+
+// ============================================================================ weighted combine
+// out[t] = sum_j w[t, j] * rms(y[rowmap[t, j]] * post_w, eps 1e-8)  (+ addend[t]); routes with
+// rowmap < 0 (another rank's expert) contribute nothing (reference.py:427-444).
+// One block per token, every thread owns one 8-channel chunk of every route's row.
+template <int MAXK, int MAXC>
+__global__ void __launch_bounds__(512)
+combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ rowmap, const float* __restrict__ w,
+               const float* __restrict__ post_w, const __nv_bfloat16* __restrict__ addend, int64_t ld_add,
+               __nv_bfloat16* __restrict__ out, int64_t ld_out, int top_k, int width) {
+  __shared__ float scratch[32 * MAXK];
+  const int t = blockIdx.x;
+  const int chunks = width / 8;
+  float acc[MAXC][8];
+#pragma unroll
+  for (int c = 0; c < MAXC; ++c)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[c][i] = 0.f;
+  int rows[MAXK];
+  float wt[MAXK];
+#pragma unroll
+  for (int j = 0; j < MAXK; ++j) {
+    rows[j] = j < top_k ? rowmap[t * top_k + j] : -1;
+    wt[j] = j < top_k ? w[t * top_k + j] : 0.f;
+  }
+#pragma unroll
+  for (int c = 0; c < MAXC; ++c) {
+    const int ch = threadIdx.x + c * blockDim.x;
+    // (MAXC > 1 only for rows wider than 8 * blockDim: the sums below then cover one chunk set at a time)
+    float v[MAXK][8];
+    float ss[MAXK];
+    float pw[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (ch < chunks) {
+      const float4 w0 = *reinterpret_cast<const float4*>(post_w + ch * 8);
+      const float4 w1 = *reinterpret_cast<const float4*>(post_w + ch * 8 + 4);
+      pw[0] = w0.x; pw[1] = w0.y; pw[2] = w0.z; pw[3] = w0.w; pw[4] = w1.x; pw[5] = w1.y; pw[6] = w1.z; pw[7] = w1.w;
+    }
+#pragma unroll
+    for (int j = 0; j < MAXK; ++j) {
+      ss[j] = 0.f;
+      if (rows[j] >= 0 && ch < chunks) {
+        unpack8(*reinterpret_cast<const uint4*>(y + static_cast<int64_t>(rows[j]) * width + ch * 8), v[j]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          v[j][i] *= pw[i];
+          ss[j] += v[j][i] * v[j][i];
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[j][i] = 0.f;
+      }
+    }
+    static_assert(MAXC == 1, "rows wider than 8 * blockDim need a two-pass sum");
+    block_sum<MAXK>(ss, scratch);
+#pragma unroll
+    for (int j = 0; j < MAXK; ++j) {
+      if (rows[j] >= 0) {
+        const float r = wt[j] / sqrtf(ss[j] / width + 1e-8f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[c][i] += v[j][i] * r;
+      }
+    }
+    if (ch < chunks) {
+      if (addend != nullptr) {
+        float a[8];
+        unpack8(*reinterpret_cast<const uint4*>(addend + t * ld_add + ch * 8), a);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[c][i] += a[i];
+      }
+      *reinterpret_cast<uint4*>(out + t * ld_out + ch * 8) = pack8(acc[c]);
+    }
+  }
+}
+
+}  // namespace msl
+
+using namespace msl;
+
+extern "C" int msl_qk_rope_store(const void* qkv, int64_t ld, const int64_t* positions, const int64_t* cache_loc,
+                                 const float* inv_freq, const float* k_scale, const float* v_scale, void* q8,
+                                 void* k_cache, void* v_cache, int tokens, int hq, int hkv, int head_dim,
+                                 int64_t cache_rows, int* status, void* stream) {
+  if (!qkv || !positions || !cache_loc || !k_scale || !v_scale || !q8 || !k_cache || !v_cache) return MSL_ERR_ARG;
+  if (tokens < 0 || hq <= 0 || hkv <= 0) return MSL_ERR_ARG;
+  if ((ld & 7) || (reinterpret_cast<uintptr_t>(qkv) & 15) || (reinterpret_cast<uintptr_t>(q8) & 7) ||
+      (reinterpret_cast<uintptr_t>(k_cache) & 7) || (reinterpret_cast<uintptr_t>(v_cache) & 7))
+    return MSL_ERR_ALIGN;
+  if (tokens == 0) return MSL_OK;
+  const int64_t items = static_cast<int64_t>(tokens) * (hq + 2 * hkv);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (head_dim == 128) {
+    const int64_t blocks = (items * 16 + 255) / 256;
+    qk_rope_store_kernel<128><<<static_cast<unsigned>(blocks), 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(qkv), ld, positions, cache_loc, inv_freq, k_scale, v_scale,
+        static_cast<uint8_t*>(q8), static_cast<uint8_t*>(k_cache), static_cast<uint8_t*>(v_cache), tokens, hq, hkv,
+        cache_rows, status);
+  } else if (head_dim == 64) {
+    const int64_t blocks = (items * 8 + 255) / 256;
+    qk_rope_store_kernel<64><<<static_cast<unsigned>(blocks), 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(qkv), ld, positions, cache_loc, inv_freq, k_scale, v_scale,
+        static_cast<uint8_t*>(q8), static_cast<uint8_t*>(k_cache), static_cast<uint8_t*>(v_cache), tokens, hq, hkv,
+        cache_rows, status);
+  } else {
+    return MSL_ERR_UNSUPPORTED;
+  }
+  return cudaGetLastError() == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
+}
+
+extern "C" int msl_boundary(const void* branch, int64_t ld_branch, const float* branch_scale, const float* stream_in,
+                            const float* alpha, const float* beta, const float* norm_w, float* stream_out,
+                            void* hidden_out, int64_t ld_hidden, int tokens, int hidden, float eps_branch,
+                            float eps_out, void* stream) {
+  if (!branch || !stream_in || !alpha || !beta || !norm_w || !stream_out || !hidden_out) return MSL_ERR_ARG;
+  if (tokens < 0 || hidden <= 0 || (hidden & 7) || (ld_branch & 7) || (ld_hidden & 7)) return MSL_ERR_ALIGN;
+  if (hidden > 8 * 256 * 4) return MSL_ERR_UNSUPPORTED;
+  if (tokens == 0) return MSL_OK;
+  const int chunks = hidden / 8;
+  int threads = std::min(256, ((chunks + 31) / 32) * 32);
+  const int per = (chunks + threads - 1) / threads;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  auto* b = static_cast<const __nv_bfloat16*>(branch);
+  auto* h = static_cast<__nv_bfloat16*>(hidden_out);
+  if (per <= 1)
+    boundary_kernel<1><<<tokens, threads, 0, st>>>(b, ld_branch, branch_scale, stream_in, alpha, beta, norm_w,
+                                                   stream_out, h, ld_hidden, hidden, eps_branch, eps_out);
+  else if (per <= 2)
+    boundary_kernel<2><<<tokens, threads, 0, st>>>(b, ld_branch, branch_scale, stream_in, alpha, beta, norm_w,
+                                                   stream_out, h, ld_hidden, hidden, eps_branch, eps_out);
+  else
+    boundary_kernel<4><<<tokens, threads, 0, st>>>(b, ld_branch, branch_scale, stream_in, alpha, beta, norm_w,
+                                                   stream_out, h, ld_hidden, hidden, eps_branch, eps_out);
+  return cudaGetLastError() == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
+}
+
+extern "C" int msl_route_topk(const float* logits, int64_t ld, int hilo, const float* bias, float multiplier,
+                              const int* local_start, int tokens, int n_experts, int top_k, int n_local, int* ids,
+                              float* weights, int* local_ids, int* slots, int* counts, void* stream) {
+  if (!logits || !bias || !local_start || !ids || !weights || !local_ids || !slots || !counts) return MSL_ERR_ARG;
+  if (tokens < 0 || n_experts <= 0 || top_k <= 0 || top_k > 32 || top_k > n_experts || n_local <= 0 ||
+      n_local > n_experts)
+    return MSL_ERR_ARG;
+  if (n_experts > 512) return MSL_ERR_UNSUPPORTED;
+  if (tokens == 0) return MSL_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int blocks = (tokens + 7) / 8;
+  const size_t smem = 2 * static_cast<size_t>(n_local) * sizeof(int);
+  if (n_experts <= 128)
+    route_topk_kernel<4><<<blocks, 256, smem, st>>>(logits, ld, hilo, bias, multiplier, local_start, tokens,
+                                                    n_experts, top_k, n_local, ids, weights, local_ids, slots, counts);
+  else if (n_experts <= 256)
+    route_topk_kernel<8><<<blocks, 256, smem, st>>>(logits, ld, hilo, bias, multiplier, local_start, tokens,
+                                                    n_experts, top_k, n_local, ids, weights, local_ids, slots, counts);
+  else
+    route_topk_kernel<16><<<blocks, 256, smem, st>>>(logits, ld, hilo, bias, multiplier, local_start, tokens,
+                                                     n_experts, top_k, n_local, ids, weights, local_ids, slots,
+                                                     counts);
+  return cudaGetLastError() == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
+}
+
+extern "C" int msl_dispatch(const void* x, int64_t ldx, const float* norm_w, const int* local_ids, const int* slots,
+                            const int* counts, int tokens, int n_local, int top_k, int width, void* slab,
+                            int64_t slab_rows, int* rowmap, int* offsets_out, int* status, void* stream) {
+  if (!x || !local_ids || !slots || !counts || !slab || !rowmap) return MSL_ERR_ARG;
+  if (tokens < 0 || n_local <= 0 || n_local > 1024 || top_k <= 0 || top_k > 16 || width <= 0) return MSL_ERR_ARG;
+  if ((width & 7) || (ldx & 7) || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(slab) & 15))
+    return MSL_ERR_ALIGN;
+  if (tokens == 0) return MSL_OK;
+  const int threads = std::min(256, ((width / 8 + 31) / 32) * 32);
+  dispatch_kernel<<<tokens, threads, (n_local + 1) * sizeof(int), static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), ldx, norm_w, local_ids, slots, counts, n_local, top_k, width,
+      static_cast<__nv_bfloat16*>(slab), slab_rows, rowmap, offsets_out, status);
+  return cudaGetLastError() == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
+}
+
+extern "C" int msl_combine(const void* y, const int* rowmap, const float* weights, const float* post_w,
+                           const void* addend, int64_t ld_addend, void* out, int64_t ld_out, int tokens, int top_k,
+                           int width, void* stream) {
+  if (!y || !rowmap || !weights || !post_w || !out) return MSL_ERR_ARG;
+  if (tokens < 0 || top_k <= 0 || top_k > 8 || width <= 0) return MSL_ERR_ARG;
+  if ((width & 7) || (ld_out & 7) || (ld_addend & 7)) return MSL_ERR_ALIGN;
+  if (width > 8 * 512) return MSL_ERR_UNSUPPORTED;
+  if (tokens == 0) return MSL_OK;
+  const int threads = ((width / 8 + 31) / 32) * 32;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  auto* yy = static_cast<const __nv_bfloat16*>(y);
+  auto* ad = static_cast<const __nv_bfloat16*>(addend);
+  auto* oo = static_cast<__nv_bfloat16*>(out);
+  if (top_k <= 4)
+    combine_kernel<4, 1><<<tokens, threads, 0, st>>>(yy, rowmap, weights, post_w, ad, ld_addend, oo, ld_out, top_k,
+                                                     width);
+  else
+    combine_kernel<8, 1><<<tokens, threads, 0, st>>>(yy, rowmap, weights, post_w, ad, ld_addend, oo, ld_out, top_k,
+                                                     width);
+  return cudaGetLastError() == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
+}

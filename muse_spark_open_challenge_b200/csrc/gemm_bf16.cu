@@ -1,0 +1,316 @@
+// Dense BF16 GEMM on tcgen05: C[m, n] = sum over K segments of A[m, k] * B[n, k]^T, fp32
+// accumulation in tensor memory.
+//
+// Replaces the cuBLAS calls the reference's layer makes through torch.mm for the QKV+gate, output,
+// pooler, unpooler and router projections (muse_prefill_layer/submission.py:1082,1096,1113,1116,
+// 1135); the fused SiLU(gate)*up epilogue also serves the BF16 shared expert.
+//
+// One persistent CTA per SM, 192 threads:
+//   warp 0     TMA producer: A tile 128x64 and B tile BNx64 (bf16, 128-byte swizzle) per stage
+//   warp 1     allocates tensor memory and issues tcgen05.mma (M=128, N=BN, K=16), 4 per stage
+//   warps 2-5  epilogue: tcgen05.ld the fp32 accumulator (one row per thread), convert, store
+// Two accumulator buffers (2 x BN columns of TMEM) let the epilogue of one tile overlap the main
+// loop of the next.  Every mbarrier wait is bounded; a wait that runs out records
+// MSL_ERR_DEVICE_TIMEOUT, and all roles fall through to the common teardown that frees the TMEM.
+#include "msl_common.cuh"
+#include "msl_host.h"
+
+namespace msl {
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;
+
+template <int BN, int STAGES>
+struct GemmSmem {
+  static constexpr int kABytes = kBM * kBK * 2;
+  static constexpr int kBBytes = BN * kBK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kBarOffset = STAGES * kStageBytes;
+  // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], tmem base, abort flag
+  static constexpr int kTotal = kBarOffset + (2 * STAGES + 4) * 8 + 16;
+};
+
+struct GemmArgs {
+  void* c;
+  int64_t ldc;
+  int m, n, k;           // k = elements per segment
+  int segs;              // number of K segments accumulated into one output
+  int a_seg_stride;      // A column offset (elements) added per segment
+  int b_seg_stride;      // B column offset (elements) added per segment
+  float alpha;
+  int* status;
+};
+
+// Tile order: groups of 16 M-tiles sweep N together so one wave of CTAs re-uses a band of A and
+// a band of B out of L2.
+__device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int& mt, int& nt) {
+  constexpr int GM = 16;
+  const int per_group = GM * n_tiles;
+  const int g = t / per_group;
+  const int first = g * GM;
+  const int gm = min(GM, m_tiles - first);
+  const int r = t - g * per_group;
+  mt = first + r % gm;
+  nt = r / gm;
+}
+
+template <int BN, int OUT>
+__device__ __forceinline__ void store_chunk(const GemmArgs& p, int row, int col0, const uint32_t (&acc)[32],
+                                            const uint32_t (&acc2)[32]) {
+  // One thread owns 32 consecutive output columns of one row.
+  if (row >= p.m) return;
+  if constexpr (OUT == MSL_OUT_F32) {
+    float* dst = reinterpret_cast<float*>(p.c) + static_cast<int64_t>(row) * p.ldc + col0;
+    if (col0 + 32 <= p.n && (p.ldc & 3) == 0) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        float4 v = make_float4(__uint_as_float(acc[j]) * p.alpha, __uint_as_float(acc[j + 1]) * p.alpha,
+                               __uint_as_float(acc[j + 2]) * p.alpha, __uint_as_float(acc[j + 3]) * p.alpha);
+        *reinterpret_cast<float4*>(dst + j) = v;
+      }
+    } else {
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.n) dst[j] = __uint_as_float(acc[j]) * p.alpha;
+    }
+  } else {
+    float v[32];
+    if constexpr (OUT == MSL_OUT_SWIGLU_BF16) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const float g = __uint_as_float(acc[j]) * p.alpha;
+        const float u = __uint_as_float(acc2[j]) * p.alpha;
+        v[j] = g / (1.0f + __expf(-g)) * u;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(acc[j]) * p.alpha;
+    }
+    const int n_out = (OUT == MSL_OUT_SWIGLU_BF16) ? p.n / 2 : p.n;
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.c) + static_cast<int64_t>(row) * p.ldc + col0;
+    if (col0 + 32 <= n_out && (p.ldc & 7) == 0) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        uint4 q = make_uint4(pack_bf16x2(v[j], v[j + 1]), pack_bf16x2(v[j + 2], v[j + 3]),
+                             pack_bf16x2(v[j + 4], v[j + 5]), pack_bf16x2(v[j + 6], v[j + 7]));
+        *reinterpret_cast<uint4*>(dst + j) = q;
+      }
+    } else {
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < n_out) dst[j] = __float2bfloat16(v[j]);
+    }
+  }
+}
+
+template <int BN, int STAGES, int OUT>
+__global__ void __launch_bounds__(192, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, GemmArgs p) {
+  using S = GemmSmem<BN, STAGES>;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  // The swizzled tiles need 1024-byte alignment; the dynamic window is aligned by hand.
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + S::kBarOffset);
+  uint64_t* empty = full + STAGES;
+  uint64_t* tmem_full = empty + STAGES;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile uint32_t* abort_flag = tmem_base_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int m_tiles = (p.m + kBM - 1) / kBM;
+  const int n_tiles = (p.n + BN - 1) / BN;
+  const int total_tiles = m_tiles * n_tiles;
+  const int kb_per_seg = (p.k + kBK - 1) / kBK;
+  const int k_blocks = kb_per_seg * p.segs;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full[a], 1);
+      mbar_init(&tmem_empty[a], 4);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) tmem_alloc(tmem_base_slot, 2 * BN);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (one elected lane)
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_a);
+      tma_prefetch_desc(&tm_b);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        int mt, nt;
+        tile_coords(t, m_tiles, n_tiles, mt, nt);
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (*abort_flag || !mbar_wait(&empty[s], ph ^ 1)) { ok = false; break; }
+          const int seg = kb / kb_per_seg;
+          const int kk = (kb - seg * kb_per_seg) * kBK;
+          uint8_t* sa = smem + s * S::kStageBytes;
+          mbar_expect_tx(&full[s], S::kStageBytes);
+          tma_load_2d(sa, &tm_a, &full[s], seg * p.a_seg_stride + kk, mt * kBM);
+          tma_load_2d(sa + S::kABytes, &tm_b, &full[s], seg * p.b_seg_stride + kk, nt * BN);
+        }
+      }
+      if (!ok) {
+        *abort_flag = 1;
+        report_error(p.status, MSL_ERR_DEVICE_TIMEOUT);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (one elected lane)
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(1, 1, kBM, BN);
+      uint32_t it = 0, tile_i = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_i) {
+        const uint32_t acc = tile_i & 1;
+        const uint32_t acc_ph = (tile_i >> 1) & 1;
+        if (*abort_flag || !mbar_wait(&tmem_empty[acc], acc_ph ^ 1)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (*abort_flag || !mbar_wait(&full[s], ph)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + s * S::kStageBytes);
+          const uint32_t sb = sa + S::kABytes;
+#pragma unroll
+          for (int k16 = 0; k16 < kBK / 16; ++k16) {
+            const uint64_t da = make_sdesc(sa + k16 * 32, 16, 1024, 2);
+            const uint64_t db = make_sdesc(sb + k16 * 32, 16, 1024, 2);
+            tc_mma_f16(d_tmem, da, db, idesc, (kb | k16) != 0);
+          }
+          tc_commit(&empty[s]);          // frees the stage once these MMAs have read it
+        }
+        if (ok) tc_commit(&tmem_full[acc]);
+      }
+      if (!ok) {
+        *abort_flag = 1;
+        report_error(p.status, MSL_ERR_DEVICE_TIMEOUT);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue warps
+    const int quarter = warp & 3;            // TMEM lanes [32*quarter, 32*quarter + 32)
+    uint32_t tile_i = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_i) {
+      int mt, nt;
+      tile_coords(t, m_tiles, n_tiles, mt, nt);
+      const uint32_t acc = tile_i & 1;
+      const uint32_t acc_ph = (tile_i >> 1) & 1;
+      if (*abort_flag || !mbar_wait(&tmem_full[acc], acc_ph)) { ok = false; break; }
+      tc_fence_after();
+      const int row = mt * kBM + quarter * 32 + lane;
+      const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
+      if constexpr (OUT == MSL_OUT_SWIGLU_BF16) {
+        // Columns [0, BN/2) of the tile are gate rows, [BN/2, BN) the matching up rows.
+#pragma unroll 1
+        for (int c = 0; c < BN / 2; c += 32) {
+          uint32_t g[32], u[32];
+          tmem_ld32(taddr + c, g);
+          tmem_ld32(taddr + BN / 2 + c, u);
+          tmem_ld_wait();
+          store_chunk<BN, OUT>(p, row, nt * (BN / 2) + c, g, u);
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t v[32];
+          tmem_ld32(taddr + c, v);
+          tmem_ld_wait();
+          store_chunk<BN, OUT>(p, row, nt * BN + c, v, v);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+    }
+    if (!ok && lane == 0) {
+      *abort_flag = 1;
+      report_error(p.status, MSL_ERR_DEVICE_TIMEOUT);
+    }
+  }
+
+  // ------------------------------------------------------------ teardown (all roles reach here)
+  // Give loads already issued a bounded time to land before the CTA's shared memory goes away.
+  if (warp == 0 && lane == 0 && *abort_flag) drain_pause();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc(tmem_base, 2 * BN);
+  }
+}
+
+template <int BN, int STAGES, int OUT>
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& args, cudaStream_t stream) {
+  using S = GemmSmem<BN, STAGES>;
+  const int smem = S::kTotal + 1024;
+  static bool configured = false;   // per template instance; attribute is per function, set once per process
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN, STAGES, OUT>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return MSL_ERR_CUDA;
+    configured = true;
+  }
+  const int m_tiles = (args.m + kBM - 1) / kBM;
+  const int n_tiles = (args.n + BN - 1) / BN;
+  const int grid = std::min(m_tiles * n_tiles, sm_count());
+  gemm_bf16_kernel<BN, STAGES, OUT><<<grid, 192, smem, stream>>>(ta, tb, args);
+  return cudaGetLastError() == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
+}
+
+}  // namespace msl
+
+using namespace msl;
+
+extern "C" int msl_gemm_bf16(const void* a, int64_t lda, const void* b, int64_t ldb, void* c, int64_t ldc, int m,
+                             int n, int k, int segs, int a_seg_stride, int b_seg_stride, int out_mode, float alpha,
+                             int* status, void* stream) {
+  if (!a || !b || !c || m < 0 || n <= 0 || k <= 0 || segs < 1) return MSL_ERR_ARG;
+  if ((lda & 7) || (ldb & 7) || (k & 7) || (a_seg_stride & 7) || (b_seg_stride & 7)) return MSL_ERR_ALIGN;
+  if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15)) return MSL_ERR_ALIGN;
+  if (out_mode == MSL_OUT_SWIGLU_BF16 && (n % 256)) return MSL_ERR_ARG;
+  if (segs > 1 && (k % kBK)) return MSL_ERR_ARG;   // a segment's K tail would read the next segment
+  if (m == 0) return MSL_OK;
+  const int a_cols = a_seg_stride * (segs - 1) + k;
+  const int b_cols = b_seg_stride * (segs - 1) + k;
+  CUtensorMap ta, tb;
+  int rc = make_tmap_2d(&ta, a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a_cols, m, lda * 2, kBK, kBM,
+                        CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc) return rc;
+  GemmArgs args{c, ldc, m, n, k, segs, a_seg_stride, b_seg_stride, alpha, status};
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // Narrow outputs use a 128-column tile so more CTAs share the work.
+  const bool narrow = (out_mode != MSL_OUT_SWIGLU_BF16) && (n <= 128 || (n % 256 != 0 && n % 128 == 0));
+  const int bn = narrow ? 128 : 256;
+  rc = make_tmap_2d(&tb, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, b_cols, n, ldb * 2, kBK, bn,
+                    CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc) return rc;
+  switch (out_mode) {
+    case MSL_OUT_BF16:
+      return narrow ? launch_gemm<128, 6, MSL_OUT_BF16>(ta, tb, args, st)
+                    : launch_gemm<256, 4, MSL_OUT_BF16>(ta, tb, args, st);
+    case MSL_OUT_F32:
+      return narrow ? launch_gemm<128, 6, MSL_OUT_F32>(ta, tb, args, st)
+                    : launch_gemm<256, 4, MSL_OUT_F32>(ta, tb, args, st);
+    case MSL_OUT_SWIGLU_BF16:
+      return launch_gemm<256, 4, MSL_OUT_SWIGLU_BF16>(ta, tb, args, st);
+    default:
+      return MSL_ERR_ARG;
+  }
+}

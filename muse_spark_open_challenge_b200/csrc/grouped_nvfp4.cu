@@ -1,0 +1,430 @@
+// Grouped expert GEMM with NVFP4 weights and BF16 activations on tcgen05 (W4A16):
+//   out[r, :] = (x[r, :] * dq(W_e)^T) * gs_e      for the rows r of expert e's slab range,
+// dq(W) = e2m1 code * e4m3 block scale (16-element blocks); the per-expert fp32 global scale is
+// applied to the fp32 accumulator.  Optional fused SiLU(gate) * up epilogue.
+//
+// Replaces the third-party grouped GEMM launches and the separate SiLU kernel of the reference's
+// layer (muse_prefill_layer/submission.py:956-1002, launches :1128-1130; _silu_mul_kernel
+// :903-913) and restates the arithmetic of reference.py:433-442 / nvfp4.py:90-97.
+//
+// One persistent CTA per SM, 448 threads:
+//   warp 0      TMA producer: activation tile 128 rows x 64 k (bf16, 128-byte swizzle)
+//   warp 1      TMEM allocation + tcgen05.mma issue (M=128 tokens, N=256 weight rows, K=16)
+//   warps 2-5   epilogue (TMEM -> registers -> global)
+//   warps 6-13  weight producers: each thread dequantises one weight row of the stage (64 codes +
+//               4 block scales -> 64 bf16) straight into the swizzled B tile in shared memory
+// The weights were re-tiled once at load time (msl_nvfp4_repack) so a stage's codes are one
+// contiguous 8 KiB block and its scales one contiguous 1 KiB block.
+//
+// Dequantisation without a table for the codes: a 4-bit code s|e1 e0|m placed at bf16 bits
+// 15|8 7|6 is the bf16 number value * 2^-126 (also for the subnormal codes 0 and 0.5); the block
+// scale is looked up as bf16(scale * 2^118); one bf16x2 multiply gives value * scale * 2^-8
+// exactly (at most 6 significant bits), and the 2^8 is folded into the epilogue scale.
+#include "msl_common.cuh"
+#include "msl_host.h"
+
+namespace msl {
+
+constexpr int kGM = 128;       // token rows per tile
+constexpr int kGN = 256;       // weight rows per tile
+constexpr int kGK = 64;        // k per stage
+constexpr int kGStages = 4;
+constexpr int kMaxLocal = 256; // experts per call
+
+struct GroupedSmem {
+  static constexpr int kABytes = kGM * kGK * 2;
+  static constexpr int kBBytes = kGN * kGK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kLutOffset = kGStages * kStageBytes;          // 256 x u32
+  static constexpr int kPrefixOffset = kLutOffset + 1024;            // (kMaxLocal + 1) x int
+  static constexpr int kBarOffset = kPrefixOffset + (kMaxLocal + 1) * 4 + 4;
+  static constexpr int kTotal = kBarOffset + (2 * kGStages + 4) * 8 + 16;
+};
+static_assert(GroupedSmem::kBarOffset % 8 == 0, "barriers must be 8-byte aligned");
+
+struct GroupedArgs {
+  const uint8_t* wq;       // [experts][n_tiles][k_blocks][256 rows][32 bytes]
+  const uint8_t* sf;       // [experts][n_tiles][k_blocks][256 rows][4 bytes]
+  const float* gs;         // [experts]
+  const int* offsets;      // [experts + 1] slab row ranges
+  void* out;
+  int64_t ld_out;
+  int experts, n, k;       // n = padded weight rows (multiple of 256), k multiple of 64
+  int n_out;               // valid output columns (after the SwiGLU halving when fused)
+  int swiglu;
+  int* status;
+};
+
+struct TileInfo {
+  int expert, row0, rows, nt;   // first slab row, valid rows in the tile, n tile
+};
+
+__device__ __forceinline__ TileInfo decode_tile(int g, const int* mt_prefix, const int* offsets, int experts,
+                                                int n_tiles) {
+  // mt_prefix[e] = number of 128-row tiles of the experts before e.
+  int lo = 0, hi = experts - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (mt_prefix[mid] * n_tiles <= g) lo = mid; else hi = mid - 1;
+  }
+  const int e = lo;
+  const int mte = mt_prefix[e + 1] - mt_prefix[e];
+  const int r = g - mt_prefix[e] * n_tiles;
+  const int nt = r / mte, mt = r - nt * mte;
+  const int start = offsets[e], cnt = offsets[e + 1] - start;
+  TileInfo ti;
+  ti.expert = e;
+  ti.row0 = start + mt * kGM;
+  ti.rows = min(kGM, cnt - mt * kGM);
+  ti.nt = nt;
+  return ti;
+}
+
+// Eight codes of one 32-bit word -> four bf16x2 words (elements 2j, 2j+1 in word j), times the
+// block scale.  Word layout made by the repack: nibble j holds element 2j, nibble j+4 element 2j+1.
+__device__ __forceinline__ uint4 dequant8(uint32_t w, uint32_t scale2) {
+  uint32_t o[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const uint32_t t = w >> (4 * j);
+    const uint32_t bits = ((t & 0x00070007u) << 6) | ((t & 0x00080008u) << 12);
+    __nv_bfloat162 v = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&bits),
+                               *reinterpret_cast<const __nv_bfloat162*>(&scale2));
+    o[j] = *reinterpret_cast<uint32_t*>(&v);
+  }
+  return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+__global__ void __launch_bounds__(448, 1)
+grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
+  using S = GroupedSmem;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint32_t* lut = reinterpret_cast<uint32_t*>(smem + S::kLutOffset);
+  int* mt_prefix = reinterpret_cast<int*>(smem + S::kPrefixOffset);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + S::kBarOffset);
+  uint64_t* empty = full + kGStages;
+  uint64_t* tmem_full = empty + kGStages;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile uint32_t* abort_flag = tmem_base_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int n_tiles = p.n / kGN;
+  const int k_blocks = p.k / kGK;
+
+  // Scale table: e4m3 byte -> bf16(scale * 2^118) in both halves.  (0x7f / 0xff are NaN codes.)
+  for (int i = threadIdx.x; i < 256; i += blockDim.x) {
+    const int e = (i >> 3) & 15, m = i & 7;
+    float s = e ? ldexpf(1.0f + m * 0.125f, e - 7) : ldexpf(m * 0.125f, -6);
+    if (i & 0x80) s = -s;
+    if ((i & 0x7f) == 0x7f) s = __int_as_float(0x7fc00000);
+    const uint32_t b = __float_as_uint(s * 3.32306998946228968e35f) >> 16;   // * 2^118: exact, top 16 bits
+    lut[i] = b | (b << 16);
+  }
+  if (warp == 0) {
+    // prefix of 128-row tile counts per expert, one warp
+    int carry = 0;
+    for (int b0 = 0; b0 < p.experts; b0 += 32) {
+      const int i = b0 + lane;
+      const int c = i < p.experts ? (p.offsets[i + 1] - p.offsets[i] + kGM - 1) / kGM : 0;
+      int inc = c;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int nb = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += nb;
+      }
+      if (i < p.experts) mt_prefix[i] = carry + inc - c;
+      carry += __shfl_sync(0xffffffffu, inc, 31);
+    }
+    if (lane == 0) mt_prefix[p.experts] = carry;
+  }
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kGStages; ++s) {
+      mbar_init(&full[s], 1 + 8);   // producer's expect_tx arrival + 8 weight-producer warps
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full[a], 1);
+      mbar_init(&tmem_empty[a], 4);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) tmem_alloc(tmem_base_slot, 2 * kGN);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+  const int total_tiles = mt_prefix[p.experts] * n_tiles;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_x);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int g = blockIdx.x; g < total_tiles && ok; g += gridDim.x) {
+        const TileInfo ti = decode_tile(g, mt_prefix, p.offsets, p.experts, n_tiles);
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % kGStages;
+          const uint32_t ph = (it / kGStages) & 1;
+          if (*abort_flag || !mbar_wait(&empty[s], ph ^ 1)) { ok = false; break; }
+          mbar_expect_tx(&full[s], S::kABytes);
+          tma_load_2d(smem + s * S::kStageBytes, &tm_x, &full[s], kb * kGK, ti.row0);
+        }
+      }
+      if (!ok) { *abort_flag = 1; report_error(p.status, MSL_ERR_DEVICE_TIMEOUT); }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(1, 1, kGM, kGN);
+      uint32_t it = 0, tile_i = 0;
+      bool ok = true;
+      for (int g = blockIdx.x; g < total_tiles && ok; g += gridDim.x, ++tile_i) {
+        const uint32_t acc = tile_i & 1, acc_ph = (tile_i >> 1) & 1;
+        if (*abort_flag || !mbar_wait(&tmem_empty[acc], acc_ph ^ 1)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * kGN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % kGStages;
+          const uint32_t ph = (it / kGStages) & 1;
+          if (*abort_flag || !mbar_wait(&full[s], ph)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + s * S::kStageBytes);
+          const uint32_t sb = sa + S::kABytes;
+#pragma unroll
+          for (int k16 = 0; k16 < kGK / 16; ++k16) {
+            tc_mma_f16(d_tmem, make_sdesc(sa + k16 * 32, 16, 1024, 2), make_sdesc(sb + k16 * 32, 16, 1024, 2),
+                       idesc, (kb | k16) != 0);
+          }
+          tc_commit(&empty[s]);
+        }
+        if (ok) tc_commit(&tmem_full[acc]);
+      }
+      if (!ok) { *abort_flag = 1; report_error(p.status, MSL_ERR_DEVICE_TIMEOUT); }
+    }
+  } else if (warp < 6) {
+    // ------------------------------------------------------------ epilogue
+    const int quarter = warp & 3;
+    uint32_t tile_i = 0;
+    bool ok = true;
+    for (int g = blockIdx.x; g < total_tiles && ok; g += gridDim.x, ++tile_i) {
+      const TileInfo ti = decode_tile(g, mt_prefix, p.offsets, p.experts, n_tiles);
+      const uint32_t acc = tile_i & 1, acc_ph = (tile_i >> 1) & 1;
+      if (*abort_flag || !mbar_wait(&tmem_full[acc], acc_ph)) { ok = false; break; }
+      tc_fence_after();
+      const int r = quarter * 32 + lane;
+      const bool valid = r < ti.rows;
+      const float alpha = p.gs[ti.expert] * 256.0f;
+      const uint32_t taddr = tmem_base + acc * kGN + (static_cast<uint32_t>(quarter * 32) << 16);
+      __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<int64_t>(ti.row0 + r) * p.ld_out;
+      if (p.swiglu) {
+#pragma unroll 1
+        for (int c = 0; c < kGN / 2; c += 32) {
+          uint32_t gt[32], up[32];
+          tmem_ld32(taddr + c, gt);
+          tmem_ld32(taddr + kGN / 2 + c, up);
+          tmem_ld_wait();
+          const int col0 = ti.nt * (kGN / 2) + c;
+          if (valid && col0 < p.n_out) {
+            uint32_t packed[16];
+#pragma unroll
+            for (int j = 0; j < 32; j += 2) {
+              const float g0 = __uint_as_float(gt[j]) * alpha, g1 = __uint_as_float(gt[j + 1]) * alpha;
+              const float u0 = __uint_as_float(up[j]) * alpha, u1 = __uint_as_float(up[j + 1]) * alpha;
+              packed[j / 2] = pack_bf16x2(g0 / (1.0f + __expf(-g0)) * u0, g1 / (1.0f + __expf(-g1)) * u1);
+            }
+            if (col0 + 32 <= p.n_out) {
+#pragma unroll
+              for (int j = 0; j < 16; j += 4)
+                *reinterpret_cast<uint4*>(orow + col0 + 2 * j) =
+                    make_uint4(packed[j], packed[j + 1], packed[j + 2], packed[j + 3]);
+            } else {
+              for (int j = 0; j < 32 && col0 + j < p.n_out; ++j)
+                orow[col0 + j] = __ushort_as_bfloat16(static_cast<unsigned short>(
+                    (j & 1) ? (packed[j / 2] >> 16) : (packed[j / 2] & 0xffffu)));
+            }
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < kGN; c += 32) {
+          uint32_t v[32];
+          tmem_ld32(taddr + c, v);
+          tmem_ld_wait();
+          const int col0 = ti.nt * kGN + c;
+          if (valid && col0 < p.n_out) {
+            uint32_t packed[16];
+#pragma unroll
+            for (int j = 0; j < 32; j += 2)
+              packed[j / 2] = pack_bf16x2(__uint_as_float(v[j]) * alpha, __uint_as_float(v[j + 1]) * alpha);
+            if (col0 + 32 <= p.n_out) {
+#pragma unroll
+              for (int j = 0; j < 16; j += 4)
+                *reinterpret_cast<uint4*>(orow + col0 + 2 * j) =
+                    make_uint4(packed[j], packed[j + 1], packed[j + 2], packed[j + 3]);
+            } else {
+              for (int j = 0; j < 32 && col0 + j < p.n_out; ++j)
+                orow[col0 + j] = __ushort_as_bfloat16(static_cast<unsigned short>(
+                    (j & 1) ? (packed[j / 2] >> 16) : (packed[j / 2] & 0xffffu)));
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+    }
+    if (!ok && lane == 0) { *abort_flag = 1; report_error(p.status, MSL_ERR_DEVICE_TIMEOUT); }
+  } else {
+    // ------------------------------------------------------------ weight producers (warps 6-13)
+    const int row = threadIdx.x - 6 * 32;      // 0..255: weight row of the tile
+    uint32_t it = 0;
+    bool ok = true;
+    for (int g = blockIdx.x; g < total_tiles && ok; g += gridDim.x) {
+      const TileInfo ti = decode_tile(g, mt_prefix, p.offsets, p.experts, n_tiles);
+      const int64_t tile_id = (static_cast<int64_t>(ti.expert) * n_tiles + ti.nt) * k_blocks;
+      const uint8_t* wq = p.wq + tile_id * (kGN * 32) + row * 32;
+      const uint8_t* sf = p.sf + tile_id * (kGN * 4) + row * 4;
+      for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        const int s = it % kGStages;
+        const uint32_t ph = (it / kGStages) & 1;
+        // Loads are issued before the wait so their latency overlaps it.
+        const uint4 c0 = __ldg(reinterpret_cast<const uint4*>(wq + static_cast<int64_t>(kb) * (kGN * 32)));
+        const uint4 c1 = __ldg(reinterpret_cast<const uint4*>(wq + static_cast<int64_t>(kb) * (kGN * 32) + 16));
+        const uint32_t sc = __ldg(reinterpret_cast<const uint32_t*>(sf + static_cast<int64_t>(kb) * (kGN * 4)));
+        if (*abort_flag || !mbar_wait(&empty[s], ph ^ 1)) { ok = false; break; }
+        uint8_t* sb = smem + s * S::kStageBytes + S::kABytes;
+        const uint32_t w[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint32_t scale2 = lut[(sc >> (8 * (c >> 1))) & 0xffu];
+          *reinterpret_cast<uint4*>(sb + swz128(row, c)) = dequant8(w[c], scale2);
+        }
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&full[s]);
+      }
+    }
+    if (!ok && lane == 0) { *abort_flag = 1; report_error(p.status, MSL_ERR_DEVICE_TIMEOUT); }
+  }
+
+  if (warp == 0 && lane == 0 && *abort_flag) drain_pause();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc(tmem_base, 2 * kGN);
+  }
+}
+
+// ---------------------------------------------------------------------------- load-time re-tiling
+// src: codes [experts, rows, k/2] (element 2i in the low nibble of byte i), scales [experts, rows,
+// k/16].  dst tiles of 256 rows x 64 k; with `interleave` (gate/up bank, rows = 2 * inter) tile j
+// holds gate rows [128 j, 128 j + 128) then up rows inter + [128 j, 128 j + 128).  Rows beyond the
+// source are zero codes / zero scales.  Within each 32-bit word the eight codes are reordered so
+// nibble j holds element 2j and nibble j+4 element 2j+1.  Lossless: a permutation of the input.
+__global__ void nvfp4_repack_kernel(const uint8_t* __restrict__ src_q, const uint8_t* __restrict__ src_sf,
+                                    uint8_t* __restrict__ dst_q, uint8_t* __restrict__ dst_sf, int experts, int rows,
+                                    int k, int n_pad, int interleave) {
+  const int k_blocks = k / kGK, n_tiles = n_pad / kGN;
+  const int64_t total = static_cast<int64_t>(experts) * n_tiles * k_blocks * kGN;
+  const int inter = rows / 2;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int r = static_cast<int>(i % kGN);
+    int64_t q = i / kGN;
+    const int kb = static_cast<int>(q % k_blocks);
+    q /= k_blocks;
+    const int nt = static_cast<int>(q % n_tiles);
+    const int e = static_cast<int>(q / n_tiles);
+    int src_row;
+    if (interleave) {
+      const int gi = nt * 128 + (r & 127);
+      src_row = gi < inter ? (r < 128 ? gi : inter + gi) : -1;
+    } else {
+      src_row = nt * kGN + r;
+      if (src_row >= rows) src_row = -1;
+    }
+    uint32_t words[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    uint32_t sc = 0;
+    if (src_row >= 0) {
+      const uint8_t* sq = src_q + (static_cast<int64_t>(e) * rows + src_row) * (k / 2) + kb * 32;
+      for (int w = 0; w < 8; ++w) {
+        uint32_t in = 0;
+        for (int b = 0; b < 4; ++b) in |= static_cast<uint32_t>(sq[w * 4 + b]) << (8 * b);
+        uint32_t out = 0;
+        for (int el = 0; el < 8; ++el) {
+          const uint32_t code = (in >> (4 * el)) & 0xfu;
+          const int nib = (el & 1) ? 4 + el / 2 : el / 2;
+          out |= code << (4 * nib);
+        }
+        words[w] = out;
+      }
+      const uint8_t* ss = src_sf + (static_cast<int64_t>(e) * rows + src_row) * (k / 16) + kb * 4;
+      sc = ss[0] | (ss[1] << 8) | (ss[2] << 16) | (static_cast<uint32_t>(ss[3]) << 24);
+    }
+    uint32_t* dq = reinterpret_cast<uint32_t*>(dst_q + i * 32);
+    for (int w = 0; w < 8; ++w) dq[w] = words[w];
+    *reinterpret_cast<uint32_t*>(dst_sf + i * 4) = sc;
+  }
+}
+
+}  // namespace msl
+
+using namespace msl;
+
+extern "C" int64_t msl_nvfp4_padded_rows(int rows, int interleave) {
+  if (interleave) {
+    const int inter = rows / 2;
+    return 2 * static_cast<int64_t>((inter + 127) / 128) * 128;
+  }
+  return static_cast<int64_t>((rows + kGN - 1) / kGN) * kGN;
+}
+
+extern "C" int msl_nvfp4_repack(const void* src_codes, const void* src_scales, void* dst_codes, void* dst_scales,
+                                int experts, int rows, int k, int interleave, void* stream) {
+  if (!src_codes || !src_scales || !dst_codes || !dst_scales || experts <= 0 || rows <= 0 || k <= 0)
+    return MSL_ERR_ARG;
+  if (k % kGK) return MSL_ERR_UNSUPPORTED;
+  if (interleave && (rows & 1)) return MSL_ERR_ARG;
+  const int n_pad = static_cast<int>(msl_nvfp4_padded_rows(rows, interleave));
+  const int64_t total = static_cast<int64_t>(experts) * n_pad * (k / kGK);
+  const int blocks = static_cast<int>(std::min<int64_t>((total + 255) / 256, 148 * 16));
+  nvfp4_repack_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint8_t*>(src_codes), static_cast<const uint8_t*>(src_scales),
+      static_cast<uint8_t*>(dst_codes), static_cast<uint8_t*>(dst_scales), experts, rows, k, n_pad, interleave);
+  return cudaGetLastError() == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
+}
+
+extern "C" int msl_grouped_gemm_nvfp4(const void* x, int64_t slab_rows, const void* codes, const void* scales,
+                                      const float* global_scales, const int* offsets, void* out, int64_t ld_out,
+                                      int experts, int n_padded, int k, int n_out, int swiglu, int* status,
+                                      void* stream) {
+  if (!x || !codes || !scales || !global_scales || !offsets || !out) return MSL_ERR_ARG;
+  if (experts <= 0 || experts > kMaxLocal || n_padded <= 0 || k <= 0 || n_out <= 0 || slab_rows < 0)
+    return MSL_ERR_ARG;
+  if ((n_padded % kGN) || (k % kGK)) return MSL_ERR_UNSUPPORTED;
+  if ((reinterpret_cast<uintptr_t>(x) & 15) || (ld_out & 7) || (reinterpret_cast<uintptr_t>(out) & 15))
+    return MSL_ERR_ALIGN;
+  if (slab_rows == 0) return MSL_OK;
+  CUtensorMap tx;
+  int rc = make_tmap_2d(&tx, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, k, slab_rows, static_cast<uint64_t>(k) * 2, kGK,
+                        kGM, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc) return rc;
+  GroupedArgs a{static_cast<const uint8_t*>(codes), static_cast<const uint8_t*>(scales), global_scales, offsets, out,
+                ld_out, experts, n_padded, k, n_out, swiglu, status};
+  const int smem = GroupedSmem::kTotal + 1024;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(grouped_nvfp4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+      return MSL_ERR_CUDA;
+    configured = true;
+  }
+  // Upper bound on tiles without reading the device counts: every expert may add one partial tile.
+  const int64_t max_tiles = ((slab_rows + kGM - 1) / kGM + experts) * (n_padded / kGN);
+  const int grid = static_cast<int>(std::min<int64_t>(max_tiles, sm_count()));
+  grouped_nvfp4_kernel<<<grid, 448, smem, static_cast<cudaStream_t>(stream)>>>(tx, a);
+  return cudaGetLastError() == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
+}

@@ -1,0 +1,113 @@
+"""No-GPU checks of the drop-in boundary: the library builds, loads and exports exactly the entry
+points include/msl.h declares; argument errors are rejected on the host before any launch; the
+pure-host parts of `prepare` (router split, gate/up interleave, synthetic generators) behave."""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+from conftest import ROOT
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from muse_spark_open_challenge_b200 import build, _lib
+    build.build()
+    return _lib.load()
+
+
+def declared_functions():
+    text = open(os.path.join(ROOT, "include", "msl.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(msl_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol(lib):
+    from muse_spark_open_challenge_b200 import _lib
+    names = declared_functions()
+    assert len(names) >= 12
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/msl.h but not exported"
+    assert sorted(_lib.SIGNATURES) == names          # the ctypes table binds exactly the header
+    assert lib.msl_abi_version() == 1
+    assert lib.msl_status_string(0) == b"ok" and b"argument" in lib.msl_status_string(-1)
+
+
+def test_argument_errors_are_rejected_before_any_launch(lib):
+    null = ctypes.c_void_p(0)
+    assert lib.msl_gemm_bf16(null, 8, null, 8, null, 8, 1, 1, 8, 1, 0, 0, 0, 1.0, null, null) == -1
+    fake = ctypes.c_void_p(1 << 20)
+    assert lib.msl_gemm_bf16(fake, 7, fake, 8, fake, 8, 1, 8, 8, 1, 0, 0, 0, 1.0, null, null) == -2   # pitch
+    assert lib.msl_gemm_bf16(fake, 8, fake, 8, fake, 8, 0, 8, 8, 1, 0, 0, 0, 1.0, null, null) == 0    # m = 0
+    assert lib.msl_boundary(fake, 8, null, fake, fake, fake, fake, fake, fake, 8, 0, 8, 1e-8, 1e-5, null) == 0
+    assert lib.msl_boundary(fake, 8, null, fake, fake, fake, fake, fake, fake, 8, 1, 12, 1e-8, 1e-5, null) == -2
+    assert lib.msl_route_topk(fake, 8, 0, fake, 1.0, fake, 1, 4, 8, 4, fake, fake, fake, fake, fake, null) == -1
+    assert lib.msl_nvfp4_padded_rows(3072, 1) == 3072 and lib.msl_nvfp4_padded_rows(512, 1) == 512
+    assert lib.msl_nvfp4_padded_rows(128, 0) == 256 and lib.msl_nvfp4_padded_rows(200, 1) == 256
+
+
+def test_missing_library_fails_loudly(tmp_path):
+    from muse_spark_open_challenge_b200 import _lib
+    with pytest.raises(_lib.MslError):
+        _lib.load(str(tmp_path / "nope.so"))
+
+
+def test_prepare_refuses_cpu_tensors():
+    from muse_spark_open_challenge_b200 import layer, synth
+    from muse_spark_open_challenge_b200._lib import MslError
+    w = synth.make_weights(synth.TINY, seed=0)
+    with pytest.raises(MslError):
+        layer.prepare(w)
+
+
+def test_interleave_gate_up_layout():
+    from muse_spark_open_challenge_b200 import ops
+    inter, k = 384, 8
+    w = torch.arange(2 * inter, dtype=torch.float32)[:, None].expand(2 * inter, k).contiguous()
+    out = ops.interleave_gate_up(w)
+    for tile in range(inter // 128):
+        blk = out[tile * 256:(tile + 1) * 256, 0]
+        assert torch.equal(blk[:128], torch.arange(tile * 128, tile * 128 + 128).float())
+        assert torch.equal(blk[128:], inter + torch.arange(tile * 128, tile * 128 + 128).float())
+
+
+def test_router_hi_lo_split_recovers_fp32_to_2e_minus_17():
+    r = 0.045 * torch.randn((64, 512), generator=torch.Generator().manual_seed(0))
+    hi = r.to(torch.bfloat16)
+    lo = (r - hi.float()).to(torch.bfloat16)
+    err = (hi.float() + lo.float() - r).abs().max() / r.abs().max()
+    assert err < 2 ** -16
+
+
+def test_synthetic_generators_follow_the_reference_schema():
+    from muse_spark_open_challenge_b200 import synth
+    from oracle import layer_ref as L
+    shape = synth.TINY
+    w = synth.make_weights(shape, seed=1)
+    data = synth.make_input(shape, [7, 64, 3], [0, 100, 5], seed=2, page=16, kv_scale=0.5)
+    assert data["stream"].dtype == torch.float32 and data["attn_input"].dtype == torch.bfloat16
+    assert data["k_cache"].dtype == torch.float8_e4m3fn and data["k_cache"].shape[1:] == (16, shape.hkv, shape.head_dim)
+    assert data["cu_seqlens_q"].tolist() == [0, 7, 71, 74] and data["positions"].dtype == torch.int64
+    assert torch.equal(data["cache_loc"], L.new_slots(data))       # the two slot derivations agree
+    assert len(set(data["cache_loc"].tolist())) == 74
+    d = L.dims_of(w, data["config"])
+    assert (d.hidden, d.moe_width, d.inter, d.pooled) == (512, 256, 256, True)
+    # a ragged batch runs through the oracle end to end
+    hidden, stream, ids, k_new, v_new = L.ref_kernel(data, w)
+    assert hidden.shape == (74, 512) and ids.shape == (74, 4) and torch.isfinite(stream).all()
+
+
+def test_zipf_targets_and_router_skew():
+    from muse_spark_open_challenge_b200 import synth
+    t = synth.zipf_targets(128, 16384 * 8, s=1.1, cap=3000, n_empty=2)
+    assert abs(float(t.sum()) - 16384 * 8) < 1 and float(t.max()) <= 3000 and int((t == 0).sum()) == 2
+    shape = synth.TINY
+    w = synth.make_weights(shape, seed=3)
+    h = torch.randn((2048, shape.hidden), generator=torch.Generator().manual_seed(4))
+    targets = synth.zipf_targets(shape.n_experts, 2048 * shape.top_k, cap=2048, n_empty=1)
+    synth.skew_router(w, h, targets, shape.top_k, sample=2048)
+    scores = torch.sigmoid((h @ w["router"].T) * synth.ROUTER_MULTIPLIER) + w["router_bias"]
+    counts = torch.bincount(scores.topk(shape.top_k, dim=-1).indices.flatten(), minlength=shape.n_experts)
+    assert int((counts == 0).sum()) >= 1 and counts.max() > 4 * counts[counts > 0].min()
