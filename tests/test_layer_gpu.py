@@ -47,7 +47,7 @@ def test_layer_on_reference_vectors(name):
     for got, want in ((k_rows, g["ref"]["k_new"]), (v_rows, g["ref"]["v_new"])):
         gb, wb = got.reshape(t, -1).view(torch.uint8), want.reshape(t, -1).view(torch.uint8)
         assert (gb != wb).float().mean() < 5e-2
-        assert L.relative_l2(got.reshape(t, -1).float(), want.reshape(t, -1).float()) < 1e-2
+        assert L.relative_l2(got.reshape(t, -1).float(), want.reshape(t, -1).float()) < 2.5e-2   # reference bound: 8e-2
     # expert ids: equal to the reference's wherever its k-th and (k+1)-th scores are not a near tie
     biased = g["ref"]["biased"]
     k = ids.shape[1]
