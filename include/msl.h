@@ -96,6 +96,22 @@ int msl_dispatch(const void* x, int64_t ldx, const float* norm_w, const int* loc
                  const int* counts, int tokens, int n_local, int top_k, int width, void* slab, int64_t slab_rows,
                  int* rowmap, int* offsets_out, int* status, void* stream);
 
+/* Routing and dispatch in one call that needs no scratch memory from the caller: the same
+ * results as msl_route_topk followed by msl_dispatch (ids, weights, rowmap, offsets_out, slab),
+ * with the per-expert counters and per-route expert/slot arrays kept in a fixed array inside the
+ * library.  No counterpart in the reference.  It exists for hosts that cannot allocate when they
+ * call in: a server whose memory pool already owns all of HBM, or a request path that cannot take
+ * the device-wide synchronisation cudaMalloc implies.  It calls no allocator of any kind.
+ * Limits: n_local <= 1024 and tokens * top_k <= 262144, otherwise MSL_ERR_CAPACITY; the array
+ * (about 2 MiB) stays resident on every GPU that loads the library.  The first call on a device
+ * looks up the array's device address (cudaGetSymbolAddress); make that first call outside any
+ * stream capture.  All calls share the one array, so two calls whose kernels overlap on the GPU
+ * (different streams, or different host threads on one device) race: serialise them. */
+int msl_route_dispatch_static(const float* logits, int64_t ld, int hilo, const float* bias, float multiplier,
+                              const int* local_start, const void* x, int64_t ldx, const float* norm_w, int tokens,
+                              int n_experts, int top_k, int n_local, int width, int* ids, float* weights, void* slab,
+                              int64_t slab_rows, int* rowmap, int* offsets_out, int* status, void* stream);
+
 /* Weighted combine: out[t] = sum_j weights[t, j] * rms(y[rowmap[t, j]] * post_w, eps 1e-8)
  * (+ addend[t] when not NULL); rowmap < 0 contributes nothing.  y: bf16 [slab rows, width].
  * Replaces _combine_kernel (submission.py:917-928, launch :1132). */

@@ -25,6 +25,8 @@ SIGNATURES = {
     "msl_boundary": (_i, [_p, _i64, _p, _p, _p, _p, _p, _p, _p, _i64, _i, _i, _f, _f, _p]),
     "msl_route_topk": (_i, [_p, _i64, _i, _p, _f, _p, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p]),
     "msl_dispatch": (_i, [_p, _i64, _p, _p, _p, _p, _i, _i, _i, _i, _p, _i64, _p, _p, _p, _p]),
+    "msl_route_dispatch_static": (_i, [_p, _i64, _i, _p, _f, _p, _p, _i64, _p, _i, _i, _i, _i, _i, _p, _p, _p, _i64,
+                                       _p, _p, _p, _p]),
     "msl_combine": (_i, [_p, _p, _p, _p, _p, _i64, _p, _i64, _i, _i, _i, _p]),
     "msl_nvfp4_padded_rows": (_i64, [_i, _i]),
     "msl_nvfp4_repack": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _p]),

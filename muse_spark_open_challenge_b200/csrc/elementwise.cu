@@ -2,6 +2,8 @@
 // the two residual boundaries, the router's top-k with slot assignment, token dispatch and the
 // weighted combine.  All use 128-bit global accesses and keep a row in registers so each tensor
 // crosses HBM once.
+#include <mutex>
+
 #include "msl_common.cuh"
 #include "msl_host.h"
 
@@ -539,4 +541,60 @@ extern "C" int msl_combine(const void* y, const int* rowmap, const float* weight
     combine_kernel<8, 1><<<tokens, threads, 0, st>>>(yy, rowmap, weights, post_w, ad, ld_addend, oo, ld_out, top_k,
                                                      width);
   return cudaGetLastError() == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
+}
+
+
+// ============================================================================ routing + dispatch without caller scratch
+// For hosts that must not allocate device memory when they call in: an inference server that
+// hands all of HBM to its own pool at start-up (a later cudaMalloc fails or fragments the pool), or
+// a request path where the implicit device-wide synchronisation of cudaMalloc / cudaFree is not
+// acceptable.  The per-expert counters and the per-route expert/slot arrays that msl_route_topk
+// hands to msl_dispatch live in this file-scope array instead of caller memory.  Every GPU that
+// loads the library holds the array (about 2 MiB) until the process exits.
+constexpr int kStaticMaxLocal = 1024;            // experts per call
+constexpr int kStaticMaxRoutes = 1 << 18;        // tokens * top_k per call
+static __device__ __align__(256) int g_route_scratch[kStaticMaxLocal + 2 * kStaticMaxRoutes];
+
+__global__ void zero_ints_kernel(int* p, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) p[i] = 0;
+}
+
+// The array's name is only a host-side handle; kernels need the device address, looked up once per
+// device (with that device current) by the first call made on it.
+static int* route_scratch_ptr() {
+  static int* ptrs[64] = {nullptr};
+  static std::mutex mu;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (ptrs[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_route_scratch) != cudaSuccess || p == nullptr) return nullptr;
+    ptrs[dev] = static_cast<int*>(p);
+  }
+  return ptrs[dev];
+}
+
+extern "C" int msl_route_dispatch_static(const float* logits, int64_t ld, int hilo, const float* bias,
+                                         float multiplier, const int* local_start, const void* x, int64_t ldx,
+                                         const float* norm_w, int tokens, int n_experts, int top_k, int n_local,
+                                         int width, int* ids, float* weights, void* slab, int64_t slab_rows,
+                                         int* rowmap, int* offsets_out, int* status, void* stream) {
+  if (tokens < 0 || top_k <= 0) return MSL_ERR_ARG;
+  if (n_local > kStaticMaxLocal || static_cast<int64_t>(tokens) * top_k > kStaticMaxRoutes) return MSL_ERR_CAPACITY;
+  int* scratch = route_scratch_ptr();
+  if (scratch == nullptr) return MSL_ERR_CUDA;
+  int* counts = scratch;
+  int* local_ids = scratch + kStaticMaxLocal;
+  int* slots = local_ids + kStaticMaxRoutes;
+  if (tokens == 0) return MSL_OK;
+  // The counters keep the previous call's totals: clear them on the stream before counting again.
+  zero_ints_kernel<<<(n_local + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(counts, n_local);
+  if (cudaGetLastError() != cudaSuccess) return MSL_ERR_CUDA;
+  int rc = msl_route_topk(logits, ld, hilo, bias, multiplier, local_start, tokens, n_experts, top_k, n_local, ids,
+                          weights, local_ids, slots, counts, stream);
+  if (rc != MSL_OK) return rc;
+  return msl_dispatch(x, ldx, norm_w, local_ids, slots, counts, tokens, n_local, top_k, width, slab, slab_rows, rowmap,
+                      offsets_out, status, stream);
 }

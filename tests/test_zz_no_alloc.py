@@ -1,0 +1,72 @@
+"""The allocation-free routing + dispatch entry point (msl_route_dispatch_static) against the
+two-call path it mirrors (msl_route_topk then msl_dispatch), through the C ABI, twice in a row.
+
+It serves hosts that cannot call cudaMalloc when they invoke the library (a server whose own pool
+already holds all device memory, or a latency-critical path that cannot afford cudaMalloc's
+device-wide synchronisation), so the per-expert counters and per-route slots live in a fixed array
+inside the library.  That array keeps the previous call's contents: the second call here, on
+different inputs, proves the counters are cleared.  Slots come from atomics, so which slab row a
+route gets may differ between the two paths; everything order-independent must be identical."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _both_paths(seed, t, e, k, n_local, width, start):
+    from muse_spark_open_challenge_b200 import _lib, ops
+    lib = _lib.lib()
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    logits = 2.0 * torch.randn((t, e), generator=g, device="cuda")
+    bias = 0.1 * torch.randn((e,), generator=g, device="cuda")
+    x = torch.randn((t, width), generator=g, device="cuda").to(torch.bfloat16)
+    norm_w = 1.0 + 0.1 * torch.randn((width,), generator=g, device="cuda")
+    ls = torch.tensor([start], dtype=torch.int32, device="cuda")
+    # existing entry points, caller-provided scratch
+    counts = torch.zeros(n_local, dtype=torch.int32, device="cuda")
+    ids0, w0, local_ids, slots = ops.route_topk(logits, bias, 0.5, ls, e, k, n_local, counts)
+    slab0 = torch.zeros((t * k, width), dtype=torch.bfloat16, device="cuda")
+    off0 = torch.zeros(n_local + 1, dtype=torch.int32, device="cuda")
+    rowmap0 = ops.dispatch(x, norm_w, local_ids, slots, counts, slab0, off0)
+    # the allocation-free entry point: outputs only
+    ids1 = torch.empty_like(ids0)
+    w1 = torch.empty_like(w0)
+    slab1 = torch.zeros_like(slab0)
+    off1 = torch.zeros_like(off0)
+    rowmap1 = torch.empty_like(rowmap0)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    rc = lib.msl_route_dispatch_static(logits.data_ptr(), logits.stride(0), 0, bias.data_ptr(), 0.5, ls.data_ptr(),
+                                       x.data_ptr(), x.stride(0), norm_w.data_ptr(), t, e, k, n_local, width,
+                                       ids1.data_ptr(), w1.data_ptr(), slab1.data_ptr(), slab1.shape[0],
+                                       rowmap1.data_ptr(), off1.data_ptr(), status.data_ptr(),
+                                       torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert torch.equal(ids0, ids1) and torch.equal(w0, w1)            # bit-exact ids and weights
+    assert torch.equal(off0, off1)                                    # same per-expert row ranges
+    live = rowmap0 >= 0
+    assert torch.equal(live, rowmap1 >= 0)
+    # each route's slab row holds the same (normalised) token row on both paths
+    assert torch.equal(slab0[rowmap0[live].long()].view(torch.int16), slab1[rowmap1[live].long()].view(torch.int16))
+    # both place every route inside its expert's range, one row per route
+    for rm in (rowmap0, rowmap1):
+        rows = rm[live].long()
+        assert len(torch.unique(rows)) == rows.numel() == int(off0[-1])
+        assert torch.equal(torch.bucketize(rows, off0[1:].long(), right=True).int(), local_ids[live])
+
+
+def test_static_route_dispatch_matches_two_call_path_twice():
+    _both_paths(seed=1, t=700, e=64, k=8, n_local=16, width=512, start=16)
+    _both_paths(seed=2, t=333, e=64, k=8, n_local=16, width=512, start=48)   # counters from call 1 must be gone
+
+
+def test_static_route_dispatch_rejects_oversize():
+    from muse_spark_open_challenge_b200 import _lib
+    lib = _lib.lib()
+    one = torch.zeros(8, device="cuda")
+    p = one.data_ptr()
+    assert lib.msl_route_dispatch_static(p, 8, 0, p, 1.0, p, p, 8, None, 40000, 16, 8, 16, 8, p, p, p, 8, p, p, None,
+                                         None) == -6          # 320000 routes > 262144
+    assert lib.msl_route_dispatch_static(p, 8, 0, p, 1.0, p, p, 8, None, 16, 4096, 8, 2048, 8, p, p, p, 8, p, p, None,
+                                         None) == -6          # 2048 local experts > 1024
