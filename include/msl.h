@@ -133,14 +133,16 @@ int msl_nvfp4_repack(const void* src_codes, const void* src_scales, void* dst_co
                      int rows, int k, int interleave, void* stream);
 
 /* Grouped expert GEMM, NVFP4 weights x BF16 activations, fp32 accumulate:
- * out[r, :] = global_scales[e] * x[r, :] * dq(W_e)^T for slab rows offsets[e] <= r < offsets[e+1];
- * x bf16 [slab_rows, k]; out bf16 [slab_rows, ld_out] with n_out valid columns; with swiglu != 0
+ * out[r, :] = global_scales[e] * x[r, :] * dq(W_e)^T for slab rows offsets[g] <= r < offsets[g+1],
+ * e = g % weight_experts (row groups may outnumber the weight banks: under expert parallelism a
+ * group is (source rank, expert), source-major); x bf16 [slab_rows, k]; out bf16 [slab_rows,
+ * ld_out] with n_out valid columns; experts = number of row groups (<= 256); with swiglu != 0
  * the bank is an interleaved gate/up bank and out = silu(gate) * up (n_out = intermediate size).
  * offsets is device memory [experts + 1]; no host synchronisation.  Replaces the two grouped GEMM
  * launches and _silu_mul_kernel (submission.py:956-1002, 903-913; launches :1128-1130). */
 int msl_grouped_gemm_nvfp4(const void* x, int64_t slab_rows, const void* codes, const void* scales,
                            const float* global_scales, const int* offsets, void* out, int64_t ld_out, int experts,
-                           int n_padded, int k, int n_out, int swiglu, int* status, void* stream);
+                           int weight_experts, int n_padded, int k, int n_out, int swiglu, int* status, void* stream);
 
 /* Causal attention of the new tokens over the paged FP8 cache (which already holds the new
  * tokens' K/V rows): q8 e4m3 [tokens, hq, head_dim]; caches e4m3 [cache_rows, hkv, head_dim];

@@ -49,7 +49,8 @@ struct GroupedArgs {
   const int* offsets;      // [experts + 1] slab row ranges
   void* out;
   int64_t ld_out;
-  int experts, n, k;       // n = padded weight rows (multiple of 256), k multiple of 64
+  int experts, n, k;       // experts = row groups; n = padded weight rows (multiple of 256), k multiple of 64
+  int wexperts;            // weight banks: group g uses bank g % wexperts
   int n_out;               // valid output columns (after the SwiGLU halving when fused)
   int swiglu;
   int* status;
@@ -216,7 +217,7 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
       tc_fence_after();
       const int r = quarter * 32 + lane;
       const bool valid = r < ti.rows;
-      const float alpha = p.gs[ti.expert] * 256.0f;
+      const float alpha = p.gs[ti.expert % p.wexperts] * 256.0f;
       const uint32_t taddr = tmem_base + acc * kGN + (static_cast<uint32_t>(quarter * 32) << 16);
       __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<int64_t>(ti.row0 + r) * p.ld_out;
       if (p.swiglu) {
@@ -284,7 +285,7 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
     bool ok = true;
     for (int g = blockIdx.x; g < total_tiles && ok; g += gridDim.x) {
       const TileInfo ti = decode_tile(g, mt_prefix, p.offsets, p.experts, n_tiles);
-      const int64_t tile_id = (static_cast<int64_t>(ti.expert) * n_tiles + ti.nt) * k_blocks;
+      const int64_t tile_id = (static_cast<int64_t>(ti.expert % p.wexperts) * n_tiles + ti.nt) * k_blocks;
       const uint8_t* wq = p.wq + tile_id * (kGN * 32) + row * 32;
       const uint8_t* sf = p.sf + tile_id * (kGN * 4) + row * 4;
       for (int kb = 0; kb < k_blocks; ++kb, ++it) {
@@ -400,10 +401,11 @@ extern "C" int msl_nvfp4_repack(const void* src_codes, const void* src_scales, v
 
 extern "C" int msl_grouped_gemm_nvfp4(const void* x, int64_t slab_rows, const void* codes, const void* scales,
                                       const float* global_scales, const int* offsets, void* out, int64_t ld_out,
-                                      int experts, int n_padded, int k, int n_out, int swiglu, int* status,
-                                      void* stream) {
+                                      int experts, int weight_experts, int n_padded, int k, int n_out, int swiglu,
+                                      int* status, void* stream) {
   if (!x || !codes || !scales || !global_scales || !offsets || !out) return MSL_ERR_ARG;
-  if (experts <= 0 || experts > kMaxLocal || n_padded <= 0 || k <= 0 || n_out <= 0 || slab_rows < 0)
+  if (experts <= 0 || experts > kMaxLocal || weight_experts <= 0 || n_padded <= 0 || k <= 0 || n_out <= 0 ||
+      slab_rows < 0)
     return MSL_ERR_ARG;
   if ((n_padded % kGN) || (k % kGK)) return MSL_ERR_UNSUPPORTED;
   if ((reinterpret_cast<uintptr_t>(x) & 15) || (ld_out & 7) || (reinterpret_cast<uintptr_t>(out) & 15))
@@ -414,7 +416,7 @@ extern "C" int msl_grouped_gemm_nvfp4(const void* x, int64_t slab_rows, const vo
                         kGM, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc) return rc;
   GroupedArgs a{static_cast<const uint8_t*>(codes), static_cast<const uint8_t*>(scales), global_scales, offsets, out,
-                ld_out, experts, n_padded, k, n_out, swiglu, status};
+                ld_out, experts, n_padded, k, weight_experts, n_out, swiglu, status};
   const int smem = GroupedSmem::kTotal + 1024;
   static bool configured = false;
   if (!configured) {

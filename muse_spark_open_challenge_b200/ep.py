@@ -1,0 +1,145 @@
+"""Expert-parallel form of the layer: one process per GPU, experts sharded contiguously
+(rank r owns experts [r*E/W, (r+1)*E/W), the reference's `local_start` notion, reference.py:48-50,
+466), requests sharded by rank, one exchange pair per layer over `torch.distributed`.
+
+The reference replaces every cross-GPU step by the identity (reference.py:438,451,467); this module
+supplies the exchange it leaves out:
+
+    route over ALL experts -> rows grouped by expert (= grouped by owner rank)
+    counts all-to-all -> row all-to-all (dispatch) -> local grouped GEMMs over (source, expert) groups
+    -> row all-to-all back (combine) -> local weighted sum
+
+The plan and both exchanges are device- and backend-agnostic (`gloo` on CPU in the tests, `nccl` on
+GPUs).  The split sizes are read on the host (one small synchronisation per layer).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+from . import layer, ops
+from ._lib import OUT_F32, OUT_SWIGLU_BF16
+
+
+@dataclass
+class ExchangePlan:
+    send_splits: list      # rows this rank sends to each rank (its routes to that rank's experts)
+    recv_splits: list      # rows this rank receives from each rank
+    recv_counts: torch.Tensor   # i32 [world, local experts]: rows from source s for local expert e
+    group_offsets: torch.Tensor  # i32 [world * local + 1]: row ranges of the (source, expert) groups
+
+    @property
+    def recv_rows(self):
+        return sum(self.recv_splits)
+
+
+def make_plan(counts: torch.Tensor, world: int, group=None) -> ExchangePlan:
+    """counts: i32 [E] routes of this rank per global expert (rows of the send slab are ordered by
+    expert).  One all-to-all of the counts tells every rank what it will receive."""
+    e = counts.numel()
+    local = e // world
+    mat = counts.view(world, local).contiguous()
+    recv = torch.empty_like(mat)
+    dist.all_to_all_single(recv, mat, group=group)
+    both = torch.stack([mat.sum(1), recv.sum(1)]).cpu()          # the one host synchronisation
+    offs = torch.zeros(world * local + 1, dtype=torch.int32, device=counts.device)
+    offs[1:] = torch.cumsum(recv.flatten(), 0).to(torch.int32)
+    return ExchangePlan(both[0].tolist(), both[1].tolist(), recv, offs)
+
+
+def exchange_rows(send: torch.Tensor, out_rows: int, send_splits, recv_splits, out=None, group=None):
+    """Variable-size all-to-all of rows (dim 0)."""
+    if out is None:
+        out = torch.empty((out_rows, send.shape[1]), dtype=send.dtype, device=send.device)
+    dist.all_to_all_single(out[:out_rows], send, list(recv_splits), list(send_splits), group=group)
+    return out
+
+
+class ExpertParallel:
+    """Per-rank context: world geometry plus grow-only receive buffers."""
+
+    def __init__(self, st: dict, world: int, rank: int, n_experts: int, group=None):
+        if n_experts % world:
+            raise ValueError("the expert count must divide evenly over the ranks")
+        if st["n_local"] != n_experts // world:
+            raise ValueError("state holds a different number of local experts than n_experts / world")
+        self.world, self.rank, self.n_experts, self.group = world, rank, n_experts, group
+        self.zero = torch.zeros(1, dtype=torch.int32, device=st["device"])
+        self.counts = torch.zeros(n_experts, dtype=torch.int32, device=st["device"])
+        self.send_offsets = torch.zeros(n_experts + 1, dtype=torch.int32, device=st["device"])
+        self.cap = 0
+        self.recv_x = self.recv_i = None
+
+    def buffers(self, st, rows):
+        if rows > self.cap:
+            rows_cap = int(rows * 1.25) + 128
+            self.recv_x = torch.empty((rows_cap, st["moe_width"]), dtype=torch.bfloat16, device=st["device"])
+            self.recv_i = torch.empty((rows_cap, st["inter"]), dtype=torch.bfloat16, device=st["device"])
+            self.cap = rows_cap
+        return self.recv_x, self.recv_i
+
+
+def moe_stage(h, data, st, ctx: ExpertParallel):
+    """Expert-parallel counterpart of layer.moe_stage."""
+    cfg = data["config"]
+    top_k, status = cfg["top_k"], st["status"]
+    tokens, hidden = h.shape
+    logits = ops.gemm(h, st["router_hilo"], out_mode=OUT_F32, k=hidden, segs=2, a_seg_stride=0, b_seg_stride=hidden,
+                      status=status)
+    layer._mark(st, "gemm_router")
+    ctx.counts.zero_()
+    # every expert is a dispatch target here: rows come out grouped by global expert
+    ids, tw, local_ids, slots = ops.route_topk(logits, st["router_bias"], layer.ROUTER_MULTIPLIER, ctx.zero,
+                                               ctx.n_experts, top_k, ctx.n_experts, ctx.counts)
+    layer._mark(st, "route_topk")
+    send_x, _ = layer._scratch(st, tokens, top_k)
+    if st["pooled"]:
+        p = ops.gemm(h, st["pooler"], status=status)
+        rowmap = ops.dispatch(p, st["w_pre_exp"], local_ids, slots, ctx.counts, send_x, ctx.send_offsets, status)
+    else:
+        rowmap = ops.dispatch(h, None, local_ids, slots, ctx.counts, send_x, ctx.send_offsets, status)
+    layer._mark(st, "dispatch")
+    plan = make_plan(ctx.counts, ctx.world, ctx.group)
+    recv_x, recv_i = ctx.buffers(st, max(plan.recv_rows, 1))
+    exchange_rows(send_x, plan.recv_rows, plan.send_splits, plan.recv_splits, out=recv_x, group=ctx.group)
+    layer._mark(st, "a2a_dispatch")
+    rows = max(plan.recv_rows, 1)
+    ops.grouped_gemm_nvfp4(recv_x[:rows], st["w13_q"], st["w13_s"], st["w13_gs"], plan.group_offsets, recv_i[:rows],
+                           st["inter"], True, status)
+    layer._mark(st, "experts_gate_up")
+    ops.grouped_gemm_nvfp4(recv_i[:rows], st["w2_q"], st["w2_s"], st["w2_gs"], plan.group_offsets, recv_x[:rows],
+                           st["moe_width"], False, status)
+    layer._mark(st, "experts_down")
+    st["offsets"][-1:] = plan.group_offsets[-1:]            # rows computed on this rank (for the bench's FLOP count)
+    exchange_rows(recv_x[:plan.recv_rows], tokens * top_k, plan.recv_splits, plan.send_splits, out=send_x,
+                  group=ctx.group)
+    layer._mark(st, "a2a_combine")
+    shared = None
+    if st["shared"]:
+        s_inter = ops.gemm(h, st["shared_w13"], out_mode=OUT_SWIGLU_BF16, status=status)
+        shared = ops.gemm(s_inter, st["shared_w2"], status=status)
+        layer._mark(st, "shared_expert")
+    moe = ops.combine(send_x, rowmap, tw, st["w_post_exp"], addend=shared)
+    layer._mark(st, "combine")
+    if st["pooled"]:
+        moe = ops.gemm(moe, st["unpooler"], status=status)
+        layer._mark(st, "gemm_unpooler")
+    return moe, ids
+
+
+def kernel_fn(data: dict, st: dict, ctx: ExpertParallel):
+    """Same contract as layer.kernel_fn for this rank's requests; `st` holds this rank's slice of
+    the expert banks."""
+    o_in = layer.attention_stage(data, st)
+    a = ops.gemm(o_in, st["o"], status=st["status"])
+    layer._mark(st, "gemm_o")
+    s1, h = ops.boundary(a, None, data["stream"], st["a1"], st["b1"], st["w_pre_ffn"], layer.POST_NORM_EPS,
+                         layer.RMS_EPS)
+    layer._mark(st, "boundary_attn")
+    f, ids = moe_stage(h, data, st, ctx)
+    s2, hidden = ops.boundary(f, st["w_post_ffn"], s1, st["a2"], st["b2"], st["w_next"], layer.POST_NORM_EPS,
+                              layer.RMS_EPS)
+    layer._mark(st, "boundary_ffn")
+    return hidden, s2, ids

@@ -154,7 +154,8 @@ def nvfp4_repack(codes, scales, interleave):
 
 
 def grouped_gemm_nvfp4(x, codes_t, scales_t, global_scales, offsets, out, n_out, swiglu, status=None):
-    """out[r] = gs[e] * x[r] @ dq(W_e).T over each expert's slab range (fused SiLU*up when swiglu)."""
+    """out[r] = gs[e] * x[r] @ dq(W_e).T over each row group's slab range (fused SiLU*up when swiglu).
+    `offsets` has one more entry than there are row groups; group g uses weight bank g % E."""
     _need(x, torch.bfloat16, "x"), _need(out, torch.bfloat16, "out"), _need(offsets, torch.int32, "offsets")
     _need(global_scales, torch.float32, "global_scales")
     e, n_tiles, k_blocks = codes_t.shape[:3]
@@ -162,7 +163,8 @@ def grouped_gemm_nvfp4(x, codes_t, scales_t, global_scales, offsets, out, n_out,
         raise MslError("x must be contiguous")
     check(_lib.lib().msl_grouped_gemm_nvfp4(x.data_ptr(), x.shape[0], codes_t.data_ptr(), scales_t.data_ptr(),
                                             global_scales.data_ptr(), offsets.data_ptr(), out.data_ptr(),
-                                            _rows(out, "out"), e, n_tiles * 256, k_blocks * 64, n_out, int(swiglu),
+                                            _rows(out, "out"), offsets.numel() - 1, e, n_tiles * 256, k_blocks * 64,
+                                            n_out, int(swiglu),
                                             _ptr(status), _stream()), "msl_grouped_gemm_nvfp4")
     return out
 

@@ -1,0 +1,60 @@
+"""Expert parallelism on real GPUs (needs >= 2): every rank runs its own requests, experts are
+sharded, rows travel by NCCL all-to-all; each rank's output must pass the reference's acceptance
+check against the CPU oracle evaluated with ALL experts local."""
+import dataclasses
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from muse_spark_open_challenge_b200 import ep, layer, synth
+        from oracle import layer_ref as L
+        from conftest import to_device
+        shape = dataclasses.replace(synth.MID, hidden=1024, hq=8, hkv=2, n_experts=16, local_experts=16,
+                                    moe_width=1024, inter=256, shared_inter=512)
+        weights = synth.make_weights(shape, seed=5)                      # identical on every rank
+        data = synth.make_input(shape, [150 + 40 * rank, 77], [30, 0], seed=20 + rank, page=64, kv_scale=0.5)
+        local = shape.n_experts // world
+        mine = dict(weights)
+        for k in ("w13", "w13_sf", "w13_gs", "w2", "w2_sf", "w2_gs"):
+            mine[k] = weights[k][rank * local:(rank + 1) * local]
+        st = layer.prepare(to_device(mine, f"cuda:{rank}"))
+        ctx = ep.ExpertParallel(st, world, rank, shape.n_experts)
+        dev = to_device(data, f"cuda:{rank}")
+        hidden, stream, ids = ep.kernel_fn(dev, st, ctx)
+        hidden2, stream2, ids2 = ep.kernel_fn(dev, st, ctx)             # repeatable
+        torch.cuda.synchronize()
+        layer.check_status(st)
+        assert torch.equal(hidden, hidden2) and torch.equal(ids, ids2)
+        d = L.dims_of(weights, data["config"])
+        slots = L.new_slots(data).cuda()
+        k_rows = dev["k_cache"].view(-1, d.hkv, d.head_dim)[slots].cpu()
+        v_rows = dev["v_cache"].view(-1, d.hkv, d.head_dim)[slots].cpu()
+        ok, msg, _ = L.check_layer(data, weights, hidden.cpu(), stream.cpu(), ids.cpu(), k_rows, v_rows)
+        assert ok, f"rank {rank}: {msg}"
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_expert_parallel_layer_matches_oracle_on_two_gpus():
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    mp.spawn(_worker, args=(2, _free_port()), nprocs=2, join=True)
