@@ -127,7 +127,7 @@ int64_t msl_nvfp4_padded_rows(int rows, int interleave);
  * tiles [experts, n_padded/256, k/64, 256, 32] and [.., 256, 4] consumed by
  * msl_grouped_gemm_nvfp4.  With interleave != 0 the bank is gate rows then up rows and tile j
  * holds gate rows [128 j, 128 j + 128) followed by their up rows.  A permutation of the input
- * bytes and nibbles; padding rows are zero.  Takes the place of the reference's load-time
+ * bits; padding rows are zero.  Takes the place of the reference's load-time
  * weight repack (submission.py:934-950).  k: multiple of 64. */
 int msl_nvfp4_repack(const void* src_codes, const void* src_scales, void* dst_codes, void* dst_scales, int experts,
                      int rows, int k, int interleave, void* stream);

@@ -351,74 +351,58 @@ dispatch_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, const float* _
 // ============================================================================ weighted combine
 // out[t] = sum_j w[t, j] * rms(y[rowmap[t, j]] * post_w, eps 1e-8)  (+ addend[t]); routes with
 // rowmap < 0 (another rank's expert) contribute nothing (reference.py:427-444).
-// One block per token, every thread owns one 8-channel chunk of every route's row.
-template <int MAXK, int MAXC>
-__global__ void __launch_bounds__(512)
+// One block per token; every thread owns one 8-channel chunk of every route's row.  The raw 16-byte
+// loads of all routes are issued first and kept in registers across the block-wide sum of squares,
+// so each row crosses HBM exactly once.
+template <int MAXK>
+__global__ void __launch_bounds__(512, 2)
 combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ rowmap, const float* __restrict__ w,
                const float* __restrict__ post_w, const __nv_bfloat16* __restrict__ addend, int64_t ld_add,
                __nv_bfloat16* __restrict__ out, int64_t ld_out, int top_k, int width) {
   __shared__ float scratch[32 * MAXK];
   const int t = blockIdx.x;
-  const int chunks = width / 8;
-  float acc[MAXC][8];
-#pragma unroll
-  for (int c = 0; c < MAXC; ++c)
-#pragma unroll
-    for (int i = 0; i < 8; ++i) acc[c][i] = 0.f;
-  int rows[MAXK];
-  float wt[MAXK];
+  const int ch = threadIdx.x;
+  const bool live = ch < width / 8;
+  uint32_t valid = 0;                      // bit j: route j has a slab row
+  uint4 raw[MAXK];
 #pragma unroll
   for (int j = 0; j < MAXK; ++j) {
-    rows[j] = j < top_k ? rowmap[t * top_k + j] : -1;
-    wt[j] = j < top_k ? w[t * top_k + j] : 0.f;
-  }
-#pragma unroll
-  for (int c = 0; c < MAXC; ++c) {
-    const int ch = threadIdx.x + c * blockDim.x;
-    // (MAXC > 1 only for rows wider than 8 * blockDim: the sums below then cover one chunk set at a time)
-    float v[MAXK][8];
-    float ss[MAXK];
-    float pw[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    if (ch < chunks) {
-      const float4 w0 = *reinterpret_cast<const float4*>(post_w + ch * 8);
-      const float4 w1 = *reinterpret_cast<const float4*>(post_w + ch * 8 + 4);
-      pw[0] = w0.x; pw[1] = w0.y; pw[2] = w0.z; pw[3] = w0.w; pw[4] = w1.x; pw[5] = w1.y; pw[6] = w1.z; pw[7] = w1.w;
-    }
-#pragma unroll
-    for (int j = 0; j < MAXK; ++j) {
-      ss[j] = 0.f;
-      if (rows[j] >= 0 && ch < chunks) {
-        unpack8(*reinterpret_cast<const uint4*>(y + static_cast<int64_t>(rows[j]) * width + ch * 8), v[j]);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          v[j][i] *= pw[i];
-          ss[j] += v[j][i] * v[j][i];
-        }
-      } else {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[j][i] = 0.f;
-      }
-    }
-    static_assert(MAXC == 1, "rows wider than 8 * blockDim need a two-pass sum");
-    block_sum<MAXK>(ss, scratch);
-#pragma unroll
-    for (int j = 0; j < MAXK; ++j) {
-      if (rows[j] >= 0) {
-        const float r = wt[j] / sqrtf(ss[j] / width + 1e-8f);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) acc[c][i] += v[j][i] * r;
-      }
-    }
-    if (ch < chunks) {
-      if (addend != nullptr) {
-        float a[8];
-        unpack8(*reinterpret_cast<const uint4*>(addend + t * ld_add + ch * 8), a);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) acc[c][i] += a[i];
-      }
-      *reinterpret_cast<uint4*>(out + t * ld_out + ch * 8) = pack8(acc[c]);
+    const int row = j < top_k ? rowmap[t * top_k + j] : -1;
+    raw[j] = make_uint4(0, 0, 0, 0);
+    if (row >= 0) {
+      valid |= 1u << j;
+      if (live) raw[j] = __ldcs(reinterpret_cast<const uint4*>(y + static_cast<int64_t>(row) * width + ch * 8));
     }
   }
+  float pw[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (live) {
+    const float4 w0 = *reinterpret_cast<const float4*>(post_w + ch * 8);
+    const float4 w1 = *reinterpret_cast<const float4*>(post_w + ch * 8 + 4);
+    pw[0] = w0.x; pw[1] = w0.y; pw[2] = w0.z; pw[3] = w0.w; pw[4] = w1.x; pw[5] = w1.y; pw[6] = w1.z; pw[7] = w1.w;
+    if (addend != nullptr) unpack8(*reinterpret_cast<const uint4*>(addend + t * ld_add + ch * 8), acc);
+  }
+  float ss[MAXK];
+#pragma unroll
+  for (int j = 0; j < MAXK; ++j) {
+    float v[8];
+    unpack8(raw[j], v);
+    ss[j] = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { const float x = v[i] * pw[i]; ss[j] += x * x; }
+  }
+  block_sum<MAXK>(ss, scratch);
+#pragma unroll
+  for (int j = 0; j < MAXK; ++j) {
+    if (valid & (1u << j)) {
+      const float r = w[t * top_k + j] / sqrtf(ss[j] / width + 1e-8f);
+      float v[8];
+      unpack8(raw[j], v);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] += v[i] * pw[i] * r;
+    }
+  }
+  if (live) *reinterpret_cast<uint4*>(out + t * ld_out + ch * 8) = pack8(acc);
 }
 
 }  // namespace msl
@@ -535,11 +519,9 @@ extern "C" int msl_combine(const void* y, const int* rowmap, const float* weight
   auto* ad = static_cast<const __nv_bfloat16*>(addend);
   auto* oo = static_cast<__nv_bfloat16*>(out);
   if (top_k <= 4)
-    combine_kernel<4, 1><<<tokens, threads, 0, st>>>(yy, rowmap, weights, post_w, ad, ld_addend, oo, ld_out, top_k,
-                                                     width);
+    combine_kernel<4><<<tokens, threads, 0, st>>>(yy, rowmap, weights, post_w, ad, ld_addend, oo, ld_out, top_k, width);
   else
-    combine_kernel<8, 1><<<tokens, threads, 0, st>>>(yy, rowmap, weights, post_w, ad, ld_addend, oo, ld_out, top_k,
-                                                     width);
+    combine_kernel<8><<<tokens, threads, 0, st>>>(yy, rowmap, weights, post_w, ad, ld_addend, oo, ld_out, top_k, width);
   return cudaGetLastError() == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
 }
 

@@ -11,10 +11,15 @@
 //   warp 0      TMA producer: activation tile 128 rows x 64 k (bf16, 128-byte swizzle)
 //   warp 1      TMEM allocation + tcgen05.mma issue (M=128 tokens, N=256 weight rows, K=16)
 //   warps 2-5   epilogue (TMEM -> registers -> global)
-//   warps 6-13  weight producers: each thread dequantises one weight row of the stage (64 codes +
-//               4 block scales -> 64 bf16) straight into the swizzled B tile in shared memory
-// The weights were re-tiled once at load time (msl_nvfp4_repack) so a stage's codes are one
-// contiguous 8 KiB block and its scales one contiguous 1 KiB block.
+//   warps 6-13  weight producers in two groups of 4 warps that take alternate stages: each thread
+//               dequantises two weight rows of its stage (2 x (64 codes + 4 block scales) -> 128 bf16)
+//               straight into the swizzled B tile in shared memory, while the codes of its next stage
+//               are already in flight from L2
+// N = 256 keeps the tensor core's operand fetch per FLOP low (a 128-column tile measured 25 % slower
+// with the dequantisation switched off); producing a stage is a latency-bound chain, and two groups
+// on different stages hide it (one group on every stage measured 30 % slower).  The weights were
+// re-tiled once at load time (msl_nvfp4_repack) so a stage's codes are one contiguous 8 KiB block and
+// its scales one contiguous 1 KiB block.
 //
 // Dequantisation without a table for the codes: a 4-bit code s|e1 e0|m placed at bf16 bits
 // 15|8 7|6 is the bf16 number value * 2^-126 (also for the subnormal codes 0 and 0.5); the block
@@ -25,14 +30,21 @@
 
 namespace msl {
 
-constexpr int kGM = 128;       // token rows per tile
-constexpr int kGN = 256;       // weight rows per tile
+constexpr int kSubM = 128;     // rows of one MMA (TMEM lanes)
+constexpr int kSubs = 1;       // activation sub-tiles (MMAs) sharing one dequantised B tile
+constexpr int kGM = kSubM * kSubs;
+constexpr int kGN = 256;       // weight rows per tile: N = 256 keeps the MMA operand fetch per FLOP low
+constexpr int kProducers = 256;               // weight-producer threads
+constexpr int kGroups = 2;                    // producer groups, each taking every kGroups-th stage
+constexpr int kGroupThreads = kProducers / kGroups;
+constexpr int kRowsPerThread = kGN / kGroupThreads;   // weight rows (64 codes each) per thread per stage
 constexpr int kGK = 64;        // k per stage
 constexpr int kGStages = 4;
-constexpr int kMaxLocal = 256; // experts per call
+constexpr int kMaxLocal = 256; // row groups per call
 
 struct GroupedSmem {
-  static constexpr int kABytes = kGM * kGK * 2;
+  static constexpr int kSubBytes = kSubM * kGK * 2;
+  static constexpr int kABytes = kSubs * kSubBytes;
   static constexpr int kBBytes = kGN * kGK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kLutOffset = kGStages * kStageBytes;          // 256 x u32
@@ -43,13 +55,13 @@ struct GroupedSmem {
 static_assert(GroupedSmem::kBarOffset % 8 == 0, "barriers must be 8-byte aligned");
 
 struct GroupedArgs {
-  const uint8_t* wq;       // [experts][n_tiles][k_blocks][256 rows][32 bytes]
-  const uint8_t* sf;       // [experts][n_tiles][k_blocks][256 rows][4 bytes]
-  const float* gs;         // [experts]
-  const int* offsets;      // [experts + 1] slab row ranges
+  const uint8_t* wq;       // [banks][n_tiles][k_blocks][128 rows][32 bytes]
+  const uint8_t* sf;       // [banks][n_tiles][k_blocks][128 rows][4 bytes]
+  const float* gs;         // [banks]
+  const int* offsets;      // [groups + 1] slab row ranges
   void* out;
   int64_t ld_out;
-  int experts, n, k;       // experts = row groups; n = padded weight rows (multiple of 256), k multiple of 64
+  int experts, n, k;       // experts = row groups; n = padded weight rows (multiple of 128), k multiple of 64
   int wexperts;            // weight banks: group g uses bank g % wexperts
   int n_out;               // valid output columns (after the SwiGLU halving when fused)
   int swiglu;
@@ -57,12 +69,13 @@ struct GroupedArgs {
 };
 
 struct TileInfo {
-  int expert, row0, rows, nt;   // first slab row, valid rows in the tile, n tile
+  int expert, row0, rows, nt;   // row group, first slab row, valid rows in the tile (<= 256), n tile
 };
 
 __device__ __forceinline__ TileInfo decode_tile(int g, const int* mt_prefix, const int* offsets, int experts,
                                                 int n_tiles) {
-  // mt_prefix[e] = number of 128-row tiles of the experts before e.
+  // mt_prefix[e] = number of 256-row tiles of the groups before e.  Tiles of one (group, n tile)
+  // are adjacent so the weight tile they share stays in L2.
   int lo = 0, hi = experts - 1;
   while (lo < hi) {
     const int mid = (lo + hi + 1) >> 1;
@@ -82,18 +95,63 @@ __device__ __forceinline__ TileInfo decode_tile(int g, const int* mt_prefix, con
 }
 
 // Eight codes of one 32-bit word -> four bf16x2 words (elements 2j, 2j+1 in word j), times the
-// block scale.  Word layout made by the repack: nibble j holds element 2j, nibble j+4 element 2j+1.
+// block scale.  The repack put the even elements in the low half-word and the odd ones in the
+// high half-word, element pair j at half-word bits: j=0: 15|8 7 6 (already in place), j=1: 12|5 4 3,
+// j=2: 9|2 1 0, j=3: 14|13 11 10 (sign | e1 e0 m).  Pairs 0-2 need one shift and one mask.
 __device__ __forceinline__ uint4 dequant8(uint32_t w, uint32_t scale2) {
+  constexpr uint32_t kMask = 0x81C081C0u;
+  uint32_t b[4];
+  b[0] = w & kMask;
+  b[1] = (w << 3) & kMask;
+  b[2] = (w << 6) & kMask;
+  b[3] = ((w >> 4) & 0x00C000C0u) | ((w >> 5) & 0x01000100u) | ((w << 1) & 0x80008000u);
   uint32_t o[4];
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
-    const uint32_t t = w >> (4 * j);
-    const uint32_t bits = ((t & 0x00070007u) << 6) | ((t & 0x00080008u) << 12);
-    __nv_bfloat162 v = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&bits),
+    __nv_bfloat162 v = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&b[j]),
                                *reinterpret_cast<const __nv_bfloat162*>(&scale2));
     o[j] = *reinterpret_cast<uint32_t*>(&v);
   }
   return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+template <bool SWIGLU>
+__device__ __forceinline__ void store_rows(const GroupedArgs& p, const TileInfo& ti, uint32_t taddr, int r,
+                                           float alpha) {
+  // One thread owns row r of the tile: 128 accumulator columns -> 128 (or 64 fused) outputs.
+  const bool valid = r < ti.rows;
+  __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<int64_t>(ti.row0 + r) * p.ld_out;
+  constexpr int kOutCols = SWIGLU ? kGN / 2 : kGN;
+#pragma unroll 1
+  for (int c = 0; c < kOutCols; c += 32) {
+    uint32_t a[32], b[32];
+    tmem_ld32(taddr + c, a);
+    if constexpr (SWIGLU) tmem_ld32(taddr + kGN / 2 + c, b);
+    tmem_ld_wait();
+    const int col0 = ti.nt * kOutCols + c;
+    if (valid && col0 < p.n_out) {
+      uint32_t packed[16];
+#pragma unroll
+      for (int j = 0; j < 32; j += 2) {
+        float v0 = __uint_as_float(a[j]) * alpha, v1 = __uint_as_float(a[j + 1]) * alpha;
+        if constexpr (SWIGLU) {
+          const float u0 = __uint_as_float(b[j]) * alpha, u1 = __uint_as_float(b[j + 1]) * alpha;
+          v0 = v0 / (1.0f + __expf(-v0)) * u0;
+          v1 = v1 / (1.0f + __expf(-v1)) * u1;
+        }
+        packed[j / 2] = pack_bf16x2(v0, v1);
+      }
+      if (col0 + 32 <= p.n_out) {
+#pragma unroll
+        for (int j = 0; j < 16; j += 4)
+          *reinterpret_cast<uint4*>(orow + col0 + 2 * j) = make_uint4(packed[j], packed[j + 1], packed[j + 2], packed[j + 3]);
+      } else {
+        for (int j = 0; j < 32 && col0 + j < p.n_out; ++j)
+          orow[col0 + j] = __ushort_as_bfloat16(
+              static_cast<unsigned short>((j & 1) ? (packed[j / 2] >> 16) : (packed[j / 2] & 0xffffu)));
+      }
+    }
+  }
 }
 
 __global__ void __launch_bounds__(448, 1)
@@ -125,7 +183,7 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
     lut[i] = b | (b << 16);
   }
   if (warp == 0) {
-    // prefix of 128-row tile counts per expert, one warp
+    // prefix of 256-row tile counts per row group, one warp
     int carry = 0;
     for (int b0 = 0; b0 < p.experts; b0 += 32) {
       const int i = b0 + lane;
@@ -143,7 +201,7 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
   }
   if (threadIdx.x == 0) {
     for (int s = 0; s < kGStages; ++s) {
-      mbar_init(&full[s], 1 + 8);   // producer's expect_tx arrival + 8 weight-producer warps
+      mbar_init(&full[s], 1 + kGroupThreads / 32);   // TMA producer's expect_tx arrival + one weight-producer group
       mbar_init(&empty[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -153,7 +211,7 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
     *abort_flag = 0;
     mbar_fence_init();
   }
-  if (warp == 1) tmem_alloc(tmem_base_slot, 2 * kGN);
+  if (warp == 1) tmem_alloc(tmem_base_slot, 2 * kSubs * kGN);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -161,32 +219,39 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
   const int total_tiles = mt_prefix[p.experts] * n_tiles;
 
   if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer: activation sub-tiles
     if (lane == 0) {
       tma_prefetch_desc(&tm_x);
       uint32_t it = 0;
       bool ok = true;
       for (int g = blockIdx.x; g < total_tiles && ok; g += gridDim.x) {
         const TileInfo ti = decode_tile(g, mt_prefix, p.offsets, p.experts, n_tiles);
+        const int nsub = (ti.rows + kSubM - 1) / kSubM;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % kGStages;
           const uint32_t ph = (it / kGStages) & 1;
           if (*abort_flag || !mbar_wait(&empty[s], ph ^ 1)) { ok = false; break; }
-          mbar_expect_tx(&full[s], S::kABytes);
-          tma_load_2d(smem + s * S::kStageBytes, &tm_x, &full[s], kb * kGK, ti.row0);
+          mbar_expect_tx(&full[s], nsub * S::kSubBytes);
+          for (int sub = 0; sub < nsub; ++sub)
+            tma_load_2d(smem + s * S::kStageBytes + sub * S::kSubBytes, &tm_x, &full[s], kb * kGK,
+                        ti.row0 + sub * kSubM);
         }
       }
       if (!ok) { *abort_flag = 1; report_error(p.status, MSL_ERR_DEVICE_TIMEOUT); }
     }
   } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(1, 1, kGM, kGN);
+      constexpr uint32_t idesc = make_idesc(1, 1, kSubM, kGN);
       uint32_t it = 0, tile_i = 0;
       bool ok = true;
       for (int g = blockIdx.x; g < total_tiles && ok; g += gridDim.x, ++tile_i) {
+        const TileInfo ti = decode_tile(g, mt_prefix, p.offsets, p.experts, n_tiles);
+        const int nsub = (ti.rows + kSubM - 1) / kSubM;
         const uint32_t acc = tile_i & 1, acc_ph = (tile_i >> 1) & 1;
         if (*abort_flag || !mbar_wait(&tmem_empty[acc], acc_ph ^ 1)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * kGN;
+        const uint32_t d_tmem = tmem_base + acc * (kSubs * kGN);
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % kGStages;
           const uint32_t ph = (it / kGStages) & 1;
@@ -196,8 +261,10 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
           const uint32_t sb = sa + S::kABytes;
 #pragma unroll
           for (int k16 = 0; k16 < kGK / 16; ++k16) {
-            tc_mma_f16(d_tmem, make_sdesc(sa + k16 * 32, 16, 1024, 2), make_sdesc(sb + k16 * 32, 16, 1024, 2),
-                       idesc, (kb | k16) != 0);
+            const uint64_t db = make_sdesc(sb + k16 * 32, 16, 1024, 2);
+            for (int sub = 0; sub < nsub; ++sub)
+              tc_mma_f16(d_tmem + sub * kGN, make_sdesc(sa + sub * S::kSubBytes + k16 * 32, 16, 1024, 2), db, idesc,
+                         (kb | k16) != 0);
           }
           tc_commit(&empty[s]);
         }
@@ -212,66 +279,17 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
     bool ok = true;
     for (int g = blockIdx.x; g < total_tiles && ok; g += gridDim.x, ++tile_i) {
       const TileInfo ti = decode_tile(g, mt_prefix, p.offsets, p.experts, n_tiles);
+      const int nsub = (ti.rows + kSubM - 1) / kSubM;
       const uint32_t acc = tile_i & 1, acc_ph = (tile_i >> 1) & 1;
       if (*abort_flag || !mbar_wait(&tmem_full[acc], acc_ph)) { ok = false; break; }
       tc_fence_after();
-      const int r = quarter * 32 + lane;
-      const bool valid = r < ti.rows;
       const float alpha = p.gs[ti.expert % p.wexperts] * 256.0f;
-      const uint32_t taddr = tmem_base + acc * kGN + (static_cast<uint32_t>(quarter * 32) << 16);
-      __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<int64_t>(ti.row0 + r) * p.ld_out;
-      if (p.swiglu) {
-#pragma unroll 1
-        for (int c = 0; c < kGN / 2; c += 32) {
-          uint32_t gt[32], up[32];
-          tmem_ld32(taddr + c, gt);
-          tmem_ld32(taddr + kGN / 2 + c, up);
-          tmem_ld_wait();
-          const int col0 = ti.nt * (kGN / 2) + c;
-          if (valid && col0 < p.n_out) {
-            uint32_t packed[16];
-#pragma unroll
-            for (int j = 0; j < 32; j += 2) {
-              const float g0 = __uint_as_float(gt[j]) * alpha, g1 = __uint_as_float(gt[j + 1]) * alpha;
-              const float u0 = __uint_as_float(up[j]) * alpha, u1 = __uint_as_float(up[j + 1]) * alpha;
-              packed[j / 2] = pack_bf16x2(g0 / (1.0f + __expf(-g0)) * u0, g1 / (1.0f + __expf(-g1)) * u1);
-            }
-            if (col0 + 32 <= p.n_out) {
-#pragma unroll
-              for (int j = 0; j < 16; j += 4)
-                *reinterpret_cast<uint4*>(orow + col0 + 2 * j) =
-                    make_uint4(packed[j], packed[j + 1], packed[j + 2], packed[j + 3]);
-            } else {
-              for (int j = 0; j < 32 && col0 + j < p.n_out; ++j)
-                orow[col0 + j] = __ushort_as_bfloat16(static_cast<unsigned short>(
-                    (j & 1) ? (packed[j / 2] >> 16) : (packed[j / 2] & 0xffffu)));
-            }
-          }
-        }
-      } else {
-#pragma unroll 1
-        for (int c = 0; c < kGN; c += 32) {
-          uint32_t v[32];
-          tmem_ld32(taddr + c, v);
-          tmem_ld_wait();
-          const int col0 = ti.nt * kGN + c;
-          if (valid && col0 < p.n_out) {
-            uint32_t packed[16];
-#pragma unroll
-            for (int j = 0; j < 32; j += 2)
-              packed[j / 2] = pack_bf16x2(__uint_as_float(v[j]) * alpha, __uint_as_float(v[j + 1]) * alpha);
-            if (col0 + 32 <= p.n_out) {
-#pragma unroll
-              for (int j = 0; j < 16; j += 4)
-                *reinterpret_cast<uint4*>(orow + col0 + 2 * j) =
-                    make_uint4(packed[j], packed[j + 1], packed[j + 2], packed[j + 3]);
-            } else {
-              for (int j = 0; j < 32 && col0 + j < p.n_out; ++j)
-                orow[col0 + j] = __ushort_as_bfloat16(static_cast<unsigned short>(
-                    (j & 1) ? (packed[j / 2] >> 16) : (packed[j / 2] & 0xffffu)));
-            }
-          }
-        }
+      for (int sub = 0; sub < nsub; ++sub) {
+        const uint32_t taddr =
+            tmem_base + acc * (kSubs * kGN) + sub * kGN + (static_cast<uint32_t>(quarter * 32) << 16);
+        const int r = sub * kSubM + quarter * 32 + lane;
+        if (p.swiglu) store_rows<true>(p, ti, taddr, r, alpha);
+        else store_rows<false>(p, ti, taddr, r, alpha);
       }
       tc_fence_before();
       __syncwarp();
@@ -280,32 +298,76 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
     if (!ok && lane == 0) { *abort_flag = 1; report_error(p.status, MSL_ERR_DEVICE_TIMEOUT); }
   } else {
     // ------------------------------------------------------------ weight producers (warps 6-13)
-    const int row = threadIdx.x - 6 * 32;      // 0..255: weight row of the tile
-    uint32_t it = 0;
+    // The 8 producer warps form kGroups groups; group q produces stages q, q + kGroups, ...  Each
+    // stage's chain (wait for the free slot, table look-up, bit work, stores, proxy fence, arrive)
+    // is latency-bound, so letting the groups work on different stages at the same time hides it.
+    const int t = threadIdx.x - 6 * 32;        // 0..255
+    const int gid = t / kGroupThreads, tg = t % kGroupThreads;
+    // Packed codes and scales of the group's NEXT stage are fetched into registers while the
+    // current one is dequantised.
+    struct Cursor {
+      int g, kb;
+      const uint8_t* wq;
+      const uint8_t* sf;
+    };
+    auto seek = [&](Cursor& c) {               // pointers of tile c.g (if any)
+      if (c.g < total_tiles) {
+        const TileInfo ti = decode_tile(c.g, mt_prefix, p.offsets, p.experts, n_tiles);
+        const int64_t tile_id = (static_cast<int64_t>(ti.expert % p.wexperts) * n_tiles + ti.nt) * k_blocks;
+        c.wq = p.wq + tile_id * (kGN * 32) + tg * 32;
+        c.sf = p.sf + tile_id * (kGN * 4) + tg * 4;
+      }
+    };
+    auto advance = [&](Cursor& c, int n) {
+      c.kb += n;
+      bool moved = false;
+      while (c.kb >= k_blocks && c.g < total_tiles) { c.kb -= k_blocks; c.g += gridDim.x; moved = true; }
+      if (moved) seek(c);
+    };
+    uint32_t wbuf[2][kRowsPerThread][8];
+    uint32_t sbuf[2][kRowsPerThread];
+    auto fetch = [&](const Cursor& c, uint32_t (&w)[kRowsPerThread][8], uint32_t (&sc)[kRowsPerThread]) {
+#pragma unroll
+      for (int r = 0; r < kRowsPerThread; ++r) {
+        const uint8_t* wk = c.wq + static_cast<int64_t>(c.kb) * (kGN * 32) + r * (kGroupThreads * 32);
+        const uint8_t* sk = c.sf + static_cast<int64_t>(c.kb) * (kGN * 4) + r * (kGroupThreads * 4);
+        const uint4 c0 = __ldg(reinterpret_cast<const uint4*>(wk));
+        const uint4 c1 = __ldg(reinterpret_cast<const uint4*>(wk + 16));
+        w[r][0] = c0.x; w[r][1] = c0.y; w[r][2] = c0.z; w[r][3] = c0.w;
+        w[r][4] = c1.x; w[r][5] = c1.y; w[r][6] = c1.z; w[r][7] = c1.w;
+        sc[r] = __ldg(reinterpret_cast<const uint32_t*>(sk));
+      }
+    };
+    Cursor cons{static_cast<int>(blockIdx.x), 0, nullptr, nullptr};
+    seek(cons);
+    advance(cons, gid);
+    Cursor pf = cons;
+    if (pf.g < total_tiles) { fetch(pf, wbuf[0], sbuf[0]); advance(pf, kGroups); }
+    uint32_t it = gid;
     bool ok = true;
-    for (int g = blockIdx.x; g < total_tiles && ok; g += gridDim.x) {
-      const TileInfo ti = decode_tile(g, mt_prefix, p.offsets, p.experts, n_tiles);
-      const int64_t tile_id = (static_cast<int64_t>(ti.expert % p.wexperts) * n_tiles + ti.nt) * k_blocks;
-      const uint8_t* wq = p.wq + tile_id * (kGN * 32) + row * 32;
-      const uint8_t* sf = p.sf + tile_id * (kGN * 4) + row * 4;
-      for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+    while (cons.g < total_tiles && ok) {
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        if (cons.g >= total_tiles) break;
+        if (pf.g < total_tiles) { fetch(pf, wbuf[u ^ 1], sbuf[u ^ 1]); advance(pf, kGroups); }
         const int s = it % kGStages;
         const uint32_t ph = (it / kGStages) & 1;
-        // Loads are issued before the wait so their latency overlaps it.
-        const uint4 c0 = __ldg(reinterpret_cast<const uint4*>(wq + static_cast<int64_t>(kb) * (kGN * 32)));
-        const uint4 c1 = __ldg(reinterpret_cast<const uint4*>(wq + static_cast<int64_t>(kb) * (kGN * 32) + 16));
-        const uint32_t sc = __ldg(reinterpret_cast<const uint32_t*>(sf + static_cast<int64_t>(kb) * (kGN * 4)));
         if (*abort_flag || !mbar_wait(&empty[s], ph ^ 1)) { ok = false; break; }
         uint8_t* sb = smem + s * S::kStageBytes + S::kABytes;
-        const uint32_t w[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          const uint32_t scale2 = lut[(sc >> (8 * (c >> 1))) & 0xffu];
-          *reinterpret_cast<uint4*>(sb + swz128(row, c)) = dequant8(w[c], scale2);
+        for (int r = 0; r < kRowsPerThread; ++r) {
+          const int row = tg + r * kGroupThreads;
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const uint32_t scale2 = lut[(sbuf[u][r] >> (8 * (c >> 1))) & 0xffu];
+            *reinterpret_cast<uint4*>(sb + swz128(row, c)) = dequant8(wbuf[u][r][c], scale2);
+          }
         }
         fence_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(&full[s]);
+        it += kGroups;
+        advance(cons, kGroups);
       }
     }
     if (!ok && lane == 0) { *abort_flag = 1; report_error(p.status, MSL_ERR_DEVICE_TIMEOUT); }
@@ -316,16 +378,26 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
   __syncthreads();
   if (warp == 1) {
     __syncwarp();
-    tmem_dealloc(tmem_base, 2 * kGN);
+    tmem_dealloc(tmem_base, 2 * kSubs * kGN);
   }
 }
 
 // ---------------------------------------------------------------------------- load-time re-tiling
-// src: codes [experts, rows, k/2] (element 2i in the low nibble of byte i), scales [experts, rows,
-// k/16].  dst tiles of 256 rows x 64 k; with `interleave` (gate/up bank, rows = 2 * inter) tile j
-// holds gate rows [128 j, 128 j + 128) then up rows inter + [128 j, 128 j + 128).  Rows beyond the
-// source are zero codes / zero scales.  Within each 32-bit word the eight codes are reordered so
-// nibble j holds element 2j and nibble j+4 element 2j+1.  Lossless: a permutation of the input.
+// src: codes [banks, rows, k/2] (element 2i in the low nibble of byte i), scales [banks, rows, k/16].
+// dst tiles of 128 rows x 64 k; with `interleave` (gate/up bank, rows = 2 * inter) tile j holds gate
+// rows [64 j, 64 j + 64) then up rows inter + [64 j, 64 j + 64).  Rows beyond the source are zero
+// codes / zero scales.  Within each 32-bit word (8 consecutive k) the codes are re-placed bit by bit
+// as dequant8 expects.  Lossless: a permutation of the input bits.
+__device__ __forceinline__ uint32_t place_code(uint32_t code, int j) {
+  const uint32_t mag = code & 7u, sgn = code >> 3;
+  switch (j) {
+    case 0: return (mag << 6) | (sgn << 15);
+    case 1: return (mag << 3) | (sgn << 12);
+    case 2: return mag | (sgn << 9);
+    default: return ((code & 1u) << 10) | (((code >> 1) & 1u) << 11) | (((code >> 2) & 1u) << 13) | (sgn << 14);
+  }
+}
+
 __global__ void nvfp4_repack_kernel(const uint8_t* __restrict__ src_q, const uint8_t* __restrict__ src_sf,
                                     uint8_t* __restrict__ dst_q, uint8_t* __restrict__ dst_sf, int experts, int rows,
                                     int k, int n_pad, int interleave) {
@@ -342,8 +414,8 @@ __global__ void nvfp4_repack_kernel(const uint8_t* __restrict__ src_q, const uin
     const int e = static_cast<int>(q / n_tiles);
     int src_row;
     if (interleave) {
-      const int gi = nt * 128 + (r & 127);
-      src_row = gi < inter ? (r < 128 ? gi : inter + gi) : -1;
+      const int gi = nt * (kGN / 2) + (r & (kGN / 2 - 1));
+      src_row = gi < inter ? (r < kGN / 2 ? gi : inter + gi) : -1;
     } else {
       src_row = nt * kGN + r;
       if (src_row >= rows) src_row = -1;
@@ -353,13 +425,10 @@ __global__ void nvfp4_repack_kernel(const uint8_t* __restrict__ src_q, const uin
     if (src_row >= 0) {
       const uint8_t* sq = src_q + (static_cast<int64_t>(e) * rows + src_row) * (k / 2) + kb * 32;
       for (int w = 0; w < 8; ++w) {
-        uint32_t in = 0;
-        for (int b = 0; b < 4; ++b) in |= static_cast<uint32_t>(sq[w * 4 + b]) << (8 * b);
         uint32_t out = 0;
-        for (int el = 0; el < 8; ++el) {
-          const uint32_t code = (in >> (4 * el)) & 0xfu;
-          const int nib = (el & 1) ? 4 + el / 2 : el / 2;
-          out |= code << (4 * nib);
+        for (int b = 0; b < 4; ++b) {
+          const uint32_t byte = sq[w * 4 + b];           // elements 2b (low nibble) and 2b+1 (high nibble)
+          out |= place_code(byte & 0xfu, b) | (place_code(byte >> 4, b) << 16);
         }
         words[w] = out;
       }
@@ -379,7 +448,7 @@ using namespace msl;
 extern "C" int64_t msl_nvfp4_padded_rows(int rows, int interleave) {
   if (interleave) {
     const int inter = rows / 2;
-    return 2 * static_cast<int64_t>((inter + 127) / 128) * 128;
+    return 2 * static_cast<int64_t>((inter + kGN / 2 - 1) / (kGN / 2)) * (kGN / 2);
   }
   return static_cast<int64_t>((rows + kGN - 1) / kGN) * kGN;
 }
@@ -413,11 +482,12 @@ extern "C" int msl_grouped_gemm_nvfp4(const void* x, int64_t slab_rows, const vo
   if (slab_rows == 0) return MSL_OK;
   CUtensorMap tx;
   int rc = make_tmap_2d(&tx, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, k, slab_rows, static_cast<uint64_t>(k) * 2, kGK,
-                        kGM, CU_TENSOR_MAP_SWIZZLE_128B);
+                        kSubM, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc) return rc;
   GroupedArgs a{static_cast<const uint8_t*>(codes), static_cast<const uint8_t*>(scales), global_scales, offsets, out,
                 ld_out, experts, n_padded, k, weight_experts, n_out, swiglu, status};
   const int smem = GroupedSmem::kTotal + 1024;
+  static_assert(kSubM == 128 && 2 * kSubs * kGN <= 512, "two accumulator sets must fit the 512 TMEM columns");
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(grouped_nvfp4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)

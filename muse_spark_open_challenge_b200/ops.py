@@ -12,6 +12,7 @@ from . import _lib
 from ._lib import OUT_BF16, OUT_F32, OUT_SWIGLU_BF16, MslError, check
 
 FP8 = torch.float8_e4m3fn
+TILE_N = 256      # weight rows per tile of a re-tiled NVFP4 bank (kGN in csrc/grouped_nvfp4.cu)
 
 
 def _ptr(t):
@@ -146,8 +147,8 @@ def nvfp4_repack(codes, scales, interleave):
     n_pad = int(_lib.lib().msl_nvfp4_padded_rows(rows, int(interleave)))
     codes = codes.contiguous().view(torch.uint8)
     scales = scales.contiguous().view(torch.uint8)
-    out_q = torch.empty((e, n_pad // 256, k // 64, 256, 32), dtype=torch.uint8, device=codes.device)
-    out_s = torch.empty((e, n_pad // 256, k // 64, 256, 4), dtype=torch.uint8, device=codes.device)
+    out_q = torch.empty((e, n_pad // TILE_N, k // 64, TILE_N, 32), dtype=torch.uint8, device=codes.device)
+    out_s = torch.empty((e, n_pad // TILE_N, k // 64, TILE_N, 4), dtype=torch.uint8, device=codes.device)
     check(_lib.lib().msl_nvfp4_repack(codes.data_ptr(), scales.data_ptr(), out_q.data_ptr(), out_s.data_ptr(), e, rows,
                                       k, int(interleave), _stream()), "msl_nvfp4_repack")
     return out_q, out_s, n_pad
@@ -163,7 +164,7 @@ def grouped_gemm_nvfp4(x, codes_t, scales_t, global_scales, offsets, out, n_out,
         raise MslError("x must be contiguous")
     check(_lib.lib().msl_grouped_gemm_nvfp4(x.data_ptr(), x.shape[0], codes_t.data_ptr(), scales_t.data_ptr(),
                                             global_scales.data_ptr(), offsets.data_ptr(), out.data_ptr(),
-                                            _rows(out, "out"), offsets.numel() - 1, e, n_tiles * 256, k_blocks * 64,
+                                            _rows(out, "out"), offsets.numel() - 1, e, n_tiles * TILE_N, k_blocks * 64,
                                             n_out, int(swiglu),
                                             _ptr(status), _stream()), "msl_grouped_gemm_nvfp4")
     return out
