@@ -5,24 +5,29 @@
 // windows (:712-721) and the per-head output norm and gate (:789-802); the arithmetic follows
 // reference.py:376-409.
 //
-// One CTA per (request, KV head, block of 128/G query tokens), G = query heads per KV head: the
-// 128 MMA rows are (token, head-in-group) pairs, so one K/V tile serves all G heads.
-//   warps 0-3  softmax + correction + epilogue, one thread per row (TMEM lane = row)
-//   warp  4    TMEM allocation, tcgen05.mma issue (FP8 operands, fp32 accumulate)
-//   warps 5-8  K/V loaders: one thread per key of the 128-key tile; the key's cache row is found
-//              through the page table and copied, 16 bytes at a time, into the swizzled tile
-// Per 128-key tile: S = Q K^T (TMEM, 128 columns) -> row softmax in the exp2 domain -> P as E4M3
-// scaled by 2^8 into shared memory -> O += P V (TMEM, D columns, V consumed N-major straight from
-// its [key][d] tile).  O is rescaled in TMEM only when a row's running maximum moved.  The Q tile
-// arrives by one TMA load.  Two CTAs share an SM (TMEM 2 x (128 + D) columns), so one CTA's
-// softmax overlaps the other's MMAs.  Every wait is bounded.
+// One CTA per (request, KV head, block of 2 * 128/G query tokens), G = query heads per KV head.
+// The CTA holds two 128-row query sub-tiles (rows are (token, head-in-group) pairs), so each K/V
+// tile staged in shared memory serves 256 MMA rows.  448 threads:
+//   warps 0-3, 4-7  softmax groups of sub-tile 0 / 1: one thread per row (TMEM lane = row); row
+//                   maximum, P = exp2(s - m) as E4M3 * 2^8 into shared memory, running sum, O
+//                   rescale in TMEM only when a row maximum moved, epilogue (1/l, v_scale, optional
+//                   per-head RMS norm * sigmoid(gate)) -> bf16
+//   warp  8         TMEM allocation + tcgen05.mma issue: S_s = Q_s K^T and O_s += P_s V (FP8 operands,
+//                   fp32 accumulators in TMEM, V consumed N-major straight from its [key][d] tile),
+//                   ordered so one group's softmax overlaps the other group's MMAs
+//   warp  9         TMA: the two Q sub-tiles, and whole 128-key K/V tiles as two 64-row boxes per
+//                   tensor when the page size is a multiple of 64 and every key of the tile exists
+//   warps 10-13     gather loaders for all other tiles (any page size, ragged tail): one thread per
+//                   key, 16-byte copies into the swizzled tile, zeros for keys past the causal end
+// K/V tiles move through a 4-stage ring.  TMEM: S0 | S1 | O0 | O1 (512 columns).  Every wait is bounded.
 #include "msl_common.cuh"
 #include "msl_host.h"
 
 namespace msl {
 
-constexpr int kAM = 128;    // rows per CTA
+constexpr int kAM = 128;    // rows per query sub-tile
 constexpr int kAN = 128;    // keys per tile
+constexpr int kAStages = 4;
 
 struct AttnArgs {
   const uint8_t* k_cache;       // [cache rows][hkv][D] e4m3
@@ -45,28 +50,100 @@ struct AttnArgs {
 
 template <int D>
 struct AttnSmem {
-  static constexpr int kQ = 0;
-  static constexpr int kTile = kAN * D;                    // bytes of one K or V tile
-  static constexpr int kK = kAM * D;                       // after Q
-  static constexpr int kV = kK + 2 * kTile;
-  static constexpr int kP = kV + 2 * kTile;                // 128 x 128 bytes
-  static constexpr int kBar = kP + kAM * kAN;
-  // q_full, kv_full[2], kv_empty[2], s_full, p_full, pv_done
-  static constexpr int kTotal = kBar + 8 * 8 + 16;
+  static constexpr int kTile = kAN * D;                    // bytes of one K or V tile, and of one Q sub-tile
+  static constexpr int kQ = 0;                             // 2 sub-tiles
+  static constexpr int kP = 2 * kTile;                     // 2 x (128 x 128 bytes)
+  static constexpr int kKV = kP + 2 * kAM * kAN;           // stages of (K tile, V tile)
+  static constexpr int kBar = kKV + kAStages * 2 * kTile;
+  // q_full, kv_full[4], kv_empty[4], s_full[2], p_full[2], pv_done[2]
+  static constexpr int kNumBars = 1 + 2 * kAStages + 6;
+  static constexpr int kTotal = kBar + kNumBars * 8 + 16;
 };
 
 // Byte offset of 16-byte chunk `chunk` of row `row` in a tile with ROWB-byte rows (64 or 128) laid
 // out with the matching swizzle: the chunk index is XORed with bits of the row index so that the
-// pattern repeats every 1024 bytes (128-byte rows: row mod 8; 64-byte rows: (row / 2) mod 4).
+// pattern repeats every 1024 / 512 bytes (128-byte rows: row mod 8; 64-byte rows: (row / 2) mod 4).
 template <int ROWB>
 __device__ __forceinline__ uint32_t swz(uint32_t row, uint32_t chunk) {
   if constexpr (ROWB == 128) return row * 128u + ((chunk ^ (row & 7u)) << 4);
   else return row * 64u + ((chunk ^ ((row >> 1) & 3u)) << 4);
 }
 
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&o)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]),
+      "r"(o[8]), "r"(o[9]), "r"(o[10]), "r"(o[11]), "r"(o[12]), "r"(o[13]), "r"(o[14]), "r"(o[15]), "r"(o[16]),
+      "r"(o[17]), "r"(o[18]), "r"(o[19]), "r"(o[20]), "r"(o[21]), "r"(o[22]), "r"(o[23]), "r"(o[24]), "r"(o[25]),
+      "r"(o[26]), "r"(o[27]), "r"(o[28]), "r"(o[29]), "r"(o[30]), "r"(o[31])
+      : "memory");
+}
+
+__device__ __forceinline__ uint32_t e4m3x4(float a, float b, float c, float d) {
+  return static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3)) |
+         (static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3)) << 16);
+}
+
+// One 64-column half of a row of S: exponentials (scaled by 2^8) summed into l, written as E4M3 to
+// the row's P chunks [chunk0, chunk0 + 4).  lim_hi / lim_lo bound the visible columns (col <= lim_hi
+// and col > lim_lo) when MASKED.
+template <bool MASKED>
+__device__ __forceinline__ void softmax_half(const uint32_t (&s0)[32], const uint32_t (&s1)[32], float scale_log2,
+                                             float neg_m, int col0, int lim_hi, int lim_lo, float& l, uint8_t* p_row_base,
+                                             uint32_t r, int chunk0) {
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const uint32_t(&s)[32] = h ? s1 : s0;
+    float e[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      float x = fmaf(__uint_as_float(s[i]), scale_log2, neg_m);
+      if constexpr (MASKED) {
+        const int col = col0 + 32 * h + i;
+        if (!(col <= lim_hi && col > lim_lo)) x = -INFINITY;
+      }
+      e[i] = ex2_approx(x);
+      l += e[i];
+    }
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      const uint4 packed = make_uint4(e4m3x4(e[16 * q + 0], e[16 * q + 1], e[16 * q + 2], e[16 * q + 3]),
+                                      e4m3x4(e[16 * q + 4], e[16 * q + 5], e[16 * q + 6], e[16 * q + 7]),
+                                      e4m3x4(e[16 * q + 8], e[16 * q + 9], e[16 * q + 10], e[16 * q + 11]),
+                                      e4m3x4(e[16 * q + 12], e[16 * q + 13], e[16 * q + 14], e[16 * q + 15]));
+      *reinterpret_cast<uint4*>(p_row_base + swz<128>(r, chunk0 + 2 * h + q)) = packed;
+    }
+  }
+}
+
+template <bool MASKED>
+__device__ __forceinline__ float row_max_half(const uint32_t (&s0)[32], const uint32_t (&s1)[32], int col0, int lim_hi,
+                                              int lim_lo, float m) {
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    float a = __uint_as_float(s0[i]), b = __uint_as_float(s1[i]);
+    if constexpr (MASKED) {
+      const int ca = col0 + i, cb = col0 + 32 + i;
+      if (!(ca <= lim_hi && ca > lim_lo)) a = -INFINITY;
+      if (!(cb <= lim_hi && cb > lim_lo)) b = -INFINITY;
+    }
+    m = fmaxf(m, fmaxf(a, b));
+  }
+  return m;
+}
+
 template <int D>
-__global__ void __launch_bounds__(288, 2)
-attention_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, AttnArgs p) {
+__global__ void __launch_bounds__(448, 1)
+attention_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                     const __grid_constant__ CUtensorMap tm_v, AttnArgs p) {
   using S = AttnSmem<D>;
   constexpr uint32_t kSwz = (D == 128) ? 2u : 4u;          // descriptor swizzle code
   constexpr uint32_t kSbo = 8 * D;                         // bytes between 8-row groups
@@ -75,91 +152,157 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, AttnArgs p) {
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::kBar);
   uint64_t* q_full = bars;
   uint64_t* kv_full = bars + 1;
-  uint64_t* kv_empty = bars + 3;
-  uint64_t* s_full = bars + 5;
-  uint64_t* p_full = bars + 6;
-  uint64_t* pv_done = bars + 7;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  uint64_t* kv_empty = kv_full + kAStages;
+  uint64_t* s_full = kv_empty + kAStages;
+  uint64_t* p_full = s_full + 2;
+  uint64_t* pv_done = p_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + S::kNumBars);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = p.hq / p.hkv;
-  const int TQ = kAM / G;                                  // query tokens per CTA
+  const int TQ = kAM / G;                                  // query tokens per sub-tile
   const int b = blockIdx.z, kvh = blockIdx.y;
   const int q_begin = p.cu_seqlens_q[b], q_len = p.cu_seqlens_q[b + 1] - q_begin;
   // Longest key ranges first: later query blocks attend to more keys.
-  const int n_qblk = (q_len + TQ - 1) / TQ;
+  const int n_qblk = (q_len + 2 * TQ - 1) / (2 * TQ);
   const int qblk = n_qblk - 1 - static_cast<int>(blockIdx.x);
   if (qblk < 0) return;                                    // uniform for the CTA, before any barrier
-  const int q0 = qblk * TQ;
+  const int q0 = qblk * 2 * TQ;
   const int seq = p.seq_lens[b];
-  const int rows_valid = min(TQ, q_len - q0) * G;
-  const int max_qpos = seq + min(q0 + TQ, q_len) - 1;
   const int min_qpos = seq + q0;
-  const int kt_end = max_qpos / kAN + 1;
   const int kt_begin = p.window ? max(0, min_qpos - p.window + 1) / kAN : 0;
-  const int n_tiles = kt_end - kt_begin;
+  // per sub-tile: valid rows, last query position, number of key tiles
+  int rows_valid[2], max_qpos[2], n_sub[2];
+#pragma unroll
+  for (int s = 0; s < 2; ++s) {
+    const int first = q0 + s * TQ;
+    const int cnt = max(0, min(TQ, q_len - first));
+    rows_valid[s] = cnt * G;
+    max_qpos[s] = seq + first + cnt - 1;
+    n_sub[s] = cnt > 0 ? max_qpos[s] / kAN + 1 - kt_begin : 0;
+  }
+  const int n_tiles = max(n_sub[0], n_sub[1]);
+  const int last_qpos = max(max_qpos[0], max_qpos[1]);
+  const bool tma_pages = (p.page_size % 64) == 0;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int i = 0; i < 2; ++i) { mbar_init(&kv_full[i], 4); mbar_init(&kv_empty[i], 1); }
-    mbar_init(s_full, 1);
-    mbar_init(p_full, 4);
-    mbar_init(pv_done, 1);
+    for (int i = 0; i < kAStages; ++i) { mbar_init(&kv_full[i], 5); mbar_init(&kv_empty[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&s_full[i], 1); mbar_init(&p_full[i], 4); mbar_init(&pv_done[i], 1); }
     *abort_flag = 0;
     mbar_fence_init();
   }
-  if (warp == 4) tmem_alloc(tmem_slot, 256);               // S: columns [0,128), O: [128, 128 + D)
+  if (warp == 8) tmem_alloc(tmem_slot, 512);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 128;
 
-  if (warp == 4) {
+  // A tile goes by TMA when its pages can be addressed as two 64-row boxes and none of its keys
+  // lies past the last query (rows the cache may never have initialised must not reach the MMA).
+  auto tile_by_tma = [&](int j) { return tma_pages && (kt_begin + j) * kAN + kAN - 1 <= last_qpos; };
+
+  if (warp == 8) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      tma_prefetch_desc(&tm_q);
-      mbar_expect_tx(q_full, kAM * D);
-      tma_load_3d(smem + S::kQ, &tm_q, q_full, 0, kvh * G, q_begin + q0);
       constexpr uint32_t idesc_qk = make_idesc(0, 0, kAM, kAN);
       constexpr uint32_t idesc_pv = make_idesc(0, 0, kAM, D, 0, 1);     // B = V, N-major
-      bool ok = mbar_wait(q_full, 0);
       const uint32_t sq = smem_u32(smem + S::kQ), sp = smem_u32(smem + S::kP);
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        const int buf = j & 1;
-        const uint32_t kv_ph = (j >> 1) & 1, ph = j & 1;
-        if (*abort_flag || !mbar_wait(&kv_full[buf], kv_ph)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t sk = smem_u32(smem + S::kK + buf * S::kTile);
-        const uint32_t sv = smem_u32(smem + S::kV + buf * S::kTile);
+      auto issue_qk = [&](int s, uint32_t sk) {
 #pragma unroll
         for (int k = 0; k < D / 32; ++k)
-          tc_mma_f8(tmem_s, make_sdesc(sq + k * 32, 16, kSbo, kSwz), make_sdesc(sk + k * 32, 16, kSbo, kSwz),
-                    idesc_qk, k != 0);
-        tc_commit(s_full);
-        if (*abort_flag || !mbar_wait(p_full, ph)) { ok = false; break; }
-        tc_fence_after();
+          tc_mma_f8(tmem_base + s * kAN, make_sdesc(sq + s * S::kTile + k * 32, 16, kSbo, kSwz),
+                    make_sdesc(sk + k * 32, 16, kSbo, kSwz), idesc_qk, k != 0);
+        tc_commit(&s_full[s]);
+      };
+      auto issue_pv = [&](int s, uint32_t sv, bool first) {
 #pragma unroll
         for (int k = 0; k < kAN / 32; ++k)
-          tc_mma_f8(tmem_o, make_sdesc(sp + k * 32, 16, 1024, 2), make_sdesc(sv + k * 32 * D, 16, kSbo, kSwz),
-                    idesc_pv, (j | k) != 0);
-        tc_commit(&kv_empty[buf]);
-        tc_commit(pv_done);
+          tc_mma_f8(tmem_base + 2 * kAN + s * kAN, make_sdesc(sp + s * (kAM * kAN) + k * 32, 16, 1024, 2),
+                    make_sdesc(sv + k * 32 * D, 16, kSbo, kSwz), idesc_pv, !(first && k == 0));
+        tc_commit(&pv_done[s]);
+      };
+      bool ok = mbar_wait(q_full, 0) && mbar_wait(&kv_full[0], 0);
+      if (ok) {
+        tc_fence_after();
+        const uint32_t sk0 = smem_u32(smem + S::kKV);
+        if (n_sub[0] > 0) issue_qk(0, sk0);
+        if (n_sub[1] > 0) issue_qk(1, sk0);
+      }
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int st = j % kAStages;
+        const uint32_t ph = j & 1;
+        const uint32_t sv = smem_u32(smem + S::kKV + st * 2 * S::kTile + S::kTile);
+        const bool next = j + 1 < n_tiles;
+        const int st1 = (j + 1) % kAStages;
+        const uint32_t sk1 = smem_u32(smem + S::kKV + st1 * 2 * S::kTile);
+        if (j < n_sub[0]) {
+          if (*abort_flag || !mbar_wait(&p_full[0], ph)) { ok = false; break; }
+          tc_fence_after();
+          issue_pv(0, sv, j == 0);
+        }
+        if (next) {
+          if (*abort_flag || !mbar_wait(&kv_full[st1], ((j + 1) / kAStages) & 1)) { ok = false; break; }
+          tc_fence_after();
+          if (j + 1 < n_sub[0]) issue_qk(0, sk1);
+        }
+        if (j < n_sub[1]) {
+          if (*abort_flag || !mbar_wait(&p_full[1], ph)) { ok = false; break; }
+          tc_fence_after();
+          issue_pv(1, sv, j == 0);
+        }
+        tc_commit(&kv_empty[st]);
+        if (next && j + 1 < n_sub[1]) issue_qk(1, sk1);
       }
       if (!ok) { *abort_flag = 1; report_error(p.status, MSL_ERR_DEVICE_TIMEOUT); }
     }
-  } else if (warp >= 5) {
-    // ------------------------------------------------------------------ K/V loaders
-    const int r = threadIdx.x - 5 * 32;                    // key row of the tile
+  } else if (warp == 9) {
+    // ------------------------------------------------------------------ TMA loader
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_q);
+      tma_prefetch_desc(&tm_k);
+      tma_prefetch_desc(&tm_v);
+      const int nq = n_sub[1] > 0 ? 2 : 1;
+      mbar_expect_tx(q_full, nq * S::kTile);
+      for (int s = 0; s < nq; ++s)
+        tma_load_3d(smem + S::kQ + s * S::kTile, &tm_q, q_full, 0, kvh * G, q_begin + q0 + s * TQ);
+      const int* pt = p.page_table + static_cast<int64_t>(b) * p.max_pages;
+      bool ok = true;
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int st = j % kAStages;
+        if (*abort_flag || !mbar_wait(&kv_empty[st], ((j / kAStages) & 1) ^ 1)) { ok = false; break; }
+        if (!tile_by_tma(j)) { mbar_arrive(&kv_full[st]); continue; }
+        uint8_t* sk = smem + S::kKV + st * 2 * S::kTile;
+        mbar_expect_tx(&kv_full[st], 2 * S::kTile);
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int key0 = (kt_begin + j) * kAN + half * 64;
+          const int pg = pt[key0 / p.page_size];
+          const int row0 = pg * p.page_size + key0 % p.page_size;
+          tma_load_3d(sk + half * 64 * D, &tm_k, &kv_full[st], 0, kvh, row0);
+          tma_load_3d(sk + S::kTile + half * 64 * D, &tm_v, &kv_full[st], 0, kvh, row0);
+        }
+      }
+      if (!ok) { *abort_flag = 1; report_error(p.status, MSL_ERR_DEVICE_TIMEOUT); }
+    }
+  } else if (warp >= 10) {
+    // ------------------------------------------------------------------ gather loaders
+    const int r = threadIdx.x - 10 * 32;                   // key row of the tile
     const int* pt = p.page_table + static_cast<int64_t>(b) * p.max_pages;
     bool ok = true;
     for (int j = 0; j < n_tiles && ok; ++j) {
-      const int buf = j & 1;
-      const uint32_t kv_ph = (j >> 1) & 1;
+      const int st = j % kAStages;
+      const uint32_t e_ph = ((j / kAStages) & 1) ^ 1;
+      if (tile_by_tma(j)) {
+        if (*abort_flag || !mbar_wait(&kv_empty[st], e_ph)) { ok = false; break; }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&kv_full[st]);
+        continue;
+      }
       const int key = (kt_begin + j) * kAN + r;
       int64_t row = -1;
-      if (key <= max_qpos) {
+      if (key <= last_qpos) {
         const int pg = pt[key / p.page_size];
         if (pg >= 0) row = static_cast<int64_t>(pg) * p.page_size + key % p.page_size;
         if (row >= p.cache_rows) row = -1;
@@ -174,9 +317,9 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, AttnArgs p) {
 #pragma unroll
         for (int c = 0; c < D / 16; ++c) { kq[c] = make_uint4(0, 0, 0, 0); vq[c] = make_uint4(0, 0, 0, 0); }
       }
-      if (*abort_flag || !mbar_wait(&kv_empty[buf], kv_ph ^ 1)) { ok = false; break; }
-      uint8_t* sk = smem + S::kK + buf * S::kTile;
-      uint8_t* sv = smem + S::kV + buf * S::kTile;
+      if (*abort_flag || !mbar_wait(&kv_empty[st], e_ph)) { ok = false; break; }
+      uint8_t* sk = smem + S::kKV + st * 2 * S::kTile;
+      uint8_t* sv = sk + S::kTile;
 #pragma unroll
       for (int c = 0; c < D / 16; ++c) {
         *reinterpret_cast<uint4*>(sk + swz<D>(r, c)) = kq[c];
@@ -184,136 +327,114 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, AttnArgs p) {
       }
       fence_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&kv_full[buf]);
+      if (lane == 0) mbar_arrive(&kv_full[st]);
     }
     if (!ok && lane == 0) { *abort_flag = 1; report_error(p.status, MSL_ERR_DEVICE_TIMEOUT); }
   } else {
     // ------------------------------------------------------------------ softmax / correction / epilogue
-    const int r = warp * 32 + lane;                        // row = TMEM lane
+    const int sub = warp >> 2;                             // query sub-tile of this group
+    const int r = (warp & 3) * 32 + lane;                  // row = TMEM lane
+    const int n_mine = n_sub[sub];
     const int tq = r / G, g = r - tq * G;
-    const bool row_valid = r < rows_valid;
-    const int qpos = seq + min(q0 + tq, q_len - 1);
+    const bool row_valid = r < rows_valid[sub];
+    const int first_tok = q0 + sub * TQ;
+    const int qpos = seq + min(first_tok + tq, max(q_len - 1, 0));
+    const int sub_min_qpos = seq + first_tok;
     const float scale_log2 = p.softmax_scale * (*p.k_scale) * 1.4426950408889634f;
-    const uint32_t lane_sel = static_cast<uint32_t>(warp * 32) << 16;
-    float m_run = -INFINITY, l_run = 0.f;
+    const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t tmem_s = tmem_base + sub * kAN + lane_sel;
+    const uint32_t tmem_o = tmem_base + 2 * kAN + sub * kAN + lane_sel;
+    uint8_t* sp = smem + S::kP + sub * (kAM * kAN);
+    float m_run = -INFINITY, l_run = 0.f;                  // l accumulates 2^8 * sum of exponentials
     bool ok = true;
-    uint8_t* sp = smem + S::kP;
-    for (int j = 0; j < n_tiles && ok; ++j) {
+    for (int j = 0; j < n_mine && ok; ++j) {
       const uint32_t ph = j & 1;
       const int key0 = (kt_begin + j) * kAN;
-      if (*abort_flag || !mbar_wait(s_full, ph)) { ok = false; break; }
+      if (*abort_flag || !mbar_wait(&s_full[sub], ph)) { ok = false; break; }
       tc_fence_after();
-      const bool full_tile = (key0 + kAN - 1 <= min_qpos) && (!p.window || key0 > max_qpos - p.window);
-      const int lo_key = p.window ? qpos - p.window : -1;   // visible keys: lo_key < key <= qpos
-      // pass 1: row maximum
+      const bool full_tile =
+          (key0 + kAN - 1 <= sub_min_qpos) && (!p.window || key0 > max_qpos[sub] - p.window);
+      const int lim_hi = qpos - key0;                       // visible columns: lim_lo < col <= lim_hi
+      const int lim_lo = p.window ? qpos - p.window - key0 : -1;
+      // pass 1: row maximum of the raw scores
       float m_tile = -INFINITY;
 #pragma unroll 1
-      for (int c = 0; c < kAN; c += 32) {
-        uint32_t s[32];
-        tmem_ld32(tmem_s + lane_sel + c, s);
+      for (int c = 0; c < kAN; c += 64) {
+        uint32_t s0[32], s1[32];
+        tmem_ld32(tmem_s + c, s0);
+        tmem_ld32(tmem_s + c + 32, s1);
         tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int key = key0 + c + i;
-          const bool vis = full_tile || (key <= qpos && key > lo_key);
-          if (vis) m_tile = fmaxf(m_tile, __uint_as_float(s[i]));
-        }
+        m_tile = full_tile ? row_max_half<false>(s0, s1, c, lim_hi, lim_lo, m_tile)
+                           : row_max_half<true>(s0, s1, c, lim_hi, lim_lo, m_tile);
       }
       const float m_new = fmaxf(m_run, m_tile * scale_log2);
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      const float corr = exp2f(m_run - m_use);               // 0 when m_run = -inf
+      const float corr = ex2_approx(m_run - m_use);         // 0 when m_run = -inf
       m_run = m_new;
       // The previous tile's P V must have finished before O is rescaled or P overwritten.
       if (j > 0) {
-        if (*abort_flag || !mbar_wait(pv_done, (j - 1) & 1)) { ok = false; break; }
+        if (*abort_flag || !mbar_wait(&pv_done[sub], (j - 1) & 1)) { ok = false; break; }
         tc_fence_after();
         if (__any_sync(0xffffffffu, corr != 1.0f)) {
 #pragma unroll 1
           for (int c = 0; c < D; c += 32) {
             uint32_t o[32];
-            tmem_ld32(tmem_o + lane_sel + c, o);
+            tmem_ld32(tmem_o + c, o);
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
-            asm volatile(
-                "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-                "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-                "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
-                ::"r"(tmem_o + lane_sel + c), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]), "r"(o[4]), "r"(o[5]),
-                "r"(o[6]), "r"(o[7]), "r"(o[8]), "r"(o[9]), "r"(o[10]), "r"(o[11]), "r"(o[12]), "r"(o[13]),
-                "r"(o[14]), "r"(o[15]), "r"(o[16]), "r"(o[17]), "r"(o[18]), "r"(o[19]), "r"(o[20]), "r"(o[21]),
-                "r"(o[22]), "r"(o[23]), "r"(o[24]), "r"(o[25]), "r"(o[26]), "r"(o[27]), "r"(o[28]), "r"(o[29]),
-                "r"(o[30]), "r"(o[31])
-                : "memory");
+            tmem_st32(tmem_o + c, o);
           }
           asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         }
       }
       l_run *= corr;
-      // pass 2: P = exp2(s - m) as E4M3 scaled by 2^8, row sum in fp32
+      // pass 2: P = 2^8 * exp2(s * scale - m) as E4M3, row sum in fp32
+      const float neg_m = 8.0f - m_use;
       float l_tile = 0.f;
 #pragma unroll 1
-      for (int c = 0; c < kAN; c += 32) {
-        uint32_t s[32];
-        tmem_ld32(tmem_s + lane_sel + c, s);
+      for (int c = 0; c < kAN; c += 64) {
+        uint32_t s0[32], s1[32];
+        tmem_ld32(tmem_s + c, s0);
+        tmem_ld32(tmem_s + c + 32, s1);
         tmem_ld_wait();
-        float pv[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int key = key0 + c + i;
-          const bool vis = full_tile || (key <= qpos && key > lo_key);
-          const float e = vis ? exp2f(__uint_as_float(s[i]) * scale_log2 - m_use) : 0.f;
-          l_tile += e;
-          pv[i] = e * 256.0f;
-        }
-#pragma unroll
-        for (int q = 0; q < 2; ++q) {
-          const uint4 packed = make_uint4(
-              __nv_cvt_float2_to_fp8x2(make_float2(pv[16 * q + 0], pv[16 * q + 1]), __NV_SATFINITE, __NV_E4M3) |
-                  (__nv_cvt_float2_to_fp8x2(make_float2(pv[16 * q + 2], pv[16 * q + 3]), __NV_SATFINITE, __NV_E4M3) << 16),
-              __nv_cvt_float2_to_fp8x2(make_float2(pv[16 * q + 4], pv[16 * q + 5]), __NV_SATFINITE, __NV_E4M3) |
-                  (__nv_cvt_float2_to_fp8x2(make_float2(pv[16 * q + 6], pv[16 * q + 7]), __NV_SATFINITE, __NV_E4M3) << 16),
-              __nv_cvt_float2_to_fp8x2(make_float2(pv[16 * q + 8], pv[16 * q + 9]), __NV_SATFINITE, __NV_E4M3) |
-                  (__nv_cvt_float2_to_fp8x2(make_float2(pv[16 * q + 10], pv[16 * q + 11]), __NV_SATFINITE, __NV_E4M3) << 16),
-              __nv_cvt_float2_to_fp8x2(make_float2(pv[16 * q + 12], pv[16 * q + 13]), __NV_SATFINITE, __NV_E4M3) |
-                  (__nv_cvt_float2_to_fp8x2(make_float2(pv[16 * q + 14], pv[16 * q + 15]), __NV_SATFINITE, __NV_E4M3) << 16));
-          *reinterpret_cast<uint4*>(sp + swz<128>(r, c / 16 + q)) = packed;
-        }
+        if (full_tile) softmax_half<false>(s0, s1, scale_log2, neg_m, c, lim_hi, lim_lo, l_tile, sp, r, c / 16);
+        else softmax_half<true>(s0, s1, scale_log2, neg_m, c, lim_hi, lim_lo, l_tile, sp, r, c / 16);
       }
       l_run += l_tile;
       tc_fence_before();
       fence_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_full);
+      if (lane == 0) mbar_arrive(&p_full[sub]);
     }
     // ---------------------------------------------------------------- epilogue
-    if (ok && n_tiles > 0) {
-      if (*abort_flag || !mbar_wait(pv_done, (n_tiles - 1) & 1)) ok = false;
+    if (ok && n_mine > 0) {
+      if (*abort_flag || !mbar_wait(&pv_done[sub], (n_mine - 1) & 1)) ok = false;
     }
-    if (ok && n_tiles > 0) {
+    if (ok && n_mine > 0) {
       tc_fence_after();
-      const float c_out = (*p.v_scale) / (256.0f * l_run);
+      const float c_out = (*p.v_scale) / l_run;             // l_run carries the 2^8 of P
       float r_norm = 1.0f;
       if (p.gate != nullptr) {
         float ss = 0.f;
 #pragma unroll 1
         for (int c = 0; c < D; c += 32) {
           uint32_t o[32];
-          tmem_ld32(tmem_o + lane_sel + c, o);
+          tmem_ld32(tmem_o + c, o);
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 32; ++i) { const float v = __uint_as_float(o[i]) * c_out; ss += v * v; }
         }
         r_norm = 1.0f / sqrtf(ss / D + 1e-5f);
       }
-      const int token = q_begin + q0 + tq;
+      const int token = q_begin + first_tok + tq;
       const int head = kvh * G + g;
       __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<int64_t>(token) * p.ld_out + head * D;
       const __nv_bfloat16* grow = p.gate ? p.gate + static_cast<int64_t>(token) * p.ld_gate + head * D : nullptr;
 #pragma unroll 1
       for (int c = 0; c < D; c += 32) {
         uint32_t o[32];
-        tmem_ld32(tmem_o + lane_sel + c, o);
+        tmem_ld32(tmem_o + c, o);
         tmem_ld_wait();
         if (row_valid) {
           float v[32];
@@ -343,17 +464,18 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, AttnArgs p) {
     if (!ok && lane == 0) { *abort_flag = 1; report_error(p.status, MSL_ERR_DEVICE_TIMEOUT); }
   }
 
-  if (warp == 4 && lane == 0 && *abort_flag) drain_pause();
+  if (warp == 9 && lane == 0 && *abort_flag) drain_pause();
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == 8) {
     __syncwarp();
-    tmem_dealloc(tmem_base, 256);
+    tmem_dealloc(tmem_base, 512);
   }
 }
 
 template <int D>
-static int launch_attention(const CUtensorMap& tq, const AttnArgs& a, int batch, int max_q_len, cudaStream_t st) {
+static int launch_attention(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnArgs& a,
+                            int batch, int max_q_len, cudaStream_t st) {
   using S = AttnSmem<D>;
   const int smem = S::kTotal + 1024;
   static bool configured = false;
@@ -363,9 +485,9 @@ static int launch_attention(const CUtensorMap& tq, const AttnArgs& a, int batch,
       return MSL_ERR_CUDA;
     configured = true;
   }
-  const int G = a.hq / a.hkv, TQ = kAM / G;
-  dim3 grid((max_q_len + TQ - 1) / TQ, a.hkv, batch);
-  attention_fp8_kernel<D><<<grid, 288, smem, st>>>(tq, a);
+  const int G = a.hq / a.hkv, TQ2 = 2 * (kAM / G);
+  dim3 grid((max_q_len + TQ2 - 1) / TQ2, a.hkv, batch);
+  attention_fp8_kernel<D><<<grid, 448, smem, st>>>(tq, tk, tv, a);
   return cudaGetLastError() == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
 }
 
@@ -382,10 +504,11 @@ extern "C" int msl_attention_fp8(const void* q8, const void* k_cache, const void
   if (!q8 || !k_cache || !v_cache || !page_table || !seq_lens || !cu_seqlens_q || !k_scale || !v_scale || !out)
     return MSL_ERR_ARG;
   if (batch <= 0 || max_q_len <= 0 || tokens <= 0 || hq <= 0 || hkv <= 0 || hq % hkv || page_size <= 0 ||
-      window < 0 || max_pages <= 0)
+      window < 0 || max_pages <= 0 || cache_rows <= 0)
     return MSL_ERR_ARG;
   const int G = hq / hkv;
   if (G > 128 || (G & (G - 1))) return MSL_ERR_UNSUPPORTED;
+  if (head_dim != 64 && head_dim != 128) return MSL_ERR_UNSUPPORTED;
   if ((reinterpret_cast<uintptr_t>(q8) & 15) || (reinterpret_cast<uintptr_t>(k_cache) & 15) ||
       (reinterpret_cast<uintptr_t>(v_cache) & 15) || (reinterpret_cast<uintptr_t>(out) & 15) || (ld_out & 7) ||
       (gate && ((reinterpret_cast<uintptr_t>(gate) & 15) || (ld_gate & 7))))
@@ -393,21 +516,20 @@ extern "C" int msl_attention_fp8(const void* q8, const void* k_cache, const void
   AttnArgs a{static_cast<const uint8_t*>(k_cache), static_cast<const uint8_t*>(v_cache), page_table, max_pages,
              seq_lens, cu_seqlens_q, k_scale, v_scale, softmax_scale, hq, hkv, page_size, window, cache_rows, out,
              ld_out, static_cast<const __nv_bfloat16*>(gate), ld_gate, status};
-  CUtensorMap tq;
+  CUtensorMap tq, tk, tv;
   const uint32_t box_t = static_cast<uint32_t>(kAM / G);
-  int rc;
+  const uint64_t d = static_cast<uint64_t>(head_dim);
+  const CUtensorMapSwizzle swz_mode = head_dim == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+  int rc = make_tmap_3d(&tq, q8, CU_TENSOR_MAP_DATA_TYPE_UINT8, d, hq, tokens, d, hq * d, head_dim, G, box_t, swz_mode);
+  if (rc) return rc;
+  // K/V caches as [rows][hkv][d]: one box = 64 consecutive cache rows of one KV head.
+  rc = make_tmap_3d(&tk, k_cache, CU_TENSOR_MAP_DATA_TYPE_UINT8, d, hkv, cache_rows, d, hkv * d, head_dim, 1, 64,
+                    swz_mode);
+  if (rc) return rc;
+  rc = make_tmap_3d(&tv, v_cache, CU_TENSOR_MAP_DATA_TYPE_UINT8, d, hkv, cache_rows, d, hkv * d, head_dim, 1, 64,
+                    swz_mode);
+  if (rc) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (head_dim == 128) {
-    rc = make_tmap_3d(&tq, q8, CU_TENSOR_MAP_DATA_TYPE_UINT8, 128, hq, tokens, 128, static_cast<uint64_t>(hq) * 128,
-                      128, G, box_t, CU_TENSOR_MAP_SWIZZLE_128B);
-    if (rc) return rc;
-    return launch_attention<128>(tq, a, batch, max_q_len, st);
-  }
-  if (head_dim == 64) {
-    rc = make_tmap_3d(&tq, q8, CU_TENSOR_MAP_DATA_TYPE_UINT8, 64, hq, tokens, 64, static_cast<uint64_t>(hq) * 64, 64,
-                      G, box_t, CU_TENSOR_MAP_SWIZZLE_64B);
-    if (rc) return rc;
-    return launch_attention<64>(tq, a, batch, max_q_len, st);
-  }
-  return MSL_ERR_UNSUPPORTED;
+  return head_dim == 128 ? launch_attention<128>(tq, tk, tv, a, batch, max_q_len, st)
+                         : launch_attention<64>(tq, tk, tv, a, batch, max_q_len, st);
 }
