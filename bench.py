@@ -141,6 +141,105 @@ def cpu_baseline_leg():
                       f"{os.cpu_count()} threads"}
 
 
+def time_steps(fn, steps, warmup):
+    for _ in range(max(warmup, 3)):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def run_attention_op(args):
+    """BASELINE config 1: attention only, 8 causal prefills of seeded uniform lengths 512-4096,
+    32 q / 8 kv heads x 128, FP8 Q/K/V, kv_scale 1/64, 64-token pages, BF16 out.  --small: 2 x 2048."""
+    from muse_spark_open_challenge_b200 import ops, synth
+    dev = torch.device("cuda", 0)
+    shape = synth.MID
+    lens = [2048, 2048] if args.small else synth.uniform_lengths(8, 512, 4096, seed=0)
+    data = synth.make_input(shape, lens, [0] * len(lens), seed=1, page=64, kv_scale=1 / 64, device=dev)
+    cfg = data["config"]
+    t = cfg["tokens"]
+    q = torch.randn((t, shape.hq, shape.head_dim), generator=torch.Generator(device=dev).manual_seed(2), device=dev)
+    q8 = (q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True))).to(torch.float8_e4m3fn)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    out = torch.empty((t, shape.q_size), dtype=torch.bfloat16, device=dev)
+
+    def step():
+        ops.attention(q8, data["k_cache"], data["v_cache"], data["page_table"], data["seq_lens"], data["cu_seqlens_q"],
+                      data["k_scale"], data["v_scale"], cfg["sm_scale"] * cfg["qk_scale_factor"], cfg["batch"],
+                      cfg["q_len"], shape.hq, shape.hkv, shape.head_dim, 64, 0, out=out, status=status)
+
+    sampler = ClockSampler(0)
+    sampler.start()
+    ms = time_steps(step, args.steps, args.warmup)
+    clocks = sampler.stop()
+    assert int(status.item()) == 0
+    flops = 4.0 * shape.hq * shape.head_dim * sum(n * (n + 1) / 2 for n in lens)
+    pk = peaks()
+    achieved = flops / (ms * 1e-3) / 1e12
+    print(json.dumps({
+        "metric": "attention prefill tokens/s (op only)", "value": t / (ms * 1e-3), "unit": UNIT, "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+        "dtype": "fp8 e4m3 Q/K/V, fp32 softmax, bf16 out", "data": "synthetic",
+        "config": {"workload": "attention only (BASELINE config 1)" + (" --small" if args.small else ""),
+                   "lengths": lens},
+        "roofline": {"kernel": "attention_fp8_kernel<128>", "bound": "tensor", "achieved": achieved,
+                     "peak": 2 * pk["tflops"], "unit": "TFLOP/s", "frac": achieved / (2 * pk["tflops"]), "traffic": None,
+                     "peak_source": "2 x " + pk["source"] + " (FP8 runs at twice the bf16 rate; no FP8 peak was measured)"},
+        "gpu_launches": args.steps, "clocks": clocks}))
+
+
+def run_moe_op(args):
+    """BASELINE config 2: MoE only, 16384 BF16 tokens, hidden 4096, 128 experts, sigmoid router with
+    fp32 bias ~ N(0, 0.1), top-8, intermediate 1536 NVFP4, router skewed so per-expert counts follow
+    Zipf(1.1) clipped at 3000 with two empty experts.  --small: 2048 tokens, 16 experts."""
+    import dataclasses
+    from muse_spark_open_challenge_b200 import layer, synth
+    dev = torch.device("cuda", 0)
+    shape = synth.MOE_ONLY
+    tokens = 16384
+    if args.small:
+        shape, tokens = dataclasses.replace(shape, n_experts=16, local_experts=16), 2048
+    weights = synth.make_weights(shape, seed=0, device=dev, router_bias_std=0.1)
+    g = torch.Generator(device=dev).manual_seed(1)
+    h = torch.randn((tokens, shape.hidden), generator=g, device=dev).to(torch.bfloat16)
+    targets = synth.zipf_targets(shape.n_experts, tokens * shape.top_k, s=1.1, cap=3000 if not args.small else tokens,
+                                 n_empty=2)
+    synth.skew_router(weights, h, targets, shape.top_k)
+    st = layer.prepare(weights)
+    data = {"config": synth.config_of(shape, 1, tokens, tokens, 64, 1.0),
+            "local_start": torch.zeros(1, dtype=torch.int32, device=dev)}
+    ms = time_steps(lambda: layer.moe_stage(h, data, st), args.steps, args.warmup)
+    layer.check_status(st)
+    st["marks"] = []
+    layer._mark(st, "begin")
+    layer.moe_stage(h, data, st)
+    torch.cuda.synchronize()
+    stages = dict(layer.stage_times_ms(st["marks"]))
+    counts = st["counts"].cpu()
+    routes = int(counts.sum())
+    flops = 2.0 * routes * 3 * shape.moe_width * shape.inter
+    pk = peaks()
+    gu = 2.0 * routes * 2 * shape.inter * shape.moe_width / (stages["experts_gate_up"] * 1e-3) / 1e12
+    print(json.dumps({
+        "metric": "MoE block tokens/s (op only)", "value": tokens / (ms * 1e-3), "unit": UNIT, "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+        "dtype": "bf16 activations, NVFP4 weights (W4A16)", "data": "synthetic",
+        "config": {"workload": "MoE only (BASELINE config 2)" + (" --small" if args.small else ""),
+                   "expert_counts": {"min": int(counts.min()), "max": int(counts.max()),
+                                     "empty": int((counts == 0).sum()), "sorted_top8": counts.sort().values[-8:].tolist()}},
+        "moe_tflops": flops / (ms * 1e-3) / 1e12, "stage_ms": {k: round(v, 4) for k, v in stages.items()},
+        "roofline": {"kernel": "grouped_nvfp4_kernel (gate/up + SiLU*up)", "bound": "tensor", "achieved": gu,
+                     "peak": pk["tflops"], "unit": "TFLOP/s", "frac": gu / pk["tflops"], "traffic": None,
+                     "peak_source": pk["source"]},
+        "gpu_launches": 6 * args.steps}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -148,9 +247,16 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="layer", choices=["layer", "attn", "moe"],
+                    help="layer = the headline full-layer step; attn / moe = the op-only configurations")
+    ap.add_argument("--small", action="store_true", help="reduced op workload, sized for an ncu capture")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.workload == "attn":
+        return run_attention_op(args)
+    if args.workload == "moe":
+        return run_moe_op(args)
 
     from muse_spark_open_challenge_b200 import _lib, layer
     rank = int(os.environ.get("RANK", "0"))

@@ -7,7 +7,7 @@
 //
 // One CTA per (request, KV head, block of 2 * 128/G query tokens), G = query heads per KV head.
 // The CTA holds two 128-row query sub-tiles (rows are (token, head-in-group) pairs), so each K/V
-// tile staged in shared memory serves 256 MMA rows.  448 threads:
+// tile staged in shared memory serves 256 MMA rows.  384 threads:
 //   warps 0-3, 4-7  softmax groups of sub-tile 0 / 1: one thread per row (TMEM lane = row); row
 //                   maximum, P = exp2(s - m) as E4M3 * 2^8 into shared memory, running sum, O
 //                   rescale in TMEM only when a row maximum moved, epilogue (1/l, v_scale, optional
@@ -17,8 +17,8 @@
 //                   ordered so one group's softmax overlaps the other group's MMAs
 //   warp  9         TMA: the two Q sub-tiles, and whole 128-key K/V tiles as two 64-row boxes per
 //                   tensor when the page size is a multiple of 64 and every key of the tile exists
-//   warps 10-13     gather loaders for all other tiles (any page size, ragged tail): one thread per
-//                   key, 16-byte copies into the swizzled tile, zeros for keys past the causal end
+//   warps 10-11     gather loaders for all other tiles (any page size, ragged tail): two keys per
+//                   thread, 16-byte copies into the swizzled tile, zeros for keys past the causal end
 // K/V tiles move through a 4-stage ring.  TMEM: S0 | S1 | O0 | O1 (512 columns).  Every wait is bounded.
 #include "msl_common.cuh"
 #include "msl_host.h"
@@ -55,8 +55,8 @@ struct AttnSmem {
   static constexpr int kP = 2 * kTile;                     // 2 x (128 x 128 bytes)
   static constexpr int kKV = kP + 2 * kAM * kAN;           // stages of (K tile, V tile)
   static constexpr int kBar = kKV + kAStages * 2 * kTile;
-  // q_full, kv_full[4], kv_empty[4], s_full[2], p_full[2], pv_done[2]
-  static constexpr int kNumBars = 1 + 2 * kAStages + 6;
+  // q_full, kv_full[4], kv_empty[4], s_full[2], s_free[2], p_full[2], pv_done[2]
+  static constexpr int kNumBars = 1 + 2 * kAStages + 8;
   static constexpr int kTotal = kBar + kNumBars * 8 + 16;
 };
 
@@ -127,6 +127,7 @@ __device__ __forceinline__ void softmax_half(const uint32_t (&s0)[32], const uin
 template <bool MASKED>
 __device__ __forceinline__ float row_max_half(const uint32_t (&s0)[32], const uint32_t (&s1)[32], int col0, int lim_hi,
                                               int lim_lo, float m) {
+  float acc[4] = {m, -INFINITY, -INFINITY, -INFINITY};     // independent chains
 #pragma unroll
   for (int i = 0; i < 32; ++i) {
     float a = __uint_as_float(s0[i]), b = __uint_as_float(s1[i]);
@@ -135,13 +136,13 @@ __device__ __forceinline__ float row_max_half(const uint32_t (&s0)[32], const ui
       if (!(ca <= lim_hi && ca > lim_lo)) a = -INFINITY;
       if (!(cb <= lim_hi && cb > lim_lo)) b = -INFINITY;
     }
-    m = fmaxf(m, fmaxf(a, b));
+    acc[i & 3] = fmaxf(acc[i & 3], fmaxf(a, b));
   }
-  return m;
+  return fmaxf(fmaxf(acc[0], acc[1]), fmaxf(acc[2], acc[3]));
 }
 
 template <int D>
-__global__ void __launch_bounds__(448, 1)
+__global__ void __launch_bounds__(384, 1)
 attention_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CUtensorMap tm_v, AttnArgs p) {
   using S = AttnSmem<D>;
@@ -154,7 +155,8 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   uint64_t* kv_full = bars + 1;
   uint64_t* kv_empty = kv_full + kAStages;
   uint64_t* s_full = kv_empty + kAStages;
-  uint64_t* p_full = s_full + 2;
+  uint64_t* s_free = s_full + 2;
+  uint64_t* p_full = s_free + 2;
   uint64_t* pv_done = p_full + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + S::kNumBars);
   volatile uint32_t* abort_flag = tmem_slot + 1;
@@ -188,8 +190,13 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int i = 0; i < kAStages; ++i) { mbar_init(&kv_full[i], 5); mbar_init(&kv_empty[i], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&s_full[i], 1); mbar_init(&p_full[i], 4); mbar_init(&pv_done[i], 1); }
+    for (int i = 0; i < kAStages; ++i) { mbar_init(&kv_full[i], 3); mbar_init(&kv_empty[i], 1); }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s_full[i], 1);
+      mbar_init(&s_free[i], 4);
+      mbar_init(&p_full[i], 4);
+      mbar_init(&pv_done[i], 1);
+    }
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -230,30 +237,38 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         if (n_sub[0] > 0) issue_qk(0, sk0);
         if (n_sub[1] > 0) issue_qk(1, sk0);
       }
+      // Per tile j: as soon as a group has copied S(j) into registers its S columns are free, so
+      // Q K^T of tile j+1 is issued while that group still works on the softmax of tile j; P V of
+      // tile j follows when the group has published P(j).
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int st = j % kAStages;
         const uint32_t ph = j & 1;
         const uint32_t sv = smem_u32(smem + S::kKV + st * 2 * S::kTile + S::kTile);
-        const bool next = j + 1 < n_tiles;
-        const int st1 = (j + 1) % kAStages;
-        const uint32_t sk1 = smem_u32(smem + S::kKV + st1 * 2 * S::kTile);
-        if (j < n_sub[0]) {
-          if (*abort_flag || !mbar_wait(&p_full[0], ph)) { ok = false; break; }
-          tc_fence_after();
-          issue_pv(0, sv, j == 0);
-        }
-        if (next) {
+        if (j + 1 < n_tiles) {
+          const int st1 = (j + 1) % kAStages;
+          const uint32_t sk1 = smem_u32(smem + S::kKV + st1 * 2 * S::kTile);
           if (*abort_flag || !mbar_wait(&kv_full[st1], ((j + 1) / kAStages) & 1)) { ok = false; break; }
           tc_fence_after();
-          if (j + 1 < n_sub[0]) issue_qk(0, sk1);
+#pragma unroll
+          for (int s = 0; s < 2; ++s) {
+            if (j + 1 < n_sub[s]) {
+              if (*abort_flag || !mbar_wait(&s_free[s], ph)) { ok = false; break; }
+              tc_fence_after();
+              issue_qk(s, sk1);
+            }
+          }
+          if (!ok) break;
         }
-        if (j < n_sub[1]) {
-          if (*abort_flag || !mbar_wait(&p_full[1], ph)) { ok = false; break; }
-          tc_fence_after();
-          issue_pv(1, sv, j == 0);
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+          if (j < n_sub[s]) {
+            if (*abort_flag || !mbar_wait(&p_full[s], ph)) { ok = false; break; }
+            tc_fence_after();
+            issue_pv(s, sv, j == 0);
+          }
         }
+        if (!ok) break;
         tc_commit(&kv_empty[st]);
-        if (next && j + 1 < n_sub[1]) issue_qk(1, sk1);
       }
       if (!ok) { *abort_flag = 1; report_error(p.status, MSL_ERR_DEVICE_TIMEOUT); }
     }
@@ -271,7 +286,7 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       bool ok = true;
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int st = j % kAStages;
-        if (*abort_flag || !mbar_wait(&kv_empty[st], ((j / kAStages) & 1) ^ 1)) { ok = false; break; }
+        if (*abort_flag || !mbar_wait(&kv_empty[st], ((j / kAStages) & 1) ^ 1, true)) { ok = false; break; }
         if (!tile_by_tma(j)) { mbar_arrive(&kv_full[st]); continue; }
         uint8_t* sk = smem + S::kKV + st * 2 * S::kTile;
         mbar_expect_tx(&kv_full[st], 2 * S::kTile);
@@ -288,42 +303,48 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     }
   } else if (warp >= 10) {
     // ------------------------------------------------------------------ gather loaders
-    const int r = threadIdx.x - 10 * 32;                   // key row of the tile
+    const int r0 = threadIdx.x - 10 * 32;                  // key rows r0 and r0 + 64 of the tile
     const int* pt = p.page_table + static_cast<int64_t>(b) * p.max_pages;
     bool ok = true;
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int st = j % kAStages;
       const uint32_t e_ph = ((j / kAStages) & 1) ^ 1;
       if (tile_by_tma(j)) {
-        if (*abort_flag || !mbar_wait(&kv_empty[st], e_ph)) { ok = false; break; }
+        if (*abort_flag || !mbar_wait(&kv_empty[st], e_ph, true)) { ok = false; break; }
         __syncwarp();
         if (lane == 0) mbar_arrive(&kv_full[st]);
         continue;
       }
-      const int key = (kt_begin + j) * kAN + r;
-      int64_t row = -1;
-      if (key <= last_qpos) {
-        const int pg = pt[key / p.page_size];
-        if (pg >= 0) row = static_cast<int64_t>(pg) * p.page_size + key % p.page_size;
-        if (row >= p.cache_rows) row = -1;
-      }
-      uint4 kq[D / 16], vq[D / 16];
-      if (row >= 0) {
-        const uint4* ks = reinterpret_cast<const uint4*>(p.k_cache + (row * p.hkv + kvh) * D);
-        const uint4* vs = reinterpret_cast<const uint4*>(p.v_cache + (row * p.hkv + kvh) * D);
+      uint4 kq[2][D / 16], vq[2][D / 16];
 #pragma unroll
-        for (int c = 0; c < D / 16; ++c) { kq[c] = ks[c]; vq[c] = vs[c]; }
-      } else {
+      for (int h = 0; h < 2; ++h) {
+        const int key = (kt_begin + j) * kAN + r0 + 64 * h;
+        int64_t row = -1;
+        if (key <= last_qpos) {
+          const int pg = pt[key / p.page_size];
+          if (pg >= 0) row = static_cast<int64_t>(pg) * p.page_size + key % p.page_size;
+          if (row >= p.cache_rows) row = -1;
+        }
+        if (row >= 0) {
+          const uint4* ks = reinterpret_cast<const uint4*>(p.k_cache + (row * p.hkv + kvh) * D);
+          const uint4* vs = reinterpret_cast<const uint4*>(p.v_cache + (row * p.hkv + kvh) * D);
 #pragma unroll
-        for (int c = 0; c < D / 16; ++c) { kq[c] = make_uint4(0, 0, 0, 0); vq[c] = make_uint4(0, 0, 0, 0); }
+          for (int c = 0; c < D / 16; ++c) { kq[h][c] = ks[c]; vq[h][c] = vs[c]; }
+        } else {
+#pragma unroll
+          for (int c = 0; c < D / 16; ++c) { kq[h][c] = make_uint4(0, 0, 0, 0); vq[h][c] = make_uint4(0, 0, 0, 0); }
+        }
       }
-      if (*abort_flag || !mbar_wait(&kv_empty[st], e_ph)) { ok = false; break; }
+      if (*abort_flag || !mbar_wait(&kv_empty[st], e_ph, true)) { ok = false; break; }
       uint8_t* sk = smem + S::kKV + st * 2 * S::kTile;
       uint8_t* sv = sk + S::kTile;
 #pragma unroll
-      for (int c = 0; c < D / 16; ++c) {
-        *reinterpret_cast<uint4*>(sk + swz<D>(r, c)) = kq[c];
-        *reinterpret_cast<uint4*>(sv + swz<D>(r, c)) = vq[c];
+      for (int h = 0; h < 2; ++h) {
+#pragma unroll
+        for (int c = 0; c < D / 16; ++c) {
+          *reinterpret_cast<uint4*>(sk + swz<D>(r0 + 64 * h, c)) = kq[h][c];
+          *reinterpret_cast<uint4*>(sv + swz<D>(r0 + 64 * h, c)) = vq[h][c];
+        }
       }
       fence_async_smem();
       __syncwarp();
@@ -356,16 +377,24 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           (key0 + kAN - 1 <= sub_min_qpos) && (!p.window || key0 > max_qpos[sub] - p.window);
       const int lim_hi = qpos - key0;                       // visible columns: lim_lo < col <= lim_hi
       const int lim_lo = p.window ? qpos - p.window - key0 : -1;
+      // The whole row of S (128 columns) is read from TMEM once and stays in registers for both passes.
+      uint32_t sa[32], sb[32], sc[32], sd[32];
+      tmem_ld32(tmem_s, sa);
+      tmem_ld32(tmem_s + 32, sb);
+      tmem_ld32(tmem_s + 64, sc);
+      tmem_ld32(tmem_s + 96, sd);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_free[sub]);            // S(j) is in registers: its TMEM columns may be overwritten
       // pass 1: row maximum of the raw scores
       float m_tile = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < kAN; c += 64) {
-        uint32_t s0[32], s1[32];
-        tmem_ld32(tmem_s + c, s0);
-        tmem_ld32(tmem_s + c + 32, s1);
-        tmem_ld_wait();
-        m_tile = full_tile ? row_max_half<false>(s0, s1, c, lim_hi, lim_lo, m_tile)
-                           : row_max_half<true>(s0, s1, c, lim_hi, lim_lo, m_tile);
+      if (full_tile) {
+        m_tile = row_max_half<false>(sa, sb, 0, lim_hi, lim_lo, m_tile);
+        m_tile = row_max_half<false>(sc, sd, 64, lim_hi, lim_lo, m_tile);
+      } else {
+        m_tile = row_max_half<true>(sa, sb, 0, lim_hi, lim_lo, m_tile);
+        m_tile = row_max_half<true>(sc, sd, 64, lim_hi, lim_lo, m_tile);
       }
       const float m_new = fmaxf(m_run, m_tile * scale_log2);
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
@@ -377,29 +406,27 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         tc_fence_after();
         if (__any_sync(0xffffffffu, corr != 1.0f)) {
 #pragma unroll 1
-          for (int c = 0; c < D; c += 32) {
-            uint32_t o[32];
-            tmem_ld32(tmem_o + c, o);
+          for (int c = 0; c < D; c += 16) {
+            uint32_t o[16];
+            tmem_ld16(tmem_o + c, o);
             tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
-            tmem_st32(tmem_o + c, o);
+            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
+            tmem_st16(tmem_o + c, o);
           }
-          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+          tmem_st_wait();
         }
       }
       l_run *= corr;
       // pass 2: P = 2^8 * exp2(s * scale - m) as E4M3, row sum in fp32
       const float neg_m = 8.0f - m_use;
       float l_tile = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < kAN; c += 64) {
-        uint32_t s0[32], s1[32];
-        tmem_ld32(tmem_s + c, s0);
-        tmem_ld32(tmem_s + c + 32, s1);
-        tmem_ld_wait();
-        if (full_tile) softmax_half<false>(s0, s1, scale_log2, neg_m, c, lim_hi, lim_lo, l_tile, sp, r, c / 16);
-        else softmax_half<true>(s0, s1, scale_log2, neg_m, c, lim_hi, lim_lo, l_tile, sp, r, c / 16);
+      if (full_tile) {
+        softmax_half<false>(sa, sb, scale_log2, neg_m, 0, lim_hi, lim_lo, l_tile, sp, r, 0);
+        softmax_half<false>(sc, sd, scale_log2, neg_m, 64, lim_hi, lim_lo, l_tile, sp, r, 4);
+      } else {
+        softmax_half<true>(sa, sb, scale_log2, neg_m, 0, lim_hi, lim_lo, l_tile, sp, r, 0);
+        softmax_half<true>(sc, sd, scale_log2, neg_m, 64, lim_hi, lim_lo, l_tile, sp, r, 4);
       }
       l_run += l_tile;
       tc_fence_before();
@@ -487,7 +514,7 @@ static int launch_attention(const CUtensorMap& tq, const CUtensorMap& tk, const 
   }
   const int G = a.hq / a.hkv, TQ2 = 2 * (kAM / G);
   dim3 grid((max_q_len + TQ2 - 1) / TQ2, a.hkv, batch);
-  attention_fp8_kernel<D><<<grid, 448, smem, st>>>(tq, tk, tv, a);
+  attention_fp8_kernel<D><<<grid, 384, smem, st>>>(tq, tk, tv, a);
   return cudaGetLastError() == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
 }
 

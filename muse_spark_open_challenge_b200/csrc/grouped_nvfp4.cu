@@ -230,7 +230,7 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % kGStages;
           const uint32_t ph = (it / kGStages) & 1;
-          if (*abort_flag || !mbar_wait(&empty[s], ph ^ 1)) { ok = false; break; }
+          if (*abort_flag || !mbar_wait(&empty[s], ph ^ 1, true)) { ok = false; break; }
           mbar_expect_tx(&full[s], nsub * S::kSubBytes);
           for (int sub = 0; sub < nsub; ++sub)
             tma_load_2d(smem + s * S::kStageBytes + sub * S::kSubBytes, &tm_x, &full[s], kb * kGK,
@@ -324,8 +324,9 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
       while (c.kb >= k_blocks && c.g < total_tiles) { c.kb -= k_blocks; c.g += gridDim.x; moved = true; }
       if (moved) seek(c);
     };
-    uint32_t wbuf[2][kRowsPerThread][8];
-    uint32_t sbuf[2][kRowsPerThread];
+    constexpr int kBufs = 3;                   // register sets: the current stage and two in flight
+    uint32_t wbuf[kBufs][kRowsPerThread][8];
+    uint32_t sbuf[kBufs][kRowsPerThread];
     auto fetch = [&](const Cursor& c, uint32_t (&w)[kRowsPerThread][8], uint32_t (&sc)[kRowsPerThread]) {
 #pragma unroll
       for (int r = 0; r < kRowsPerThread; ++r) {
@@ -342,14 +343,19 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
     seek(cons);
     advance(cons, gid);
     Cursor pf = cons;
-    if (pf.g < total_tiles) { fetch(pf, wbuf[0], sbuf[0]); advance(pf, kGroups); }
+#pragma unroll
+    for (int u = 0; u < kBufs - 1; ++u)
+      if (pf.g < total_tiles) { fetch(pf, wbuf[u], sbuf[u]); advance(pf, kGroups); }
     uint32_t it = gid;
     bool ok = true;
     while (cons.g < total_tiles && ok) {
 #pragma unroll
-      for (int u = 0; u < 2; ++u) {
+      for (int u = 0; u < kBufs; ++u) {
         if (cons.g >= total_tiles) break;
-        if (pf.g < total_tiles) { fetch(pf, wbuf[u ^ 1], sbuf[u ^ 1]); advance(pf, kGroups); }
+        if (pf.g < total_tiles) {
+          fetch(pf, wbuf[(u + kBufs - 1) % kBufs], sbuf[(u + kBufs - 1) % kBufs]);
+          advance(pf, kGroups);
+        }
         const int s = it % kGStages;
         const uint32_t ph = (it / kGStages) & 1;
         if (*abort_flag || !mbar_wait(&empty[s], ph ^ 1)) { ok = false; break; }

@@ -35,18 +35,39 @@ class ExchangePlan:
         return sum(self.recv_splits)
 
 
-def make_plan(counts: torch.Tensor, world: int, group=None) -> ExchangePlan:
-    """counts: i32 [E] routes of this rank per global expert (rows of the send slab are ordered by
-    expert).  One all-to-all of the counts tells every rank what it will receive."""
+def begin_plan(counts: torch.Tensor, world: int, group=None):
+    """First half of the plan: the counts all-to-all and an asynchronous copy of the split sizes to
+    the host.  counts: i32 [E] routes of this rank per global expert (rows of the send slab are
+    ordered by expert).  Returns the pending pieces for `finish_plan`."""
     e = counts.numel()
     local = e // world
     mat = counts.view(world, local).contiguous()
     recv = torch.empty_like(mat)
     dist.all_to_all_single(recv, mat, group=group)
-    both = torch.stack([mat.sum(1), recv.sum(1)]).cpu()          # the one host synchronisation
+    both = torch.stack([mat.sum(1), recv.sum(1)])
     offs = torch.zeros(world * local + 1, dtype=torch.int32, device=counts.device)
     offs[1:] = torch.cumsum(recv.flatten(), 0).to(torch.int32)
-    return ExchangePlan(both[0].tolist(), both[1].tolist(), recv, offs)
+    if both.is_cuda:
+        host = torch.empty(both.shape, dtype=both.dtype, pin_memory=True)
+        host.copy_(both, non_blocking=True)
+        done = torch.cuda.Event()
+        done.record()
+    else:
+        host, done = both, None
+    return host, done, recv, offs
+
+
+def finish_plan(pending) -> ExchangePlan:
+    """Second half: wait (on the host) for the split sizes only."""
+    host, done, recv, offs = pending
+    if done is not None:
+        done.synchronize()                   # the one host synchronisation of the layer
+    return ExchangePlan(host[0].tolist(), host[1].tolist(), recv, offs)
+
+
+def make_plan(counts: torch.Tensor, world: int, group=None) -> ExchangePlan:
+    """One all-to-all of the counts tells every rank what it will receive."""
+    return finish_plan(begin_plan(counts, world, group))
 
 
 def exchange_rows(send: torch.Tensor, out_rows: int, send_splits, recv_splits, out=None, group=None):
@@ -71,6 +92,7 @@ class ExpertParallel:
         self.send_offsets = torch.zeros(n_experts + 1, dtype=torch.int32, device=st["device"])
         self.cap = 0
         self.recv_x = self.recv_i = None
+        self.side = torch.cuda.Stream(st["device"]) if torch.device(st["device"]).type == "cuda" else None
 
     def buffers(self, st, rows):
         if rows > self.cap:
@@ -101,7 +123,19 @@ def moe_stage(h, data, st, ctx: ExpertParallel):
     else:
         rowmap = ops.dispatch(h, None, local_ids, slots, ctx.counts, send_x, ctx.send_offsets, status)
     layer._mark(st, "dispatch")
-    plan = make_plan(ctx.counts, ctx.world, ctx.group)
+    # The split sizes travel to the host on a side stream while the main stream computes the shared
+    # expert, which does not depend on the routing: the host wait does not drain the main stream.
+    main = torch.cuda.current_stream()
+    ctx.side.wait_stream(main)
+    with torch.cuda.stream(ctx.side):
+        pending = begin_plan(ctx.counts, ctx.world, ctx.group)
+    shared = None
+    if st["shared"]:
+        s_inter = ops.gemm(h, st["shared_w13"], out_mode=OUT_SWIGLU_BF16, status=status)
+        shared = ops.gemm(s_inter, st["shared_w2"], status=status)
+        layer._mark(st, "shared_expert")
+    plan = finish_plan(pending)
+    main.wait_stream(ctx.side)
     recv_x, recv_i = ctx.buffers(st, max(plan.recv_rows, 1))
     exchange_rows(send_x, plan.recv_rows, plan.send_splits, plan.recv_splits, out=recv_x, group=ctx.group)
     layer._mark(st, "a2a_dispatch")
@@ -116,11 +150,6 @@ def moe_stage(h, data, st, ctx: ExpertParallel):
     exchange_rows(recv_x[:plan.recv_rows], tokens * top_k, plan.recv_splits, plan.send_splits, out=send_x,
                   group=ctx.group)
     layer._mark(st, "a2a_combine")
-    shared = None
-    if st["shared"]:
-        s_inter = ops.gemm(h, st["shared_w13"], out_mode=OUT_SWIGLU_BF16, status=status)
-        shared = ops.gemm(s_inter, st["shared_w2"], status=status)
-        layer._mark(st, "shared_expert")
     moe = ops.combine(send_x, rowmap, tw, st["w_post_exp"], addend=shared)
     layer._mark(st, "combine")
     if st["pooled"]:
