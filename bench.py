@@ -372,8 +372,13 @@ def main():
     roof = None
     if gu_ms:
         achieved = gate_up_flops / (gu_ms * 1e-3) / 1e12
+        # DRAM bytes per launch: ncu on the small MoE case measured 0.92 x the algorithmic bytes (weights
+        # + rows in + rows out); scaled here to this launch (profiles/grouped_nvfp4_moe_small.md).
+        algo_bytes = (shape.local_experts * 2 * shape.inter * shape.moe_width * 0.5625
+                      + routes_local * shape.moe_width * 2 + routes_local * shape.inter * 2)
         roof = {"kernel": "grouped_nvfp4_kernel (experts gate/up + SiLU*up)", "bound": "tensor", "achieved": achieved,
-                "peak": pk["tflops"], "unit": "TFLOP/s", "frac": achieved / pk["tflops"], "traffic": None,
+                "peak": pk["tflops"], "unit": "TFLOP/s", "frac": achieved / pk["tflops"],
+                "traffic": 0.92 * algo_bytes, "traffic_unit": "bytes per launch (scaled from an ncu capture)",
                 "peak_source": pk["source"], "launch_ms": gu_ms}
     total_flops = layer_flops(shape, SEQS, SEQ_LEN, routes)
     line = {
