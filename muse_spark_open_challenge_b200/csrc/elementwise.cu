@@ -351,58 +351,73 @@ dispatch_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, const float* _
 // ============================================================================ weighted combine
 // out[t] = sum_j w[t, j] * rms(y[rowmap[t, j]] * post_w, eps 1e-8)  (+ addend[t]); routes with
 // rowmap < 0 (another rank's expert) contribute nothing (reference.py:427-444).
-// One block per token; every thread owns one 8-channel chunk of every route's row.  The raw 16-byte
-// loads of all routes are issued first and kept in registers across the block-wide sum of squares,
-// so each row crosses HBM exactly once.
+// One block per token.  The token's routed rows are copied global -> shared memory with 16-byte
+// asynchronous copies (no registers held while they are in flight, so several blocks per SM keep
+// enough bytes outstanding), then read twice from shared memory: once for the sums of squares,
+// once for the weighted accumulation.  Each row crosses HBM exactly once.
 template <int MAXK>
-__global__ void __launch_bounds__(512, 2)
+__global__ void __launch_bounds__(512)
 combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ rowmap, const float* __restrict__ w,
                const float* __restrict__ post_w, const __nv_bfloat16* __restrict__ addend, int64_t ld_add,
                __nv_bfloat16* __restrict__ out, int64_t ld_out, int top_k, int width) {
+  extern __shared__ __align__(16) uint8_t rows_smem[];      // [top_k][width] bf16
   __shared__ float scratch[32 * MAXK];
   const int t = blockIdx.x;
-  const int ch = threadIdx.x;
-  const bool live = ch < width / 8;
-  uint32_t valid = 0;                      // bit j: route j has a slab row
-  uint4 raw[MAXK];
-#pragma unroll
-  for (int j = 0; j < MAXK; ++j) {
-    const int row = j < top_k ? rowmap[t * top_k + j] : -1;
-    raw[j] = make_uint4(0, 0, 0, 0);
+  const int chunks = width / 8;
+  uint32_t valid = 0;                                       // bit j: route j has a slab row
+  for (int j = 0; j < top_k; ++j) {
+    const int row = rowmap[t * top_k + j];
     if (row >= 0) {
       valid |= 1u << j;
-      if (live) raw[j] = __ldcs(reinterpret_cast<const uint4*>(y + static_cast<int64_t>(row) * width + ch * 8));
+      const __nv_bfloat16* src = y + static_cast<int64_t>(row) * width;
+      for (int ch = threadIdx.x; ch < chunks; ch += blockDim.x) {
+        const uint32_t dst = smem_u32(rows_smem + (static_cast<size_t>(j) * width + ch * 8) * 2);
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src + ch * 8) : "memory");
+      }
     }
   }
-  float pw[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-  if (live) {
-    const float4 w0 = *reinterpret_cast<const float4*>(post_w + ch * 8);
-    const float4 w1 = *reinterpret_cast<const float4*>(post_w + ch * 8 + 4);
-    pw[0] = w0.x; pw[1] = w0.y; pw[2] = w0.z; pw[3] = w0.w; pw[4] = w1.x; pw[5] = w1.y; pw[6] = w1.z; pw[7] = w1.w;
-    if (addend != nullptr) unpack8(*reinterpret_cast<const uint4*>(addend + t * ld_add + ch * 8), acc);
-  }
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  __syncthreads();
   float ss[MAXK];
 #pragma unroll
-  for (int j = 0; j < MAXK; ++j) {
-    float v[8];
-    unpack8(raw[j], v);
-    ss[j] = 0.f;
+  for (int j = 0; j < MAXK; ++j) ss[j] = 0.f;
+  for (int ch = threadIdx.x; ch < chunks; ch += blockDim.x) {
+    const float4 w0 = *reinterpret_cast<const float4*>(post_w + ch * 8);
+    const float4 w1 = *reinterpret_cast<const float4*>(post_w + ch * 8 + 4);
+    const float pw[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
-    for (int i = 0; i < 8; ++i) { const float x = v[i] * pw[i]; ss[j] += x * x; }
-  }
-  block_sum<MAXK>(ss, scratch);
+    for (int j = 0; j < MAXK; ++j) {
+      if (valid & (1u << j)) {
+        float v[8];
+        unpack8(*reinterpret_cast<const uint4*>(rows_smem + (static_cast<size_t>(j) * width + ch * 8) * 2), v);
 #pragma unroll
-  for (int j = 0; j < MAXK; ++j) {
-    if (valid & (1u << j)) {
-      const float r = w[t * top_k + j] / sqrtf(ss[j] / width + 1e-8f);
-      float v[8];
-      unpack8(raw[j], v);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) acc[i] += v[i] * pw[i] * r;
+        for (int i = 0; i < 8; ++i) { const float x = v[i] * pw[i]; ss[j] += x * x; }
+      }
     }
   }
-  if (live) *reinterpret_cast<uint4*>(out + t * ld_out + ch * 8) = pack8(acc);
+  block_sum<MAXK>(ss, scratch);
+  float r[MAXK];
+#pragma unroll
+  for (int j = 0; j < MAXK; ++j)
+    r[j] = (valid & (1u << j)) ? w[t * top_k + j] / sqrtf(ss[j] / width + 1e-8f) : 0.f;
+  for (int ch = threadIdx.x; ch < chunks; ch += blockDim.x) {
+    const float4 w0 = *reinterpret_cast<const float4*>(post_w + ch * 8);
+    const float4 w1 = *reinterpret_cast<const float4*>(post_w + ch * 8 + 4);
+    const float pw[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (addend != nullptr) unpack8(*reinterpret_cast<const uint4*>(addend + t * ld_add + ch * 8), acc);
+#pragma unroll
+    for (int j = 0; j < MAXK; ++j) {
+      if (valid & (1u << j)) {
+        float v[8];
+        unpack8(*reinterpret_cast<const uint4*>(rows_smem + (static_cast<size_t>(j) * width + ch * 8) * 2), v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] += v[i] * pw[i] * r[j];
+      }
+    }
+    *reinterpret_cast<uint4*>(out + t * ld_out + ch * 8) = pack8(acc);
+  }
 }
 
 }  // namespace msl
@@ -511,17 +526,25 @@ extern "C" int msl_combine(const void* y, const int* rowmap, const float* weight
   if (!y || !rowmap || !weights || !post_w || !out) return MSL_ERR_ARG;
   if (tokens < 0 || top_k <= 0 || top_k > 8 || width <= 0) return MSL_ERR_ARG;
   if ((width & 7) || (ld_out & 7) || (ld_addend & 7)) return MSL_ERR_ALIGN;
-  if (width > 8 * 512) return MSL_ERR_UNSUPPORTED;
+  if (static_cast<int64_t>(top_k) * width * 2 > 200 * 1024) return MSL_ERR_UNSUPPORTED;   // rows staged in smem
   if (tokens == 0) return MSL_OK;
-  const int threads = ((width / 8 + 31) / 32) * 32;
+  const int threads = std::min(512, ((width / 8 + 31) / 32) * 32);
+  const int smem = top_k * width * 2;
+  static int configured = 0;       // largest dynamic shared-memory size set so far
+  if (smem > 48 * 1024 && smem > configured) {
+    if (cudaFuncSetAttribute(combine_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
+        cudaFuncSetAttribute(combine_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+      return MSL_ERR_CUDA;
+    configured = smem;
+  }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   auto* yy = static_cast<const __nv_bfloat16*>(y);
   auto* ad = static_cast<const __nv_bfloat16*>(addend);
   auto* oo = static_cast<__nv_bfloat16*>(out);
   if (top_k <= 4)
-    combine_kernel<4><<<tokens, threads, 0, st>>>(yy, rowmap, weights, post_w, ad, ld_addend, oo, ld_out, top_k, width);
+    combine_kernel<4><<<tokens, threads, smem, st>>>(yy, rowmap, weights, post_w, ad, ld_addend, oo, ld_out, top_k, width);
   else
-    combine_kernel<8><<<tokens, threads, 0, st>>>(yy, rowmap, weights, post_w, ad, ld_addend, oo, ld_out, top_k, width);
+    combine_kernel<8><<<tokens, threads, smem, st>>>(yy, rowmap, weights, post_w, ad, ld_addend, oo, ld_out, top_k, width);
   return cudaGetLastError() == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
 }
 

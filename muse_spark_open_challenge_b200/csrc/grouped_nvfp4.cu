@@ -25,43 +25,47 @@
 // 15|8 7|6 is the bf16 number value * 2^-126 (also for the subnormal codes 0 and 0.5); the block
 // scale is looked up as bf16(scale * 2^118); one bf16x2 multiply gives value * scale * 2^-8
 // exactly (at most 6 significant bits), and the 2^8 is folded into the epilogue scale.
+#include <cstdlib>
+
 #include "msl_common.cuh"
 #include "msl_host.h"
 
 namespace msl {
 
-constexpr int kSubM = 128;     // rows of one MMA (TMEM lanes)
-constexpr int kSubs = 1;       // activation sub-tiles (MMAs) sharing one dequantised B tile
-constexpr int kGM = kSubM * kSubs;
+constexpr int kSubM = 128;     // rows of one CTA's MMA share (TMEM lanes)
 constexpr int kGN = 256;       // weight rows per tile: N = 256 keeps the MMA operand fetch per FLOP low
-constexpr int kProducers = 256;               // weight-producer threads
+constexpr int kGK = 64;        // k per stage
+constexpr int kMaxLocal = 256; // row groups per call
+constexpr int kProducers = 256;               // weight-producer threads per CTA
 constexpr int kGroups = 2;                    // producer groups, each taking every kGroups-th stage
 constexpr int kGroupThreads = kProducers / kGroups;
-constexpr int kRowsPerThread = kGN / kGroupThreads;   // weight rows (64 codes each) per thread per stage
-constexpr int kGK = 64;        // k per stage
-constexpr int kGStages = 4;
-constexpr int kMaxLocal = 256; // row groups per call
 
-struct GroupedSmem {
-  static constexpr int kSubBytes = kSubM * kGK * 2;
-  static constexpr int kABytes = kSubs * kSubBytes;
-  static constexpr int kBBytes = kGN * kGK * 2;
+// PAIR = two CTAs of a cluster run one M=256 x N=256 MMA (cta_group::2): each CTA stages its own 128
+// token rows and dequantises only its 128 of the tile's 256 weight rows.
+template <bool PAIR>
+struct GroupedCfg {
+  static constexpr int kTileM = PAIR ? 256 : 128;            // token rows per tile
+  static constexpr int kBRows = PAIR ? 128 : 256;            // weight rows dequantised per CTA per stage
+  static constexpr int kStages = PAIR ? 6 : 4;
+  static constexpr int kRowsPerThread = kBRows / kGroupThreads;
+  static constexpr int kABytes = kSubM * kGK * 2;
+  static constexpr int kBBytes = kBRows * kGK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kLutOffset = kGStages * kStageBytes;          // 256 x u32
+  static constexpr int kLutOffset = kStages * kStageBytes;           // 256 x u32
   static constexpr int kPrefixOffset = kLutOffset + 1024;            // (kMaxLocal + 1) x int
   static constexpr int kBarOffset = kPrefixOffset + (kMaxLocal + 1) * 4 + 4;
-  static constexpr int kTotal = kBarOffset + (2 * kGStages + 4) * 8 + 16;
+  static constexpr int kTotal = kBarOffset + (2 * kStages + 4) * 8 + 16;
+  static_assert(kBarOffset % 8 == 0, "barriers must be 8-byte aligned");
 };
-static_assert(GroupedSmem::kBarOffset % 8 == 0, "barriers must be 8-byte aligned");
 
 struct GroupedArgs {
-  const uint8_t* wq;       // [banks][n_tiles][k_blocks][128 rows][32 bytes]
-  const uint8_t* sf;       // [banks][n_tiles][k_blocks][128 rows][4 bytes]
+  const uint8_t* wq;       // [banks][n_tiles][k_blocks][256 rows][32 bytes]
+  const uint8_t* sf;       // [banks][n_tiles][k_blocks][256 rows][4 bytes]
   const float* gs;         // [banks]
   const int* offsets;      // [groups + 1] slab row ranges
   void* out;
   int64_t ld_out;
-  int experts, n, k;       // experts = row groups; n = padded weight rows (multiple of 128), k multiple of 64
+  int experts, n, k;       // experts = row groups; n = padded weight rows (multiple of 256), k multiple of 64
   int wexperts;            // weight banks: group g uses bank g % wexperts
   int n_out;               // valid output columns (after the SwiGLU halving when fused)
   int swiglu;
@@ -69,13 +73,13 @@ struct GroupedArgs {
 };
 
 struct TileInfo {
-  int expert, row0, rows, nt;   // row group, first slab row, valid rows in the tile (<= 256), n tile
+  int expert, row0, rows, nt;   // row group, first slab row, valid rows in the tile, n tile
 };
 
 __device__ __forceinline__ TileInfo decode_tile(int g, const int* mt_prefix, const int* offsets, int experts,
-                                                int n_tiles) {
-  // mt_prefix[e] = number of 256-row tiles of the groups before e.  Tiles of one (group, n tile)
-  // are adjacent so the weight tile they share stays in L2.
+                                                int n_tiles, int tile_m) {
+  // mt_prefix[e] = number of row tiles of the groups before e.  Tiles of one (group, n tile) are
+  // adjacent so the weight tile they share stays in L2.
   int lo = 0, hi = experts - 1;
   while (lo < hi) {
     const int mid = (lo + hi + 1) >> 1;
@@ -88,8 +92,8 @@ __device__ __forceinline__ TileInfo decode_tile(int g, const int* mt_prefix, con
   const int start = offsets[e], cnt = offsets[e + 1] - start;
   TileInfo ti;
   ti.expert = e;
-  ti.row0 = start + mt * kGM;
-  ti.rows = min(kGM, cnt - mt * kGM);
+  ti.row0 = start + mt * tile_m;
+  ti.rows = min(tile_m, cnt - mt * tile_m);
   ti.nt = nt;
   return ti;
 }
@@ -154,16 +158,18 @@ __device__ __forceinline__ void store_rows(const GroupedArgs& p, const TileInfo&
   }
 }
 
+template <bool PAIR>
 __global__ void __launch_bounds__(448, 1)
 grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
-  using S = GroupedSmem;
+  using S = GroupedCfg<PAIR>;
+  constexpr int kStages = S::kStages;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint32_t* lut = reinterpret_cast<uint32_t*>(smem + S::kLutOffset);
   int* mt_prefix = reinterpret_cast<int*>(smem + S::kPrefixOffset);
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + S::kBarOffset);
-  uint64_t* empty = full + kGStages;
-  uint64_t* tmem_full = empty + kGStages;
+  uint64_t* empty = full + kStages;
+  uint64_t* tmem_full = empty + kStages;
   uint64_t* tmem_empty = tmem_full + 2;
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
   volatile uint32_t* abort_flag = tmem_base_slot + 1;
@@ -172,6 +178,9 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
   const int lane = threadIdx.x & 31;
   const int n_tiles = p.n / kGN;
   const int k_blocks = p.k / kGK;
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;        // 0 = the CTA that issues the MMAs
+  const int worker = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  const int n_workers = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
 
   // Scale table: e4m3 byte -> bf16(scale * 2^118) in both halves.  (0x7f / 0xff are NaN codes.)
   for (int i = threadIdx.x; i < 256; i += blockDim.x) {
@@ -183,11 +192,11 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
     lut[i] = b | (b << 16);
   }
   if (warp == 0) {
-    // prefix of 256-row tile counts per row group, one warp
+    // prefix of row-tile counts per row group, one warp
     int carry = 0;
     for (int b0 = 0; b0 < p.experts; b0 += 32) {
       const int i = b0 + lane;
-      const int c = i < p.experts ? (p.offsets[i + 1] - p.offsets[i] + kGM - 1) / kGM : 0;
+      const int c = i < p.experts ? (p.offsets[i + 1] - p.offsets[i] + S::kTileM - 1) / S::kTileM : 0;
       int inc = c;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
@@ -200,100 +209,114 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
     if (lane == 0) mt_prefix[p.experts] = carry;
   }
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kGStages; ++s) {
-      mbar_init(&full[s], 1 + kGroupThreads / 32);   // TMA producer's expect_tx arrival + one weight-producer group
+    // full: one expect_tx arrival per CTA's TMA lane + the warps of one producer group per CTA
+    // (with PAIR both CTAs arrive on the leader's barrier); tmem_empty: 4 epilogue warps per CTA.
+    constexpr int kCtas = PAIR ? 2 : 1;
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full[s], kCtas * (1 + kGroupThreads / 32));
       mbar_init(&empty[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tmem_full[a], 1);
-      mbar_init(&tmem_empty[a], 4);
+      mbar_init(&tmem_empty[a], kCtas * 4);
     }
     *abort_flag = 0;
     mbar_fence_init();
   }
-  if (warp == 1) tmem_alloc(tmem_base_slot, 2 * kSubs * kGN);
+  if (warp == 1) {
+    if constexpr (PAIR) tmem_alloc_pair(tmem_base_slot, 2 * kGN);
+    else tmem_alloc(tmem_base_slot, 2 * kGN);
+  }
   tc_fence_before();
-  __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();
+  else __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_slot;
   const int total_tiles = mt_prefix[p.experts] * n_tiles;
 
   if (warp == 0) {
-    // ------------------------------------------------------------ TMA producer: activation sub-tiles
+    // ------------------------------------------------------------ TMA producer: this CTA's 128 token rows
     if (lane == 0) {
       tma_prefetch_desc(&tm_x);
       uint32_t it = 0;
       bool ok = true;
-      for (int g = blockIdx.x; g < total_tiles && ok; g += gridDim.x) {
-        const TileInfo ti = decode_tile(g, mt_prefix, p.offsets, p.experts, n_tiles);
-        const int nsub = (ti.rows + kSubM - 1) / kSubM;
+      for (int g = worker; g < total_tiles && ok; g += n_workers) {
+        const TileInfo ti = decode_tile(g, mt_prefix, p.offsets, p.experts, n_tiles, S::kTileM);
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-          const int s = it % kGStages;
-          const uint32_t ph = (it / kGStages) & 1;
-          if (*abort_flag || !mbar_wait(&empty[s], ph ^ 1, true)) { ok = false; break; }
-          mbar_expect_tx(&full[s], nsub * S::kSubBytes);
-          for (int sub = 0; sub < nsub; ++sub)
-            tma_load_2d(smem + s * S::kStageBytes + sub * S::kSubBytes, &tm_x, &full[s], kb * kGK,
-                        ti.row0 + sub * kSubM);
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1;
+          if (*abort_flag || !mbar_wait(&empty[s], ph ^ 1)) { ok = false; break; }
+          if constexpr (PAIR) {
+            const uint32_t bar = map_to_cta(smem_u32(&full[s]), 0);
+            mbar_expect_tx_cluster(bar, S::kABytes);
+            tma_load_2d_pair(smem + s * S::kStageBytes, &tm_x, bar, kb * kGK, ti.row0 + rank * kSubM);
+          } else {
+            mbar_expect_tx(&full[s], S::kABytes);
+            tma_load_2d(smem + s * S::kStageBytes, &tm_x, &full[s], kb * kGK, ti.row0);
+          }
         }
       }
       if (!ok) { *abort_flag = 1; report_error(p.status, MSL_ERR_DEVICE_TIMEOUT); }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(1, 1, kSubM, kGN);
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = make_idesc(1, 1, S::kTileM, kGN);
       uint32_t it = 0, tile_i = 0;
       bool ok = true;
-      for (int g = blockIdx.x; g < total_tiles && ok; g += gridDim.x, ++tile_i) {
-        const TileInfo ti = decode_tile(g, mt_prefix, p.offsets, p.experts, n_tiles);
-        const int nsub = (ti.rows + kSubM - 1) / kSubM;
+      for (int g = worker; g < total_tiles && ok; g += n_workers, ++tile_i) {
         const uint32_t acc = tile_i & 1, acc_ph = (tile_i >> 1) & 1;
         if (*abort_flag || !mbar_wait(&tmem_empty[acc], acc_ph ^ 1)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * (kSubs * kGN);
+        const uint32_t d_tmem = tmem_base + acc * kGN;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-          const int s = it % kGStages;
-          const uint32_t ph = (it / kGStages) & 1;
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1;
           if (*abort_flag || !mbar_wait(&full[s], ph)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + s * S::kStageBytes);
           const uint32_t sb = sa + S::kABytes;
 #pragma unroll
           for (int k16 = 0; k16 < kGK / 16; ++k16) {
-            const uint64_t db = make_sdesc(sb + k16 * 32, 16, 1024, 2);
-            for (int sub = 0; sub < nsub; ++sub)
-              tc_mma_f16(d_tmem + sub * kGN, make_sdesc(sa + sub * S::kSubBytes + k16 * 32, 16, 1024, 2), db, idesc,
-                         (kb | k16) != 0);
+            const uint64_t da = make_sdesc(sa + k16 * 32, 16, 1024, 2), db = make_sdesc(sb + k16 * 32, 16, 1024, 2);
+            if constexpr (PAIR) tc_mma_f16_pair(d_tmem, da, db, idesc, (kb | k16) != 0);
+            else tc_mma_f16(d_tmem, da, db, idesc, (kb | k16) != 0);
           }
-          tc_commit(&empty[s]);
+          if constexpr (PAIR) tc_commit_pair(&empty[s]);
+          else tc_commit(&empty[s]);
         }
-        if (ok) tc_commit(&tmem_full[acc]);
+        if (ok) {
+          if constexpr (PAIR) tc_commit_pair(&tmem_full[acc]);
+          else tc_commit(&tmem_full[acc]);
+        }
       }
       if (!ok) { *abort_flag = 1; report_error(p.status, MSL_ERR_DEVICE_TIMEOUT); }
     }
   } else if (warp < 6) {
-    // ------------------------------------------------------------ epilogue
+    // ------------------------------------------------------------ epilogue: this CTA's 128 rows
     const int quarter = warp & 3;
     uint32_t tile_i = 0;
     bool ok = true;
-    for (int g = blockIdx.x; g < total_tiles && ok; g += gridDim.x, ++tile_i) {
-      const TileInfo ti = decode_tile(g, mt_prefix, p.offsets, p.experts, n_tiles);
-      const int nsub = (ti.rows + kSubM - 1) / kSubM;
+    for (int g = worker; g < total_tiles && ok; g += n_workers, ++tile_i) {
+      TileInfo ti = decode_tile(g, mt_prefix, p.offsets, p.experts, n_tiles, S::kTileM);
+      ti.row0 += rank * kSubM;
+      ti.rows = max(0, min(kSubM, ti.rows - static_cast<int>(rank) * kSubM));
       const uint32_t acc = tile_i & 1, acc_ph = (tile_i >> 1) & 1;
       if (*abort_flag || !mbar_wait(&tmem_full[acc], acc_ph)) { ok = false; break; }
       tc_fence_after();
       const float alpha = p.gs[ti.expert % p.wexperts] * 256.0f;
-      for (int sub = 0; sub < nsub; ++sub) {
-        const uint32_t taddr =
-            tmem_base + acc * (kSubs * kGN) + sub * kGN + (static_cast<uint32_t>(quarter * 32) << 16);
-        const int r = sub * kSubM + quarter * 32 + lane;
+      const uint32_t taddr = tmem_base + acc * kGN + (static_cast<uint32_t>(quarter * 32) << 16);
+      const int r = quarter * 32 + lane;
+      if (ti.rows > 0) {                                     // uniform per CTA
         if (p.swiglu) store_rows<true>(p, ti, taddr, r, alpha);
         else store_rows<false>(p, ti, taddr, r, alpha);
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+      if (lane == 0) {
+        if constexpr (PAIR) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[acc]), 0));
+        else mbar_arrive(&tmem_empty[acc]);
+      }
     }
     if (!ok && lane == 0) { *abort_flag = 1; report_error(p.status, MSL_ERR_DEVICE_TIMEOUT); }
   } else {
@@ -301,9 +324,10 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
     // The 8 producer warps form kGroups groups; group q produces stages q, q + kGroups, ...  Each
     // stage's chain (wait for the free slot, table look-up, bit work, stores, proxy fence, arrive)
     // is latency-bound, so letting the groups work on different stages at the same time hides it.
+    constexpr int kRows = S::kRowsPerThread;
     const int t = threadIdx.x - 6 * 32;        // 0..255
     const int gid = t / kGroupThreads, tg = t % kGroupThreads;
-    // Packed codes and scales of the group's NEXT stage are fetched into registers while the
+    // Packed codes and scales of the group's next stages are fetched into registers while the
     // current one is dequantised.
     struct Cursor {
       int g, kb;
@@ -312,24 +336,25 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
     };
     auto seek = [&](Cursor& c) {               // pointers of tile c.g (if any)
       if (c.g < total_tiles) {
-        const TileInfo ti = decode_tile(c.g, mt_prefix, p.offsets, p.experts, n_tiles);
+        const TileInfo ti = decode_tile(c.g, mt_prefix, p.offsets, p.experts, n_tiles, S::kTileM);
         const int64_t tile_id = (static_cast<int64_t>(ti.expert % p.wexperts) * n_tiles + ti.nt) * k_blocks;
-        c.wq = p.wq + tile_id * (kGN * 32) + tg * 32;
-        c.sf = p.sf + tile_id * (kGN * 4) + tg * 4;
+        const int first_row = static_cast<int>(rank) * S::kBRows + tg;   // this CTA's rows of the 256-row tile
+        c.wq = p.wq + tile_id * (kGN * 32) + first_row * 32;
+        c.sf = p.sf + tile_id * (kGN * 4) + first_row * 4;
       }
     };
     auto advance = [&](Cursor& c, int n) {
       c.kb += n;
       bool moved = false;
-      while (c.kb >= k_blocks && c.g < total_tiles) { c.kb -= k_blocks; c.g += gridDim.x; moved = true; }
+      while (c.kb >= k_blocks && c.g < total_tiles) { c.kb -= k_blocks; c.g += n_workers; moved = true; }
       if (moved) seek(c);
     };
     constexpr int kBufs = 3;                   // register sets: the current stage and two in flight
-    uint32_t wbuf[kBufs][kRowsPerThread][8];
-    uint32_t sbuf[kBufs][kRowsPerThread];
-    auto fetch = [&](const Cursor& c, uint32_t (&w)[kRowsPerThread][8], uint32_t (&sc)[kRowsPerThread]) {
+    uint32_t wbuf[kBufs][kRows][8];
+    uint32_t sbuf[kBufs][kRows];
+    auto fetch = [&](const Cursor& c, uint32_t (&w)[kRows][8], uint32_t (&sc)[kRows]) {
 #pragma unroll
-      for (int r = 0; r < kRowsPerThread; ++r) {
+      for (int r = 0; r < kRows; ++r) {
         const uint8_t* wk = c.wq + static_cast<int64_t>(c.kb) * (kGN * 32) + r * (kGroupThreads * 32);
         const uint8_t* sk = c.sf + static_cast<int64_t>(c.kb) * (kGN * 4) + r * (kGroupThreads * 4);
         const uint4 c0 = __ldg(reinterpret_cast<const uint4*>(wk));
@@ -339,7 +364,7 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
         sc[r] = __ldg(reinterpret_cast<const uint32_t*>(sk));
       }
     };
-    Cursor cons{static_cast<int>(blockIdx.x), 0, nullptr, nullptr};
+    Cursor cons{worker, 0, nullptr, nullptr};
     seek(cons);
     advance(cons, gid);
     Cursor pf = cons;
@@ -356,12 +381,12 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
           fetch(pf, wbuf[(u + kBufs - 1) % kBufs], sbuf[(u + kBufs - 1) % kBufs]);
           advance(pf, kGroups);
         }
-        const int s = it % kGStages;
-        const uint32_t ph = (it / kGStages) & 1;
+        const int s = it % kStages;
+        const uint32_t ph = (it / kStages) & 1;
         if (*abort_flag || !mbar_wait(&empty[s], ph ^ 1)) { ok = false; break; }
         uint8_t* sb = smem + s * S::kStageBytes + S::kABytes;
 #pragma unroll
-        for (int r = 0; r < kRowsPerThread; ++r) {
+        for (int r = 0; r < kRows; ++r) {
           const int row = tg + r * kGroupThreads;
 #pragma unroll
           for (int c = 0; c < 8; ++c) {
@@ -371,7 +396,10 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
         }
         fence_async_smem();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&full[s]);
+        if (lane == 0) {
+          if constexpr (PAIR) mbar_arrive_cluster(map_to_cta(smem_u32(&full[s]), 0));
+          else mbar_arrive(&full[s]);
+        }
         it += kGroups;
         advance(cons, kGroups);
       }
@@ -382,9 +410,11 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
   if (warp == 0 && lane == 0 && *abort_flag) drain_pause();
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();    // neither CTA leaves while the other may still signal it
   if (warp == 1) {
     __syncwarp();
-    tmem_dealloc(tmem_base, 2 * kSubs * kGN);
+    if constexpr (PAIR) tmem_dealloc_pair(tmem_base, 2 * kGN);
+    else tmem_dealloc(tmem_base, 2 * kGN);
   }
 }
 
@@ -492,17 +522,49 @@ extern "C" int msl_grouped_gemm_nvfp4(const void* x, int64_t slab_rows, const vo
   if (rc) return rc;
   GroupedArgs a{static_cast<const uint8_t*>(codes), static_cast<const uint8_t*>(scales), global_scales, offsets, out,
                 ld_out, experts, n_padded, k, weight_experts, n_out, swiglu, status};
-  const int smem = GroupedSmem::kTotal + 1024;
-  static_assert(kSubM == 128 && 2 * kSubs * kGN <= 512, "two accumulator sets must fit the 512 TMEM columns");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const char* pair_env = getenv("MSL_GROUPED_PAIR");
+  // The CTA-pair variant (256-row tiles, each CTA dequantises half of the weight tile) is correct but
+  // measured slower than the single-CTA kernel here (820 vs 1012 TFLOP/s): opt-in only.
+  const bool use_pair = slab_rows >= 256LL * experts && pair_env && pair_env[0] == '1';
+  if (use_pair) {
+    using S = GroupedCfg<true>;
+    const int smem = S::kTotal + 1024;
+    static bool configured = false;
+    if (!configured) {
+      if (cudaFuncSetAttribute(grouped_nvfp4_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
+          cudaSuccess)
+        return MSL_ERR_CUDA;
+      configured = true;
+    }
+    const int64_t max_tiles = ((slab_rows + S::kTileM - 1) / S::kTileM + experts) * (n_padded / kGN);
+    const int pairs = static_cast<int>(std::min<int64_t>(max_tiles, sm_count() / 2));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs);
+    cfg.blockDim = dim3(448);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, grouped_nvfp4_kernel<true>, tx, a) == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
+  }
+  using S = GroupedCfg<false>;
+  const int smem = S::kTotal + 1024;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(grouped_nvfp4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+    if (cudaFuncSetAttribute(grouped_nvfp4_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
+        cudaSuccess)
       return MSL_ERR_CUDA;
     configured = true;
   }
-  // Upper bound on tiles without reading the device counts: every expert may add one partial tile.
-  const int64_t max_tiles = ((slab_rows + kGM - 1) / kGM + experts) * (n_padded / kGN);
+  // Upper bound on tiles without reading the device counts: every group may add one partial tile.
+  const int64_t max_tiles = ((slab_rows + S::kTileM - 1) / S::kTileM + experts) * (n_padded / kGN);
   const int grid = static_cast<int>(std::min<int64_t>(max_tiles, sm_count()));
-  grouped_nvfp4_kernel<<<grid, 448, smem, static_cast<cudaStream_t>(stream)>>>(tx, a);
+  grouped_nvfp4_kernel<false><<<grid, 448, smem, st>>>(tx, a);
   return cudaGetLastError() == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
 }

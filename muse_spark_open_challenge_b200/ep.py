@@ -123,21 +123,23 @@ def moe_stage(h, data, st, ctx: ExpertParallel):
     else:
         rowmap = ops.dispatch(h, None, local_ids, slots, ctx.counts, send_x, ctx.send_offsets, status)
     layer._mark(st, "dispatch")
-    # The split sizes travel to the host on a side stream while the main stream computes the shared
-    # expert, which does not depend on the routing: the host wait does not drain the main stream.
+    # The split sizes travel to the host on a side stream; the row exchange then runs on that side
+    # stream too, while the main stream computes the shared expert, which does not depend on the
+    # routing.  The host wait (one event) does not drain the main stream.
     main = torch.cuda.current_stream()
     ctx.side.wait_stream(main)
     with torch.cuda.stream(ctx.side):
         pending = begin_plan(ctx.counts, ctx.world, ctx.group)
+    plan = finish_plan(pending)
+    recv_x, recv_i = ctx.buffers(st, max(plan.recv_rows, 1))
+    with torch.cuda.stream(ctx.side):
+        exchange_rows(send_x, plan.recv_rows, plan.send_splits, plan.recv_splits, out=recv_x, group=ctx.group)
     shared = None
     if st["shared"]:
         s_inter = ops.gemm(h, st["shared_w13"], out_mode=OUT_SWIGLU_BF16, status=status)
         shared = ops.gemm(s_inter, st["shared_w2"], status=status)
         layer._mark(st, "shared_expert")
-    plan = finish_plan(pending)
     main.wait_stream(ctx.side)
-    recv_x, recv_i = ctx.buffers(st, max(plan.recv_rows, 1))
-    exchange_rows(send_x, plan.recv_rows, plan.send_splits, plan.recv_splits, out=recv_x, group=ctx.group)
     layer._mark(st, "a2a_dispatch")
     rows = max(plan.recv_rows, 1)
     ops.grouped_gemm_nvfp4(recv_x[:rows], st["w13_q"], st["w13_s"], st["w13_gs"], plan.group_offsets, recv_i[:rows],

@@ -94,6 +94,9 @@ def test_layer_is_repeatable_and_graph_capturable():
 
 SYNTH_CASES = [
     # (shape, new lens, cached lens, page, kv_scale, local_start)
+    # the reference's own shard sizes (hidden 8192, 16q/2kv x 64, 32 of 256 experts x 4096, pooler and
+    # unpooler) on the contest's first must-pass shape: sliding window + RoPE, page size 1
+    ("NATIVE_SLIDING", [300], [0], 1, 1.0, 96),
     ("MID_SMALL", [300, 211], [0, 130], 64, 1 / 64, 0),
     ("EP_SMALL", [257], [64], 64, 1.0, 32),
     ("TINY", [5, 64, 1, 130], [0, 3, 700, 64], 16, 0.25, 0),
@@ -108,6 +111,7 @@ def test_layer_on_synthetic_shapes(case):
     name, lens, ctxs, page, kv_scale, local_start = case
     shapes = {
         "TINY": synth.TINY,
+        "NATIVE_SLIDING": dataclasses.replace(synth.NATIVE, window=2048, rope_theta=5e5),
         # the mid-prefill architecture at reduced width: no pooler, shared expert, head_dim 128
         "MID_SMALL": dataclasses.replace(synth.MID, hidden=1024, hq=8, hkv=2, n_experts=32, local_experts=32,
                                          moe_width=1024, inter=384, shared_inter=512),

@@ -42,6 +42,23 @@ def test_gemm_bf16_matches_fp32_matmul(ops, m, n, k):
     assert int(status.item()) == 0
 
 
+@pytest.mark.parametrize("m,n,k,mode", [(256, 512, 512, 0), (300, 1280, 512, 0), (4096, 4096, 1024, 1),
+                                        (2500, 10240, 512, 0), (700, 512, 256, 2)])
+def test_gemm_cta_pair_variant(ops, m, n, k, mode, monkeypatch):
+    """The opt-in CTA-pair kernel (cluster of 2, one M256 x N256 MMA per step) gives the same result
+    as the default kernel: bit-identical, since both accumulate the same products in the same order."""
+    g = torch.Generator(device="cuda").manual_seed(m + n)
+    a = torch.randn((m, k), generator=g, device="cuda").to(torch.bfloat16)
+    w = (torch.randn((n, k), generator=g, device="cuda") / math.sqrt(k)).to(torch.bfloat16)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    monkeypatch.setenv("MSL_GEMM_PAIR", "0")
+    want = ops.gemm(a, w, out_mode=mode, status=status)
+    monkeypatch.setenv("MSL_GEMM_PAIR", "1")
+    got = ops.gemm(a, w, out_mode=mode, status=status)
+    assert int(status.item()) == 0
+    assert torch.equal(got, want)
+
+
 def test_gemm_two_segment_router_product(ops):
     """fp32 router as BF16 hi + lo: logits within 2e-5 of the fp64 product."""
     t, h, e = 500, 512, 16
@@ -260,8 +277,11 @@ def test_grouped_dequant_is_exact_for_every_code_and_scale(ops):
     ([0, 1, 7, 128, 129, 300, 0, 5], 256, 256, False),
     ([255, 256, 257, 0, 0, 16, 17, 15], 128, 128, False),
     ([2000, 800, 0, 3], 3072, 1024, True),
+    ([255, 256, 257, 0, 511, 513, 1, 900], 512, 256, True),
+    ([255, 256, 257, 0, 511, 513, 1, 900], 1024, 512, False),
 ])
-def test_grouped_gemm_matches_dequantised_matmul(ops, counts, n, k, swiglu):
+@pytest.mark.parametrize("pair", [False, True])
+def test_grouped_gemm_matches_dequantised_matmul(ops, counts, n, k, swiglu, pair, monkeypatch):
     """rel-L2 per expert against x.float() @ dequantize(w).T (the check of the reference's
     tools/prefill/moe_kernel/test_moe_fp4.py:124-145; its kernels score about 1.7e-3)."""
     g = torch.Generator(device="cuda").manual_seed(n + k)
