@@ -40,15 +40,25 @@ constexpr int kProducers = 256;               // weight-producer threads per CTA
 constexpr int kGroups = 2;                    // producer groups, each taking every kGroups-th stage
 constexpr int kGroupThreads = kProducers / kGroups;
 
-// PAIR = two CTAs of a cluster run one M=256 x N=256 MMA (cta_group::2): each CTA stages its own 128
-// token rows and dequantises only its 128 of the tile's 256 weight rows.
-template <bool PAIR>
+// Tile geometries (MODE):
+//   kNarrow  128 token rows x 256 weight rows per tile, 4 stages, two accumulator sets (the epilogue of
+//            one tile overlaps the main loop of the next).  For calls whose groups are small.
+//   kWide    256 token rows (two 128-row MMAs per K step sharing one dequantised weight tile) x 256
+//            weight rows, 3 stages, one accumulator set (both sub-tiles fill the 512 TMEM columns).
+//            Halves the weight bytes staged, dequantised and fetched per FLOP.
+//   kPair    two CTAs of a cluster run one M=256 x N=256 MMA (cta_group::2): each CTA stages its own
+//            128 token rows and dequantises only its 128 of the tile's 256 weight rows.
+constexpr int kNarrow = 0, kPair = 1, kWide = 2;
+template <int MODE>
 struct GroupedCfg {
-  static constexpr int kTileM = PAIR ? 256 : 128;            // token rows per tile
+  static constexpr bool PAIR = MODE == kPair, WIDE = MODE == kWide;
+  static constexpr int kSubs = WIDE ? 2 : 1;                 // 128-row MMAs per K step in one CTA
+  static constexpr int kTileM = MODE == kNarrow ? 128 : 256; // token rows per tile
   static constexpr int kBRows = PAIR ? 128 : 256;            // weight rows dequantised per CTA per stage
-  static constexpr int kStages = PAIR ? 6 : 4;
+  static constexpr int kStages = PAIR ? 6 : (WIDE ? 3 : 4);
   static constexpr int kRowsPerThread = kBRows / kGroupThreads;
-  static constexpr int kABytes = kSubM * kGK * 2;
+  static constexpr int kSubBytes = kSubM * kGK * 2;
+  static constexpr int kABytes = kSubs * kSubBytes;
   static constexpr int kBBytes = kBRows * kGK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kLutOffset = kStages * kStageBytes;           // 256 x u32
@@ -158,10 +168,11 @@ __device__ __forceinline__ void store_rows(const GroupedArgs& p, const TileInfo&
   }
 }
 
-template <bool PAIR>
+template <int MODE>
 __global__ void __launch_bounds__(448, 1)
 grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
-  using S = GroupedCfg<PAIR>;
+  using S = GroupedCfg<MODE>;
+  constexpr bool PAIR = S::PAIR, WIDE = S::WIDE;
   constexpr int kStages = S::kStages;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -251,8 +262,11 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
             mbar_expect_tx_cluster(bar, S::kABytes);
             tma_load_2d_pair(smem + s * S::kStageBytes, &tm_x, bar, kb * kGK, ti.row0 + rank * kSubM);
           } else {
-            mbar_expect_tx(&full[s], S::kABytes);
-            tma_load_2d(smem + s * S::kStageBytes, &tm_x, &full[s], kb * kGK, ti.row0);
+            const int nsub = WIDE ? (ti.rows + kSubM - 1) / kSubM : 1;
+            mbar_expect_tx(&full[s], nsub * S::kSubBytes);
+            for (int sub = 0; sub < nsub; ++sub)
+              tma_load_2d(smem + s * S::kStageBytes + sub * S::kSubBytes, &tm_x, &full[s], kb * kGK,
+                          ti.row0 + sub * kSubM);
           }
         }
       }
@@ -261,11 +275,17 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0 && rank == 0) {
-      constexpr uint32_t idesc = make_idesc(1, 1, S::kTileM, kGN);
+      constexpr uint32_t idesc = make_idesc(1, 1, PAIR ? 256 : 128, kGN);
       uint32_t it = 0, tile_i = 0;
       bool ok = true;
       for (int g = worker; g < total_tiles && ok; g += n_workers, ++tile_i) {
-        const uint32_t acc = tile_i & 1, acc_ph = (tile_i >> 1) & 1;
+        // kWide has one accumulator set (index 0, phase flips every tile); the others alternate two.
+        const uint32_t acc = WIDE ? 0u : (tile_i & 1), acc_ph = WIDE ? (tile_i & 1) : ((tile_i >> 1) & 1);
+        int nsub = 1;
+        if constexpr (WIDE) {
+          const TileInfo ti = decode_tile(g, mt_prefix, p.offsets, p.experts, n_tiles, S::kTileM);
+          nsub = (ti.rows + kSubM - 1) / kSubM;
+        }
         if (*abort_flag || !mbar_wait(&tmem_empty[acc], acc_ph ^ 1)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * kGN;
@@ -279,8 +299,14 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
 #pragma unroll
           for (int k16 = 0; k16 < kGK / 16; ++k16) {
             const uint64_t da = make_sdesc(sa + k16 * 32, 16, 1024, 2), db = make_sdesc(sb + k16 * 32, 16, 1024, 2);
-            if constexpr (PAIR) tc_mma_f16_pair(d_tmem, da, db, idesc, (kb | k16) != 0);
-            else tc_mma_f16(d_tmem, da, db, idesc, (kb | k16) != 0);
+            if constexpr (PAIR) {
+              tc_mma_f16_pair(d_tmem, da, db, idesc, (kb | k16) != 0);
+            } else {
+              tc_mma_f16(d_tmem, da, db, idesc, (kb | k16) != 0);
+              if (WIDE && nsub > 1)
+                tc_mma_f16(d_tmem + kGN, make_sdesc(sa + S::kSubBytes + k16 * 32, 16, 1024, 2), db, idesc,
+                           (kb | k16) != 0);
+            }
           }
           if constexpr (PAIR) tc_commit_pair(&empty[s]);
           else tc_commit(&empty[s]);
@@ -299,15 +325,18 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
     bool ok = true;
     for (int g = worker; g < total_tiles && ok; g += n_workers, ++tile_i) {
       TileInfo ti = decode_tile(g, mt_prefix, p.offsets, p.experts, n_tiles, S::kTileM);
-      ti.row0 += rank * kSubM;
-      ti.rows = max(0, min(kSubM, ti.rows - static_cast<int>(rank) * kSubM));
-      const uint32_t acc = tile_i & 1, acc_ph = (tile_i >> 1) & 1;
+      if constexpr (PAIR) {                                  // this CTA's 128 rows of the pair's tile
+        ti.row0 += rank * kSubM;
+        ti.rows = max(0, min(kSubM, ti.rows - static_cast<int>(rank) * kSubM));
+      }
+      const uint32_t acc = WIDE ? 0u : (tile_i & 1), acc_ph = WIDE ? (tile_i & 1) : ((tile_i >> 1) & 1);
       if (*abort_flag || !mbar_wait(&tmem_full[acc], acc_ph)) { ok = false; break; }
       tc_fence_after();
       const float alpha = p.gs[ti.expert % p.wexperts] * 256.0f;
-      const uint32_t taddr = tmem_base + acc * kGN + (static_cast<uint32_t>(quarter * 32) << 16);
-      const int r = quarter * 32 + lane;
-      if (ti.rows > 0) {                                     // uniform per CTA
+      const int nsub = WIDE ? (ti.rows + kSubM - 1) / kSubM : (ti.rows > 0 ? 1 : 0);   // uniform per CTA
+      for (int sub = 0; sub < nsub; ++sub) {
+        const uint32_t taddr = tmem_base + (acc + sub) * kGN + (static_cast<uint32_t>(quarter * 32) << 16);
+        const int r = sub * kSubM + quarter * 32 + lane;
         if (p.swiglu) store_rows<true>(p, ti, taddr, r, alpha);
         else store_rows<false>(p, ti, taddr, r, alpha);
       }
@@ -524,15 +553,16 @@ extern "C" int msl_grouped_gemm_nvfp4(const void* x, int64_t slab_rows, const vo
                 ld_out, experts, n_padded, k, weight_experts, n_out, swiglu, status};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const char* pair_env = getenv("MSL_GROUPED_PAIR");
+  const char* wide_env = getenv("MSL_GROUPED_WIDE");
   // The CTA-pair variant (256-row tiles, each CTA dequantises half of the weight tile) is correct but
   // measured slower than the single-CTA kernel here (820 vs 1012 TFLOP/s): opt-in only.
   const bool use_pair = slab_rows >= 256LL * experts && pair_env && pair_env[0] == '1';
   if (use_pair) {
-    using S = GroupedCfg<true>;
+    using S = GroupedCfg<kPair>;
     const int smem = S::kTotal + 1024;
     static bool configured = false;
     if (!configured) {
-      if (cudaFuncSetAttribute(grouped_nvfp4_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
+      if (cudaFuncSetAttribute(grouped_nvfp4_kernel<kPair>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
           cudaSuccess)
         return MSL_ERR_CUDA;
       configured = true;
@@ -551,13 +581,30 @@ extern "C" int msl_grouped_gemm_nvfp4(const void* x, int64_t slab_rows, const vo
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, grouped_nvfp4_kernel<true>, tx, a) == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
+    return cudaLaunchKernelEx(&cfg, grouped_nvfp4_kernel<kPair>, tx, a) == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
   }
-  using S = GroupedCfg<false>;
+  // 256-row tiles when the groups are large enough on average to fill them.
+  const bool use_wide = slab_rows >= 256LL * experts && !(wide_env && wide_env[0] == '0');
+  if (use_wide) {
+    using S = GroupedCfg<kWide>;
+    const int smem = S::kTotal + 1024;
+    static bool configured = false;
+    if (!configured) {
+      if (cudaFuncSetAttribute(grouped_nvfp4_kernel<kWide>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
+          cudaSuccess)
+        return MSL_ERR_CUDA;
+      configured = true;
+    }
+    const int64_t max_tiles = ((slab_rows + S::kTileM - 1) / S::kTileM + experts) * (n_padded / kGN);
+    const int grid = static_cast<int>(std::min<int64_t>(max_tiles, sm_count()));
+    grouped_nvfp4_kernel<kWide><<<grid, 448, smem, st>>>(tx, a);
+    return cudaGetLastError() == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
+  }
+  using S = GroupedCfg<kNarrow>;
   const int smem = S::kTotal + 1024;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(grouped_nvfp4_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
+    if (cudaFuncSetAttribute(grouped_nvfp4_kernel<kNarrow>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
         cudaSuccess)
       return MSL_ERR_CUDA;
     configured = true;
@@ -565,6 +612,6 @@ extern "C" int msl_grouped_gemm_nvfp4(const void* x, int64_t slab_rows, const vo
   // Upper bound on tiles without reading the device counts: every group may add one partial tile.
   const int64_t max_tiles = ((slab_rows + S::kTileM - 1) / S::kTileM + experts) * (n_padded / kGN);
   const int grid = static_cast<int>(std::min<int64_t>(max_tiles, sm_count()));
-  grouped_nvfp4_kernel<false><<<grid, 448, smem, st>>>(tx, a);
+  grouped_nvfp4_kernel<kNarrow><<<grid, 448, smem, st>>>(tx, a);
   return cudaGetLastError() == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
 }

@@ -280,8 +280,8 @@ def test_grouped_dequant_is_exact_for_every_code_and_scale(ops):
     ([255, 256, 257, 0, 511, 513, 1, 900], 512, 256, True),
     ([255, 256, 257, 0, 511, 513, 1, 900], 1024, 512, False),
 ])
-@pytest.mark.parametrize("pair", [False, True])
-def test_grouped_gemm_matches_dequantised_matmul(ops, counts, n, k, swiglu, pair, monkeypatch):
+@pytest.mark.parametrize("variant", ["narrow", "wide", "pair"])
+def test_grouped_gemm_matches_dequantised_matmul(ops, counts, n, k, swiglu, variant, monkeypatch):
     """rel-L2 per expert against x.float() @ dequantize(w).T (the check of the reference's
     tools/prefill/moe_kernel/test_moe_fp4.py:124-145; its kernels score about 1.7e-3)."""
     g = torch.Generator(device="cuda").manual_seed(n + k)
