@@ -250,6 +250,7 @@ def main():
     ap.add_argument("--workload", default="layer", choices=["layer", "attn", "moe"],
                     help="layer = the headline full-layer step; attn / moe = the op-only configurations")
     ap.add_argument("--small", action="store_true", help="reduced op workload, sized for an ncu capture")
+    ap.add_argument("--eager", action="store_true", help="time eager launches instead of a CUDA-graph replay")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -303,19 +304,39 @@ def main():
     ids = out[2]
     routes_local = int(st["offsets"][-1].item())
 
-    # ---- device-timed region: K steps, inputs resident in HBM (per-step working set >> L2)
+    # ---- device-timed region: K steps, inputs resident in HBM (per-step working set >> L2).
+    # On one GPU the step is captured once as a CUDA graph and replayed (the way the reference's
+    # harness times a layer, tools/prefill/judge.py:53-75); the expert-parallel step reads split sizes
+    # on the host and runs eagerly.
+    launches0 = _lib.LAUNCHES
+    step(data)
+    launches_per_step = _lib.LAUNCHES - launches0
+    graph = None
+    if world == 1 and not args.eager:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            step(data)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            graph_out = step(data)
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(graph_out[0], out[0]) and torch.equal(graph_out[2], out[2])
+    run_step = graph.replay if graph is not None else (lambda: step(data))
     sampler = ClockSampler(local_rank)
     sampler.start()
-    launches0 = _lib.LAUNCHES
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
-        step(data)
+        run_step()
     e1.record()
     barrier()
     ms = e0.elapsed_time(e1) / args.steps
-    launches = _lib.LAUNCHES - launches0
+    launches = launches_per_step * args.steps
     clocks = sampler.stop()
 
     # ---- per-kernel times of the same steps (events between launches), for the roofline
@@ -330,30 +351,61 @@ def main():
     st["marks"] = None
     stage_ms = {k: sum(v) / len(v) for k, v in per_stage.items()}
 
-    # ---- end to end through kernel_fn with host buffers
-    host_in = {k: data[k].cpu().pin_memory() for k in ("stream", "attn_input", "positions", "cache_loc", "seq_lens",
-                                                       "cu_seqlens_q", "page_table", "cache_seqlens")}
+    # ---- end to end through kernel_fn with host buffers: every step copies its inputs from pinned
+    # host memory and its three outputs back to pinned host memory inside the timed region.  The
+    # copies run on their own streams with double-buffered device tensors, so the upload of step i+1
+    # and the download of step i-1 overlap the kernels of step i (PCIe is full duplex).
+    keys = ("stream", "attn_input", "positions", "cache_loc", "seq_lens", "cu_seqlens_q", "page_table",
+            "cache_seqlens")
+    host_in = {k: data[k].cpu().pin_memory() for k in keys}
     h2d = sum(v.numel() * v.element_size() for v in host_in.values())
-    host_out = [torch.empty_like(o, device="cpu").pin_memory() for o in out]
-    d2h = sum(v.numel() * v.element_size() for v in host_out)
-    dev_in = dict(data)
+    host_out = [[torch.empty_like(o, device="cpu").pin_memory() for o in out] for _ in range(2)]
+    d2h = sum(v.numel() * v.element_size() for v in host_out[0])
+    dev_in = [dict(data), dict(data)]
+    for slot in dev_in:
+        for k in keys:
+            slot[k] = torch.empty_like(data[k])
+    s_up, s_run, s_down = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+    ev_up = [torch.cuda.Event() for _ in range(2)]
+    ev_run = [torch.cuda.Event() for _ in range(2)]
+    ev_down = [torch.cuda.Event() for _ in range(2)]
+    keep = [None, None]
 
-    def e2e_step():
-        for k, v in host_in.items():
-            dev_in[k] = v.to(dev, non_blocking=True)
-        o = step(dev_in)
-        for dst, src in zip(host_out, o):
-            dst.copy_(src, non_blocking=True)
+    def e2e_loop(n):
+        for i in range(n):
+            b2 = i & 1
+            with torch.cuda.stream(s_up):
+                s_up.wait_event(ev_run[b2])            # the step that last read this input slot is done
+                for k in keys:
+                    dev_in[b2][k].copy_(host_in[k], non_blocking=True)
+                ev_up[b2].record(s_up)
+            with torch.cuda.stream(s_run):
+                s_run.wait_event(ev_up[b2])
+                s_run.wait_event(ev_down[b2])          # outputs of two steps ago have left the device
+                o = step(dev_in[b2])
+                ev_run[b2].record(s_run)
+            with torch.cuda.stream(s_down):
+                s_down.wait_event(ev_run[b2])
+                for dst, src in zip(host_out[b2], o):
+                    dst.copy_(src, non_blocking=True)
+                ev_down[b2].record(s_down)
+            keep[b2] = o
 
-    e2e_step()
+    for s_ in (s_up, s_run, s_down):
+        s_.wait_stream(torch.cuda.current_stream())
+    e2e_loop(2)
     barrier()
     t0e, t1e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0e.record()
-    for _ in range(args.steps):
-        e2e_step()
+    for s_ in (s_up, s_run, s_down):
+        s_.wait_event(t0e)
+    e2e_loop(args.steps)
+    for s_ in (s_up, s_run, s_down):
+        torch.cuda.current_stream().wait_stream(s_)
     t1e.record()
     barrier()
     e2e_ms = t0e.elapsed_time(t1e) / args.steps
+    assert torch.equal(host_out[(args.steps - 1) & 1][2], out[2].cpu())
     layer.check_status(st)
 
     times = torch.tensor([ms, e2e_ms], device=dev)
@@ -388,7 +440,8 @@ def main():
         "data": "synthetic",
         "config": {"workload": "full decoder layer, mid prefill (BASELINE config 3): 4 x 4096 tokens per GPU, hidden "
                                "4096, 32q/8kv x 128, page 64, 128 experts top-8 x 1536 NVFP4 + shared 4096",
-                   "tokens_per_gpu": tokens, "expert_parallel": world, "l2": "per-step working set (weights 2.6 GB) "
+                   "tokens_per_gpu": tokens, "expert_parallel": world,
+                   "launch": "CUDA graph replay" if graph is not None else "eager", "l2": "per-step working set (weights 2.6 GB) "
                    "exceeds the 126 MB L2; no explicit flush"},
         "layer_tflops": total_flops / (ms * 1e-3) / 1e12,
         "stage_ms": {k: round(v, 4) for k, v in stage_ms.items()},
