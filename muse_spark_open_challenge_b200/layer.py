@@ -72,6 +72,7 @@ def prepare(weights: dict) -> dict:
     st["status"] = torch.zeros(1, dtype=torch.int32, device=dev)
     st["inv_freq"] = {}
     st["cap"] = 0
+    st["side"] = torch.cuda.Stream(dev)
     torch.cuda.synchronize(dev)
     return st
 
@@ -134,38 +135,68 @@ def attention_stage(data, st):
     return out
 
 
-def moe_stage(h, data, st):
-    """Router, dispatch, routed experts (+ shared expert), weighted combine, unpooler.
-    h: bf16 [T, H], the FFN input.  Returns (FFN branch bf16 [T, H], expert ids i32 [T, K])."""
-    cfg = data["config"]
-    top_k, status = cfg["top_k"], st["status"]
-    tokens, hidden = h.shape
+def _route(h, data, st, top_k):
+    """Router logits (BF16 hi + lo product, fp32 out), top-k, weights, per-expert slots."""
+    hidden = h.shape[1]
     logits = ops.gemm(h, st["router_hilo"], out_mode=OUT_F32, k=hidden, segs=2, a_seg_stride=0, b_seg_stride=hidden,
-                      status=status)
+                      status=st["status"])
     _mark(st, "gemm_router")
     st["counts"].zero_()
-    ids, tw, local_ids, slots = ops.route_topk(logits, st["router_bias"], ROUTER_MULTIPLIER, data["local_start"],
-                                               st["n_experts"], top_k, st["n_local"], st["counts"])
+    routed = ops.route_topk(logits, st["router_bias"], ROUTER_MULTIPLIER, data["local_start"], st["n_experts"], top_k,
+                            st["n_local"], st["counts"])
     _mark(st, "route_topk")
+    return routed
+
+
+def _shared_expert(h, st):
+    s_inter = ops.gemm(h, st["shared_w13"], out_mode=OUT_SWIGLU_BF16, status=st["status"])
+    shared = ops.gemm(s_inter, st["shared_w2"], status=st["status"])
+    _mark(st, "shared_expert")
+    return shared
+
+
+def moe_stage(h, data, st):
+    """Router, dispatch, routed experts (+ shared expert), weighted combine, unpooler.
+    h: bf16 [T, H], the FFN input.  Returns (FFN branch bf16 [T, H], expert ids i32 [T, K]).
+
+    The routing chain (router GEMM, top-k, and without a pooler the dispatch) runs on a side stream
+    next to the dense GEMM that does not depend on it (shared expert, or pooler), as the reference
+    forks its router (submission.py:1105-1117); fork and join are stream waits, so the call stays
+    capturable.  With per-stage timing marks enabled everything runs on one stream."""
+    cfg = data["config"]
+    top_k, status = cfg["top_k"], st["status"]
+    tokens = h.shape[0]
     slab_x, slab_i = _scratch(st, tokens, top_k)
+    overlap = st.get("marks") is None
+    main = torch.cuda.current_stream()
+    side = st["side"] if overlap else main
+    if overlap:
+        side.wait_stream(main)
+    with torch.cuda.stream(side):
+        ids, tw, local_ids, slots = _route(h, data, st, top_k)
+        rowmap = None
+        if not st["pooled"]:
+            rowmap = ops.dispatch(h, None, local_ids, slots, st["counts"], slab_x, st["offsets"], status)
+            _mark(st, "dispatch")
+    shared = None
     if st["pooled"]:
         p = ops.gemm(h, st["pooler"], status=status)
         _mark(st, "gemm_pooler")
+    elif st["shared"]:
+        shared = _shared_expert(h, st)
+    if overlap:
+        main.wait_stream(side)
+        for t in (ids, tw, local_ids, slots) + ((rowmap,) if rowmap is not None else ()):
+            t.record_stream(main)          # allocated on the side stream, read on the main one
+    if st["pooled"]:
         rowmap = ops.dispatch(p, st["w_pre_exp"], local_ids, slots, st["counts"], slab_x, st["offsets"], status)
-    else:
-        rowmap = ops.dispatch(h, None, local_ids, slots, st["counts"], slab_x, st["offsets"], status)
-    _mark(st, "dispatch")
+        _mark(st, "dispatch")
     ops.grouped_gemm_nvfp4(slab_x, st["w13_q"], st["w13_s"], st["w13_gs"], st["offsets"], slab_i, st["inter"], True,
                            status)
     _mark(st, "experts_gate_up")
     ops.grouped_gemm_nvfp4(slab_i, st["w2_q"], st["w2_s"], st["w2_gs"], st["offsets"], slab_x, st["moe_width"],
                            False, status)
     _mark(st, "experts_down")
-    shared = None
-    if st["shared"]:
-        s_inter = ops.gemm(h, st["shared_w13"], out_mode=OUT_SWIGLU_BF16, status=status)
-        shared = ops.gemm(s_inter, st["shared_w2"], status=status)
-        _mark(st, "shared_expert")
     moe = ops.combine(slab_x, rowmap, tw, st["w_post_exp"], addend=shared)
     _mark(st, "combine")
     if st["pooled"]:
