@@ -250,6 +250,9 @@ def main():
     ap.add_argument("--workload", default="layer", choices=["layer", "attn", "moe"],
                     help="layer = the headline full-layer step; attn / moe = the op-only configurations")
     ap.add_argument("--small", action="store_true", help="reduced op workload, sized for an ncu capture")
+    ap.add_argument("--transport", default="peer", choices=["peer", "collective"],
+                    help="expert-parallel row exchange (N > 1): peer-memory stores/loads fused into the dispatch and "
+                         "combine kernels, or NCCL all-to-alls")
     ap.add_argument("--eager", action="store_true", help="time eager launches instead of a CUDA-graph replay")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -284,6 +287,8 @@ def main():
                 dist.broadcast(v, 0)
         st = layer.prepare(weights)
         ctx = ep.ExpertParallel(st, world, rank, shape.n_experts)
+        if args.transport == "peer":
+            ep.enable_peer(ctx, st, max_tokens=data["config"]["tokens"], top_k=shape.top_k)
         step = lambda d: ep.kernel_fn(d, st, ctx)  # noqa: E731
     else:
         shape, weights, data = make_workload(dev)
@@ -441,6 +446,7 @@ def main():
         "config": {"workload": "full decoder layer, mid prefill (BASELINE config 3): 4 x 4096 tokens per GPU, hidden "
                                "4096, 32q/8kv x 128, page 64, 128 experts top-8 x 1536 NVFP4 + shared 4096",
                    "tokens_per_gpu": tokens, "expert_parallel": world,
+                   "ep_transport": (args.transport if world > 1 else None),
                    "launch": "CUDA graph replay" if graph is not None else "eager", "l2": "per-step working set (weights 2.6 GB) "
                    "exceeds the 126 MB L2; no explicit flush"},
         "layer_tflops": total_flops / (ms * 1e-3) / 1e12,

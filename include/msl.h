@@ -118,6 +118,40 @@ int msl_route_dispatch_static(const float* logits, int64_t ld, int hilo, const f
 int msl_combine(const void* y, const int* rowmap, const float* weights, const float* post_w, const void* addend,
                 int64_t ld_addend, void* out, int64_t ld_out, int tokens, int top_k, int width, void* stream);
 
+/* Expert parallelism over peer memory (one process per GPU, every rank's row slab mapped into every
+ * other rank's address space).  These three calls stand where the reference leaves identities for
+ * the cross-GPU steps (reference.py:438 all-gather, :451 reduce-scatter, :467 "LOCAL experts") and
+ * have no kernel counterpart there.
+ *
+ * msl_ep_plan: counts_all i32 [world, world * local_experts] (row s = routes of rank s per global
+ * expert, all-gathered).  Writes dest_base i32 [world * local_experts] (first row, in the owning
+ * rank's slab, of this rank's rows for each expert) and group_offsets i32 [world * local_experts + 1]
+ * (row ranges of this rank's own slab, groups ordered (source rank, local expert)).  Sets *status to
+ * MSL_ERR_CAPACITY when this rank's slab would need more than `cap` rows. */
+int msl_ep_plan(const int* counts_all, int world, int local_experts, int rank, int cap, int* dest_base,
+                int* group_offsets, int* status, void* stream);
+
+/* Barrier over the ranks of one node, on the stream: flag_bases is a DEVICE array of `world` pointers
+ * to the ranks' i32 [world + 1] flag words (peer-mapped, zeroed once before the first barrier).
+ * Orders every earlier peer store of every rank before every later peer load.  A rank that waits longer
+ * than timeout_ms sets *status to MSL_ERR_DEVICE_TIMEOUT and carries on.  Each rank must run on its
+ * own GPU. */
+int msl_peer_barrier(int* const* flag_bases, int rank, int world, int timeout_ms, int* status, void* stream);
+
+/* Dispatch into the owning ranks' slabs: peer_bases is a DEVICE array of `world` pointers to the
+ * ranks' bf16 [cap, width] slabs; ids i32 [tokens, top_k] are global expert ids, slots the ranks
+ * within (this rank, expert) from msl_route_topk.  The row of route (t, j) lands at
+ * peer_bases[e / local_experts] + (dest_base[e] + slot) * width; rowmap receives
+ * rank * cap + row (or -1 for a row beyond cap).  Optional RMS norm as in msl_dispatch. */
+int msl_dispatch_peer(const void* x, int64_t ldx, const float* norm_w, const int* ids, const int* slots,
+                      const int* dest_base, void* const* peer_bases, int local_experts, int cap, int tokens,
+                      int top_k, int width, int* rowmap, void* stream);
+
+/* msl_combine with the rows read from the owning ranks' slabs (rowmap from msl_dispatch_peer). */
+int msl_combine_peer(const void* const* peer_bases, int peer_cap, const int* rowmap, const float* weights,
+                     const float* post_w, const void* addend, int64_t ld_addend, void* out, int64_t ld_out,
+                     int tokens, int top_k, int width, void* stream);
+
 /* Rows of a re-tiled NVFP4 bank: `rows` padded to whole 256-row tiles (for a gate/up bank,
  * interleave != 0, each half padded to whole 128-row blocks). */
 int64_t msl_nvfp4_padded_rows(int rows, int interleave);

@@ -348,6 +348,111 @@ dispatch_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, const float* _
   }
 }
 
+// ============================================================================ expert-parallel plan + dispatch
+// counts_all[s][e]: routes of rank s to global expert e (all-gathered).  Rank d owns experts
+// [d * el, (d + 1) * el); its slab holds row groups ordered (source rank, local expert).  For this
+// rank `me`: dest_base[e] = first row, in the owner's slab, of the group (me, e); group_offsets =
+// row ranges of this rank's own slab (consumed by the grouped GEMM).  A slab that would need more than
+// `cap` rows is reported in *status.
+__global__ void ep_plan_kernel(const int* __restrict__ counts_all, int world, int el, int me, int cap,
+                               int* __restrict__ dest_base, int* __restrict__ group_offsets, int* status) {
+  const int n_experts = world * el;
+  for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
+    const int d = e / el;
+    int base = 0;
+    for (int s = 0; s < me; ++s)
+      for (int x = d * el; x < (d + 1) * el; ++x) base += counts_all[s * n_experts + x];
+    for (int x = d * el; x < e; ++x) base += counts_all[me * n_experts + x];
+    dest_base[e] = base;
+  }
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int s = 0; s < world; ++s)
+      for (int le = 0; le < el; ++le) {
+        group_offsets[s * el + le] = run;
+        run += counts_all[s * n_experts + me * el + le];
+      }
+    group_offsets[world * el] = run;
+    if (run > cap) report_error(status, MSL_ERR_CAPACITY);
+  }
+}
+
+// Token dispatch straight into the expert-owning ranks' slabs (peer_bases[d], NVLink stores): the
+// dispatch all-to-all of expert parallelism fused into the dispatch kernel.  rowmap receives
+// d * cap + row.
+__global__ void __launch_bounds__(256)
+dispatch_peer_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, const float* __restrict__ norm_w,
+                     const int* __restrict__ ids, const int* __restrict__ slots, const int* __restrict__ dest_base,
+                     __nv_bfloat16* const* __restrict__ peer_bases, int el, int cap, int top_k, int width,
+                     int* __restrict__ rowmap) {
+  __shared__ float scratch[32];
+  const int t = blockIdx.x;
+  const int chunks = width / 8;
+  float ss[1] = {0.f};
+  if (norm_w != nullptr) {
+    for (int ch = threadIdx.x; ch < chunks; ch += blockDim.x) {
+      float v[8];
+      unpack8(*reinterpret_cast<const uint4*>(x + t * ldx + ch * 8), v);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss[0] += v[i] * v[i];
+    }
+    block_sum<1>(ss, scratch);
+  }
+  const float r = norm_w != nullptr ? 1.0f / sqrtf(ss[0] / width + 1e-5f) : 1.0f;
+  __nv_bfloat16* dst[16];
+  int nr = 0;
+  for (int j = 0; j < top_k && j < 16; ++j) {
+    const int e = ids[t * top_k + j];
+    const int d = e / el;
+    const int row = dest_base[e] + slots[t * top_k + j];
+    const bool ok = row < cap;                 // an overflowing slab was already reported by the plan
+    if (threadIdx.x == 0) rowmap[t * top_k + j] = ok ? d * cap + row : -1;
+    if (ok) dst[nr++] = peer_bases[d] + static_cast<int64_t>(row) * width;
+  }
+  for (int ch = threadIdx.x; ch < chunks; ch += blockDim.x) {
+    uint4 raw = *reinterpret_cast<const uint4*>(x + t * ldx + ch * 8);
+    if (norm_w != nullptr) {
+      float v[8];
+      unpack8(raw, v);
+      const float4 w0 = *reinterpret_cast<const float4*>(norm_w + ch * 8);
+      const float4 w1 = *reinterpret_cast<const float4*>(norm_w + ch * 8 + 4);
+      v[0] *= r * w0.x; v[1] *= r * w0.y; v[2] *= r * w0.z; v[3] *= r * w0.w;
+      v[4] *= r * w1.x; v[5] *= r * w1.y; v[6] *= r * w1.z; v[7] *= r * w1.w;
+      raw = pack8(v);
+    }
+    for (int j = 0; j < nr; ++j) *reinterpret_cast<uint4*>(dst[j] + ch * 8) = raw;
+  }
+}
+
+// Barrier over the ranks of one node.  flag_bases[r] -> rank r's i32 [world + 1] words in peer-mapped
+// memory: word s = last barrier number rank s announced to r, word `world` = r's own barrier number.
+// Every rank stores its next number into its word on every peer (release, system scope), then waits
+// until every peer's number has reached it.  Each rank runs this on its own GPU.  A wait that
+// exceeds `limit_ns` records MSL_ERR_DEVICE_TIMEOUT and returns.
+__global__ void peer_barrier_kernel(int* const* __restrict__ flag_bases, int rank, int world, uint64_t limit_ns,
+                                    int* status) {
+  int* mine = flag_bases[rank];
+  const int number = mine[world] + 1;            // only thread 0 rewrites it, after the barrier below
+  const int p = threadIdx.x;
+  if (p < world) {
+    __threadfence_system();
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flag_bases[p] + rank), "r"(number) : "memory");
+    const uint64_t t0 = global_ns();
+    for (uint32_t i = 0;; ++i) {
+      int seen;
+      asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(mine + p) : "memory");
+      if (seen - number >= 0) break;
+      if ((i & 255u) == 255u && global_ns() - t0 > limit_ns) {
+        report_error(status, MSL_ERR_DEVICE_TIMEOUT);
+        break;
+      }
+      __nanosleep(64);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) mine[world] = number;
+}
+
 // ============================================================================ weighted combine
 // out[t] = sum_j w[t, j] * rms(y[rowmap[t, j]] * post_w, eps 1e-8)  (+ addend[t]); routes with
 // rowmap < 0 (another rank's expert) contribute nothing (reference.py:427-444).
@@ -355,11 +460,15 @@ dispatch_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, const float* _
 // asynchronous copies (no registers held while they are in flight, so several blocks per SM keep
 // enough bytes outstanding), then read twice from shared memory: once for the sums of squares,
 // once for the weighted accumulation.  Each row crosses HBM exactly once.
-template <int MAXK>
+// With PEER the rows live in the expert-owning ranks' slabs: rowmap holds rank * peer_cap + row and the
+// row is read straight from that rank's memory (peer_bases[rank], NVLink) - the combine all-to-all of
+// expert parallelism fused into this kernel.
+template <int MAXK, bool PEER>
 __global__ void __launch_bounds__(512)
 combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ rowmap, const float* __restrict__ w,
                const float* __restrict__ post_w, const __nv_bfloat16* __restrict__ addend, int64_t ld_add,
-               __nv_bfloat16* __restrict__ out, int64_t ld_out, int top_k, int width) {
+               __nv_bfloat16* __restrict__ out, int64_t ld_out, int top_k, int width,
+               const __nv_bfloat16* const* __restrict__ peer_bases, int peer_cap) {
   extern __shared__ __align__(16) uint8_t rows_smem[];      // [top_k][width] bf16
   __shared__ float scratch[32 * MAXK];
   const int t = blockIdx.x;
@@ -369,7 +478,8 @@ combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ rowm
     const int row = rowmap[t * top_k + j];
     if (row >= 0) {
       valid |= 1u << j;
-      const __nv_bfloat16* src = y + static_cast<int64_t>(row) * width;
+      const __nv_bfloat16* src = PEER ? peer_bases[row / peer_cap] + static_cast<int64_t>(row % peer_cap) * width
+                                      : y + static_cast<int64_t>(row) * width;
       for (int ch = threadIdx.x; ch < chunks; ch += blockDim.x) {
         const uint32_t dst = smem_u32(rows_smem + (static_cast<size_t>(j) * width + ch * 8) * 2);
         asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src + ch * 8) : "memory");
@@ -520,10 +630,10 @@ extern "C" int msl_dispatch(const void* x, int64_t ldx, const float* norm_w, con
   return cudaGetLastError() == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
 }
 
-extern "C" int msl_combine(const void* y, const int* rowmap, const float* weights, const float* post_w,
-                           const void* addend, int64_t ld_addend, void* out, int64_t ld_out, int tokens, int top_k,
-                           int width, void* stream) {
-  if (!y || !rowmap || !weights || !post_w || !out) return MSL_ERR_ARG;
+static int combine_launch(const void* y, const int* rowmap, const float* weights, const float* post_w,
+                          const void* addend, int64_t ld_addend, void* out, int64_t ld_out, int tokens, int top_k,
+                          int width, const void* const* peer_bases, int peer_cap, void* stream) {
+  if ((!y && !peer_bases) || !rowmap || !weights || !post_w || !out) return MSL_ERR_ARG;
   if (tokens < 0 || top_k <= 0 || top_k > 8 || width <= 0) return MSL_ERR_ARG;
   if ((width & 7) || (ld_out & 7) || (ld_addend & 7)) return MSL_ERR_ALIGN;
   if (static_cast<int64_t>(top_k) * width * 2 > 200 * 1024) return MSL_ERR_UNSUPPORTED;   // rows staged in smem
@@ -532,8 +642,10 @@ extern "C" int msl_combine(const void* y, const int* rowmap, const float* weight
   const int smem = top_k * width * 2;
   static int configured = 0;       // largest dynamic shared-memory size set so far
   if (smem > 48 * 1024 && smem > configured) {
-    if (cudaFuncSetAttribute(combine_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
-        cudaFuncSetAttribute(combine_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+    if (cudaFuncSetAttribute(combine_kernel<4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
+        cudaFuncSetAttribute(combine_kernel<8, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
+        cudaFuncSetAttribute(combine_kernel<4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
+        cudaFuncSetAttribute(combine_kernel<8, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
       return MSL_ERR_CUDA;
     configured = smem;
   }
@@ -541,11 +653,38 @@ extern "C" int msl_combine(const void* y, const int* rowmap, const float* weight
   auto* yy = static_cast<const __nv_bfloat16*>(y);
   auto* ad = static_cast<const __nv_bfloat16*>(addend);
   auto* oo = static_cast<__nv_bfloat16*>(out);
-  if (top_k <= 4)
-    combine_kernel<4><<<tokens, threads, smem, st>>>(yy, rowmap, weights, post_w, ad, ld_addend, oo, ld_out, top_k, width);
-  else
-    combine_kernel<8><<<tokens, threads, smem, st>>>(yy, rowmap, weights, post_w, ad, ld_addend, oo, ld_out, top_k, width);
+  auto* pb = reinterpret_cast<const __nv_bfloat16* const*>(peer_bases);
+  if (pb != nullptr) {
+    if (peer_cap <= 0) return MSL_ERR_ARG;
+    if (top_k <= 4)
+      combine_kernel<4, true><<<tokens, threads, smem, st>>>(yy, rowmap, weights, post_w, ad, ld_addend, oo, ld_out,
+                                                             top_k, width, pb, peer_cap);
+    else
+      combine_kernel<8, true><<<tokens, threads, smem, st>>>(yy, rowmap, weights, post_w, ad, ld_addend, oo, ld_out,
+                                                             top_k, width, pb, peer_cap);
+  } else if (top_k <= 4) {
+    combine_kernel<4, false><<<tokens, threads, smem, st>>>(yy, rowmap, weights, post_w, ad, ld_addend, oo, ld_out,
+                                                            top_k, width, nullptr, 1);
+  } else {
+    combine_kernel<8, false><<<tokens, threads, smem, st>>>(yy, rowmap, weights, post_w, ad, ld_addend, oo, ld_out,
+                                                            top_k, width, nullptr, 1);
+  }
   return cudaGetLastError() == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
+}
+
+extern "C" int msl_combine(const void* y, const int* rowmap, const float* weights, const float* post_w,
+                           const void* addend, int64_t ld_addend, void* out, int64_t ld_out, int tokens, int top_k,
+                           int width, void* stream) {
+  return combine_launch(y, rowmap, weights, post_w, addend, ld_addend, out, ld_out, tokens, top_k, width, nullptr, 0,
+                        stream);
+}
+
+extern "C" int msl_combine_peer(const void* const* peer_bases, int peer_cap, const int* rowmap, const float* weights,
+                                const float* post_w, const void* addend, int64_t ld_addend, void* out, int64_t ld_out,
+                                int tokens, int top_k, int width, void* stream) {
+  if (!peer_bases) return MSL_ERR_ARG;
+  return combine_launch(nullptr, rowmap, weights, post_w, addend, ld_addend, out, ld_out, tokens, top_k, width,
+                        peer_bases, peer_cap, stream);
 }
 
 
@@ -602,4 +741,37 @@ extern "C" int msl_route_dispatch_static(const float* logits, int64_t ld, int hi
   if (rc != MSL_OK) return rc;
   return msl_dispatch(x, ldx, norm_w, local_ids, slots, counts, tokens, n_local, top_k, width, slab, slab_rows, rowmap,
                       offsets_out, status, stream);
+}
+
+
+extern "C" int msl_ep_plan(const int* counts_all, int world, int local_experts, int rank, int cap, int* dest_base,
+                           int* group_offsets, int* status, void* stream) {
+  if (!counts_all || !dest_base || !group_offsets || world <= 0 || local_experts <= 0 || rank < 0 || rank >= world ||
+      cap <= 0)
+    return MSL_ERR_ARG;
+  ep_plan_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(counts_all, world, local_experts, rank, cap,
+                                                                    dest_base, group_offsets, status);
+  return cudaGetLastError() == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
+}
+
+extern "C" int msl_dispatch_peer(const void* x, int64_t ldx, const float* norm_w, const int* ids, const int* slots,
+                                 const int* dest_base, void* const* peer_bases, int local_experts, int cap,
+                                 int tokens, int top_k, int width, int* rowmap, void* stream) {
+  if (!x || !ids || !slots || !dest_base || !peer_bases || !rowmap) return MSL_ERR_ARG;
+  if (tokens < 0 || local_experts <= 0 || cap <= 0 || top_k <= 0 || top_k > 16 || width <= 0) return MSL_ERR_ARG;
+  if ((width & 7) || (ldx & 7) || (reinterpret_cast<uintptr_t>(x) & 15)) return MSL_ERR_ALIGN;
+  if (tokens == 0) return MSL_OK;
+  const int threads = std::min(256, ((width / 8 + 31) / 32) * 32);
+  dispatch_peer_kernel<<<tokens, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), ldx, norm_w, ids, slots, dest_base,
+      reinterpret_cast<__nv_bfloat16* const*>(peer_bases), local_experts, cap, top_k, width, rowmap);
+  return cudaGetLastError() == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
+}
+
+extern "C" int msl_peer_barrier(int* const* flag_bases, int rank, int world, int timeout_ms, int* status,
+                                void* stream) {
+  if (!flag_bases || world <= 0 || world > 64 || rank < 0 || rank >= world || timeout_ms <= 0) return MSL_ERR_ARG;
+  peer_barrier_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(
+      flag_bases, rank, world, static_cast<uint64_t>(timeout_ms) * 1000000ull, status);
+  return cudaGetLastError() == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
 }

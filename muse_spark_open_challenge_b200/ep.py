@@ -9,11 +9,21 @@ supplies the exchange it leaves out:
     counts all-to-all -> row all-to-all (dispatch) -> local grouped GEMMs over (source, expert) groups
     -> row all-to-all back (combine) -> local weighted sum
 
-The plan and both exchanges are device- and backend-agnostic (`gloo` on CPU in the tests, `nccl` on
-GPUs).  The split sizes are read on the host (one small synchronisation per layer).
+Two transports:
+
+* collective (`moe_stage`): the plan and both row exchanges are `torch.distributed` all-to-alls,
+  device- and backend-agnostic (`gloo` on CPU in the tests, `nccl` on GPUs).  The split sizes are read
+  on the host (one small synchronisation per layer).
+* peer memory (`moe_stage_peer`, GPUs of one NVLink domain): every rank's row slab is mapped into
+  every other rank; the dispatch kernel stores token rows straight into the owners' slabs and the
+  combine kernel loads expert outputs straight from them, so both row exchanges are fused into the
+  kernels either side of the expert GEMMs.  The route counts are all-gathered on the device and the
+  row placement is computed there: no host synchronisation.  Three stream barriers per layer order
+  the peer stores and loads.
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 
 import torch
@@ -92,6 +102,7 @@ class ExpertParallel:
         self.send_offsets = torch.zeros(n_experts + 1, dtype=torch.int32, device=st["device"])
         self.cap = 0
         self.recv_x = self.recv_i = None
+        self.peer = None                       # set by enable_peer
         self.side = torch.cuda.Stream(st["device"]) if torch.device(st["device"]).type == "cuda" else None
 
     def buffers(self, st, rows):
@@ -101,6 +112,110 @@ class ExpertParallel:
             self.recv_i = torch.empty((rows_cap, st["inter"]), dtype=torch.bfloat16, device=st["device"])
             self.cap = rows_cap
         return self.recv_x, self.recv_i
+
+
+class PeerSlabs:
+    """Peer-mapped memory of one rank: a bf16 [cap, width] row slab plus the barrier's flag words,
+    allocated as symmetric memory and exchanged once; holds the device arrays of every rank's slab
+    and flag pointers."""
+
+    FLAG_BYTES = 4096
+
+    def __init__(self, ctx: "ExpertParallel", st: dict, cap: int):
+        import torch.distributed._symmetric_memory as symm
+
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # plain peer loads/stores only
+        dev = torch.device(st["device"])
+        width = st["moe_width"]
+        slab_bytes = cap * width * 2
+        self.raw = symm.empty(slab_bytes + self.FLAG_BYTES, dtype=torch.uint8, device=dev)
+        self.raw.zero_()
+        group = ctx.group if ctx.group is not None else dist.group.WORLD
+        self.handle = symm.rendezvous(self.raw, group)
+        bases = [int(p) for p in self.handle.buffer_ptrs]
+        self.slab = self.raw[:slab_bytes].view(torch.bfloat16).view(cap, width)
+        self.slab_ptrs = torch.tensor(bases, dtype=torch.int64, device=dev)
+        self.flag_ptrs = torch.tensor([b + slab_bytes for b in bases], dtype=torch.int64, device=dev)
+        self.cap = cap
+        torch.cuda.synchronize(dev)
+        dist.barrier(group=ctx.group)          # every rank's flag words are zero before the first barrier
+
+
+def enable_peer(ctx: "ExpertParallel", st: dict, max_tokens: int, top_k: int, capacity_factor: float = 2.0):
+    """Switch `ctx` to the peer-memory transport.  Every rank's slab holds up to
+    capacity_factor * max_tokens * top_k rows (never more than the worst case world * max_tokens *
+    top_k); a layer whose routing needs more sets MSL_ERR_CAPACITY in the status word."""
+    dev = st["device"]
+    most = torch.tensor([max_tokens], dtype=torch.int64, device=dev)
+    dist.all_reduce(most, op=dist.ReduceOp.MAX, group=ctx.group)       # slabs have one size on every rank
+    cap = int(min(ctx.world, capacity_factor) * int(most.item()) * top_k)
+    cap = (cap + 255) // 256 * 256
+    ctx.peer = PeerSlabs(ctx, st, cap)
+    ctx.recv_i = torch.empty((cap, st["inter"]), dtype=torch.bfloat16, device=dev)
+    ctx.counts_all = torch.zeros((ctx.world, ctx.n_experts), dtype=torch.int32, device=dev)
+    ctx.dest_base = torch.zeros(ctx.n_experts, dtype=torch.int32, device=dev)
+    ctx.group_offsets = torch.zeros(ctx.n_experts + 1, dtype=torch.int32, device=dev)
+    return ctx
+
+
+def moe_stage_peer(h, data, st, ctx: ExpertParallel):
+    """Expert-parallel MoE stage over peer memory: dispatch and combine kernels move the rows."""
+    cfg = data["config"]
+    top_k, status = cfg["top_k"], st["status"]
+    peer, local = ctx.peer, ctx.n_experts // ctx.world
+    logits = ops.gemm(h, st["router_hilo"], out_mode=OUT_F32, k=h.shape[1], segs=2, a_seg_stride=0,
+                      b_seg_stride=h.shape[1], status=status)
+    layer._mark(st, "gemm_router")
+    ctx.counts.zero_()
+    ids, tw, _, slots = ops.route_topk(logits, st["router_bias"], layer.ROUTER_MULTIPLIER, ctx.zero, ctx.n_experts,
+                                       top_k, ctx.n_experts, ctx.counts)
+    layer._mark(st, "route_topk")
+    # The plan and the NVLink-bound dispatch run on a side stream next to the compute-bound shared
+    # expert (per-stage timing keeps one stream so that the marks mean something).
+    main = torch.cuda.current_stream()
+    fork = st.get("marks") is None and bool(st["shared"])
+    if fork:
+        ctx.side.wait_stream(main)
+    with torch.cuda.stream(ctx.side if fork else main):
+        dist.all_gather_into_tensor(ctx.counts_all.view(-1), ctx.counts, group=ctx.group)
+        ops.ep_plan(ctx.counts_all, ctx.rank, peer.cap, ctx.dest_base, ctx.group_offsets, status)
+        # every rank has finished reading this rank's slab (the previous layer's combine) before new rows land
+        ops.peer_barrier(peer.flag_ptrs.data_ptr(), ctx.rank, ctx.world, status)
+        layer._mark(st, "plan")
+        if st["pooled"]:
+            p = ops.gemm(h, st["pooler"], status=status)
+            rowmap = ops.dispatch_peer(p, st["w_pre_exp"], ids, slots, ctx.dest_base, peer.slab_ptrs.data_ptr(),
+                                       local, peer.cap)
+        else:
+            rowmap = ops.dispatch_peer(h, None, ids, slots, ctx.dest_base, peer.slab_ptrs.data_ptr(), local,
+                                       peer.cap)
+        layer._mark(st, "dispatch")
+    shared = None
+    if st["shared"]:                           # also absorbs the skew between ranks ahead of the barrier
+        s_inter = ops.gemm(h, st["shared_w13"], out_mode=OUT_SWIGLU_BF16, status=status)
+        shared = ops.gemm(s_inter, st["shared_w2"], status=status)
+        layer._mark(st, "shared_expert")
+    if fork:
+        main.wait_stream(ctx.side)
+        rowmap.record_stream(main)             # allocated on the side stream, read on the main one
+    ops.peer_barrier(peer.flag_ptrs.data_ptr(), ctx.rank, ctx.world, status)      # all rows have landed
+    layer._mark(st, "barrier_rows")
+    ops.grouped_gemm_nvfp4(peer.slab, st["w13_q"], st["w13_s"], st["w13_gs"], ctx.group_offsets, ctx.recv_i,
+                           st["inter"], True, status)
+    layer._mark(st, "experts_gate_up")
+    ops.grouped_gemm_nvfp4(ctx.recv_i, st["w2_q"], st["w2_s"], st["w2_gs"], ctx.group_offsets, peer.slab,
+                           st["moe_width"], False, status)
+    layer._mark(st, "experts_down")
+    st["offsets"][-1:] = ctx.group_offsets[-1:]             # rows computed on this rank (for the bench's FLOP count)
+    ops.peer_barrier(peer.flag_ptrs.data_ptr(), ctx.rank, ctx.world, status)      # all expert outputs are written
+    layer._mark(st, "barrier_outputs")
+    moe = ops.combine_peer(peer.slab_ptrs.data_ptr(), peer.cap, st["moe_width"], rowmap, tw, st["w_post_exp"],
+                           addend=shared)
+    layer._mark(st, "combine")
+    if st["pooled"]:
+        moe = ops.gemm(moe, st["unpooler"], status=status)
+        layer._mark(st, "gemm_unpooler")
+    return moe, ids
 
 
 def moe_stage(h, data, st, ctx: ExpertParallel):
@@ -169,7 +284,7 @@ def kernel_fn(data: dict, st: dict, ctx: ExpertParallel):
     s1, h = ops.boundary(a, None, data["stream"], st["a1"], st["b1"], st["w_pre_ffn"], layer.POST_NORM_EPS,
                          layer.RMS_EPS)
     layer._mark(st, "boundary_attn")
-    f, ids = moe_stage(h, data, st, ctx)
+    f, ids = (moe_stage_peer if ctx.peer is not None else moe_stage)(h, data, st, ctx)
     s2, hidden = ops.boundary(f, st["w_post_ffn"], s1, st["a2"], st["b2"], st["w_next"], layer.POST_NORM_EPS,
                               layer.RMS_EPS)
     layer._mark(st, "boundary_ffn")

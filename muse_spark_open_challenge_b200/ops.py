@@ -139,6 +139,46 @@ def combine(y, rowmap, weights, post_w, addend=None, out=None):
     return out
 
 
+def ep_plan(counts_all, rank, cap, dest_base, group_offsets, status):
+    """Row bases in the owners' slabs and this rank's (source, expert) group ranges from the
+    all-gathered route counts i32 [world, E]."""
+    _need(counts_all, torch.int32, "counts_all")
+    world, e = counts_all.shape
+    check(_lib.lib().msl_ep_plan(counts_all.data_ptr(), world, e // world, rank, cap, dest_base.data_ptr(),
+                                 group_offsets.data_ptr(), _ptr(status), _stream()), "msl_ep_plan")
+
+
+def peer_barrier(flag_bases, rank, world, status, timeout_ms=20000):
+    """Barrier over the ranks on the current stream (flag_bases: device array of flag-word pointers)."""
+    check(_lib.lib().msl_peer_barrier(int(flag_bases), rank, world, timeout_ms, _ptr(status), _stream()),
+          "msl_peer_barrier")
+
+
+def dispatch_peer(x, norm_w, ids, slots, dest_base, peer_bases, local_experts, cap, rowmap=None):
+    """Token rows written straight into the owning ranks' slabs (peer_bases: device array of slab
+    pointers, one per rank)."""
+    _need(x, torch.bfloat16, "x"), _need(ids, torch.int32, "ids"), _need(slots, torch.int32, "slots")
+    t, top_k = ids.shape
+    if rowmap is None:
+        rowmap = torch.empty((t, top_k), dtype=torch.int32, device=x.device)
+    check(_lib.lib().msl_dispatch_peer(x.data_ptr(), _rows(x, "x"), _ptr(norm_w), ids.data_ptr(), slots.data_ptr(),
+                                       dest_base.data_ptr(), int(peer_bases), local_experts, cap, t, top_k,
+                                       x.shape[1], rowmap.data_ptr(), _stream()), "msl_dispatch_peer")
+    return rowmap
+
+
+def combine_peer(peer_bases, cap, width, rowmap, weights, post_w, addend=None, out=None):
+    """`combine` with the expert outputs read from the owning ranks' slabs."""
+    _need(rowmap, torch.int32, "rowmap"), _need(weights, torch.float32, "weights")
+    t, top_k = rowmap.shape
+    if out is None:
+        out = torch.empty((t, width), dtype=torch.bfloat16, device=rowmap.device)
+    check(_lib.lib().msl_combine_peer(int(peer_bases), cap, rowmap.data_ptr(), weights.data_ptr(), post_w.data_ptr(),
+                                      _ptr(addend), 0 if addend is None else _rows(addend, "addend"), out.data_ptr(),
+                                      _rows(out, "out"), t, top_k, width, _stream()), "msl_combine_peer")
+    return out
+
+
 def nvfp4_repack(codes, scales, interleave):
     """Re-tile an NVFP4 bank (codes u8 [E, rows, k/2], scales e4m3 [E, rows, k/16]) for the grouped
     GEMM.  Returns (tiled codes u8, tiled scales u8, padded rows)."""

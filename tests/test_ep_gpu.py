@@ -1,5 +1,6 @@
 """Expert parallelism on real GPUs (needs >= 2): every rank runs its own requests, experts are
-sharded, rows travel by NCCL all-to-all; each rank's output must pass the reference's acceptance
+sharded, rows travel by NCCL all-to-all or - fused into the dispatch and combine kernels - by
+stores to and loads from the peers' memory; each rank's output must pass the reference's acceptance
 check against the CPU oracle evaluated with ALL experts local."""
 import dataclasses
 import os
@@ -49,6 +50,24 @@ def _worker(rank, world, port):
         v_rows = dev["v_cache"].view(-1, d.hkv, d.head_dim)[slots].cpu()
         ok, msg, _ = L.check_layer(data, weights, hidden.cpu(), stream.cpu(), ids.cpu(), k_rows, v_rows)
         assert ok, f"rank {rank}: {msg}"
+        # peer-memory transport: same rows, same order, same arithmetic -> identical bits
+        ep.enable_peer(ctx, st, max_tokens=hidden.shape[0], top_k=shape.top_k)
+        for _ in range(3):                                               # slab reuse across layers
+            hidden3, stream3, ids3 = ep.kernel_fn(dev, st, ctx)
+        torch.cuda.synchronize()
+        layer.check_status(st)
+        assert torch.equal(ids3, ids), f"rank {rank}: peer transport changed the routing"
+        assert torch.equal(hidden3, hidden) and torch.equal(stream3, stream), f"rank {rank}: peer transport differs"
+        # a slab too small for the routing is reported, not overrun
+        ctx.peer.cap_saved = ctx.peer.cap
+        ctx.peer.cap = 256
+        ep.kernel_fn(dev, st, ctx)
+        torch.cuda.synchronize()
+        with pytest.raises(Exception, match="out of range"):
+            layer.check_status(st)
+        st["status"].zero_()
+        ctx.peer.cap = ctx.peer.cap_saved
+        dist.barrier()
     finally:
         dist.destroy_process_group()
 
