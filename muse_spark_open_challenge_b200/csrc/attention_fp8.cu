@@ -28,6 +28,7 @@ namespace msl {
 constexpr int kAM = 128;    // rows per query sub-tile
 constexpr int kAN = 128;    // keys per tile
 constexpr int kAStages = 4;
+constexpr float kTau = 4.0f;   // log2 slack of the running softmax maximum before O is rescaled
 
 struct AttnArgs {
   const uint8_t* k_cache;       // [cache rows][hkv][D] e4m3
@@ -366,7 +367,7 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     const uint32_t tmem_s = tmem_base + sub * kAN + lane_sel;
     const uint32_t tmem_o = tmem_base + 2 * kAN + sub * kAN + lane_sel;
     uint8_t* sp = smem + S::kP + sub * (kAM * kAN);
-    float m_run = -INFINITY, l_run = 0.f;                  // l accumulates 2^8 * sum of exponentials
+    float m_run = -INFINITY, l_run = 0.f;                  // l accumulates 2^(8 - kTau) * sum of exponentials
     bool ok = true;
     for (int j = 0; j < n_mine && ok; ++j) {
       const uint32_t ph = j & 1;
@@ -396,10 +397,17 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         m_tile = row_max_half<true>(sa, sb, 0, lim_hi, lim_lo, m_tile);
         m_tile = row_max_half<true>(sc, sd, 64, lim_hi, lim_lo, m_tile);
       }
-      const float m_new = fmaxf(m_run, m_tile * scale_log2);
-      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      const float corr = ex2_approx(m_run - m_use);         // 0 when m_run = -inf
-      m_run = m_new;
+      // The reference maximum m_run moves only when the tile's maximum exceeds it by more than kTau
+      // (log2 units): the exponentials then stay below 2^kTau, P = 2^(8 - kTau) * exp2(.) stays within
+      // E4M3's range (<= 256), and the rescale of O in TMEM below becomes rare instead of per tile.
+      const float m_cand = m_tile * scale_log2;
+      float corr = 1.0f;
+      if (m_cand > m_run + kTau || m_run == -INFINITY) {
+        const float m_new = fmaxf(m_run, m_cand);
+        corr = ex2_approx(m_run - ((m_new == -INFINITY) ? 0.f : m_new));   // 0 when m_run = -inf
+        m_run = m_new;
+      }
+      const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
       // The previous tile's P V must have finished before O is rescaled or P overwritten.
       if (j > 0) {
         if (*abort_flag || !mbar_wait(&pv_done[sub], (j - 1) & 1)) { ok = false; break; }
@@ -418,8 +426,8 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         }
       }
       l_run *= corr;
-      // pass 2: P = 2^8 * exp2(s * scale - m) as E4M3, row sum in fp32
-      const float neg_m = 8.0f - m_use;
+      // pass 2: P = 2^(8 - kTau) * exp2(s * scale - m) as E4M3, row sum in fp32
+      const float neg_m = (8.0f - kTau) - m_use;
       float l_tile = 0.f;
       if (full_tile) {
         softmax_half<false>(sa, sb, scale_log2, neg_m, 0, lim_hi, lim_lo, l_tile, sp, r, 0);
@@ -440,7 +448,7 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     }
     if (ok && n_mine > 0) {
       tc_fence_after();
-      const float c_out = (*p.v_scale) / l_run;             // l_run carries the 2^8 of P
+      const float c_out = (*p.v_scale) / l_run;             // l_run carries the same power of two as P
       float r_norm = 1.0f;
       if (p.gate != nullptr) {
         float ss = 0.f;

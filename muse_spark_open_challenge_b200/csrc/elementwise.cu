@@ -2,6 +2,7 @@
 // the two residual boundaries, the router's top-k with slot assignment, token dispatch and the
 // weighted combine.  All use 128-bit global accesses and keep a row in registers so each tensor
 // crosses HBM once.
+#include <cstdlib>
 #include <mutex>
 
 #include "msl_common.cuh"
@@ -116,8 +117,8 @@ qk_rope_store_kernel(const __nv_bfloat16* __restrict__ qkv, int64_t ld, const in
 // ============================================================================ residual boundary
 // branch' = branch * branch_scale (optional); s_out = alpha * s_in + beta * rms(branch', eps_branch);
 // h_out = rms(s_out, eps_out) * norm_w.  One block per token row; the row stays in registers.
-template <int MAXC>
-__global__ void __launch_bounds__(256)
+template <int MAXC, int THREADS>
+__global__ void __launch_bounds__(THREADS)
 boundary_kernel(const __nv_bfloat16* __restrict__ branch, int64_t ld_branch, const float* __restrict__ branch_scale,
                 const float* __restrict__ s_in, const float* __restrict__ alpha, const float* __restrict__ beta,
                 const float* __restrict__ norm_w, float* __restrict__ s_out, __nv_bfloat16* __restrict__ h_out,
@@ -454,79 +455,111 @@ __global__ void peer_barrier_kernel(int* const* __restrict__ flag_bases, int ran
 }
 
 // ============================================================================ weighted combine
-// out[t] = sum_j w[t, j] * rms(y[rowmap[t, j]] * post_w, eps 1e-8)  (+ addend[t]); routes with
-// rowmap < 0 (another rank's expert) contribute nothing (reference.py:427-444).
-// One block per token.  The token's routed rows are copied global -> shared memory with 16-byte
-// asynchronous copies (no registers held while they are in flight, so several blocks per SM keep
-// enough bytes outstanding), then read twice from shared memory: once for the sums of squares,
-// once for the weighted accumulation.  Each row crosses HBM exactly once.
+// out[t] = sum_j w[t,j] * rms(y[rowmap[t,j]] * post_w, 1e-8) (+ addend[t]).  One block per token.  The
+// routes that have a slab row (rowmap >= 0; under the reference's sharding only the local experts'
+// routes do) are taken kStage at a time: their rows are brought into shared memory with asynchronous
+// copies (no registers held while they are in flight; the small footprint lets many blocks per SM keep
+// bytes outstanding), then read twice from shared memory: once for the sums of squares, once for the
+// weighted accumulation, which stays in registers across the rounds.  Each row crosses HBM exactly once.
 // With PEER the rows live in the expert-owning ranks' slabs: rowmap holds rank * peer_cap + row and the
 // row is read straight from that rank's memory (peer_bases[rank], NVLink) - the combine all-to-all of
 // expert parallelism fused into this kernel.
-template <int MAXK, bool PEER>
-__global__ void __launch_bounds__(512)
+constexpr int kCombineStage = 4;        // rows staged per round
+constexpr int kCombineThreads = 256;
+constexpr int kCombineMaxChunks = 4;    // 8-element chunks per thread: width <= 8192 (MAXC = 2: <= 4096)
+
+template <bool PEER, int MAXC>
+__global__ void __launch_bounds__(kCombineThreads, MAXC <= 2 ? 5 : 4)
 combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ rowmap, const float* __restrict__ w,
                const float* __restrict__ post_w, const __nv_bfloat16* __restrict__ addend, int64_t ld_add,
                __nv_bfloat16* __restrict__ out, int64_t ld_out, int top_k, int width,
                const __nv_bfloat16* const* __restrict__ peer_bases, int peer_cap) {
-  extern __shared__ __align__(16) uint8_t rows_smem[];      // [top_k][width] bf16
-  __shared__ float scratch[32 * MAXK];
+  extern __shared__ __align__(16) uint8_t rows_smem[];      // [kCombineStage][width] bf16
+  __shared__ float scratch[32 * kCombineStage];
+  __shared__ int route_of[32];
+  __shared__ int n_valid_s;
   const int t = blockIdx.x;
   const int chunks = width / 8;
-  uint32_t valid = 0;                                       // bit j: route j has a slab row
-  for (int j = 0; j < top_k; ++j) {
-    const int row = rowmap[t * top_k + j];
-    if (row >= 0) {
-      valid |= 1u << j;
+  if (threadIdx.x == 0) {                                   // compact the routes that have a row, in route order
+    int n = 0;
+    for (int j = 0; j < top_k; ++j)
+      if (rowmap[t * top_k + j] >= 0) route_of[n++] = j;
+    n_valid_s = n;
+  }
+  __syncthreads();
+  const int n_valid = n_valid_s;
+  float acc[MAXC][8];
+#pragma unroll
+  for (int c = 0; c < MAXC; ++c) {
+    const int ch = threadIdx.x + c * kCombineThreads;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[c][i] = 0.f;
+    if (addend != nullptr && ch < chunks) unpack8(*reinterpret_cast<const uint4*>(addend + t * ld_add + ch * 8), acc[c]);
+  }
+  for (int base = 0; base < n_valid; base += kCombineStage) {
+    const int n_round = min(kCombineStage, n_valid - base);
+    for (int q = 0; q < n_round; ++q) {
+      const int row = rowmap[t * top_k + route_of[base + q]];
       const __nv_bfloat16* src = PEER ? peer_bases[row / peer_cap] + static_cast<int64_t>(row % peer_cap) * width
                                       : y + static_cast<int64_t>(row) * width;
-      for (int ch = threadIdx.x; ch < chunks; ch += blockDim.x) {
-        const uint32_t dst = smem_u32(rows_smem + (static_cast<size_t>(j) * width + ch * 8) * 2);
+      for (int ch = threadIdx.x; ch < chunks; ch += kCombineThreads) {
+        const uint32_t dst = smem_u32(rows_smem + (static_cast<size_t>(q) * width + ch * 8) * 2);
         asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src + ch * 8) : "memory");
       }
     }
-  }
-  asm volatile("cp.async.commit_group;" ::: "memory");
-  asm volatile("cp.async.wait_group 0;" ::: "memory");
-  __syncthreads();
-  float ss[MAXK];
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    float ss[kCombineStage];
 #pragma unroll
-  for (int j = 0; j < MAXK; ++j) ss[j] = 0.f;
-  for (int ch = threadIdx.x; ch < chunks; ch += blockDim.x) {
-    const float4 w0 = *reinterpret_cast<const float4*>(post_w + ch * 8);
-    const float4 w1 = *reinterpret_cast<const float4*>(post_w + ch * 8 + 4);
-    const float pw[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+    for (int q = 0; q < kCombineStage; ++q) ss[q] = 0.f;
 #pragma unroll
-    for (int j = 0; j < MAXK; ++j) {
-      if (valid & (1u << j)) {
-        float v[8];
-        unpack8(*reinterpret_cast<const uint4*>(rows_smem + (static_cast<size_t>(j) * width + ch * 8) * 2), v);
+    for (int c = 0; c < MAXC; ++c) {
+      const int ch = threadIdx.x + c * kCombineThreads;
+      if (ch < chunks) {
+        const float4 w0 = *reinterpret_cast<const float4*>(post_w + ch * 8);
+        const float4 w1 = *reinterpret_cast<const float4*>(post_w + ch * 8 + 4);
+        const float pw[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
-        for (int i = 0; i < 8; ++i) { const float x = v[i] * pw[i]; ss[j] += x * x; }
+        for (int q = 0; q < kCombineStage; ++q) {
+          if (q < n_round) {
+            float v[8];
+            unpack8(*reinterpret_cast<const uint4*>(rows_smem + (static_cast<size_t>(q) * width + ch * 8) * 2), v);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { const float x = v[i] * pw[i]; ss[q] += x * x; }
+          }
+        }
       }
     }
-  }
-  block_sum<MAXK>(ss, scratch);
-  float r[MAXK];
+    block_sum<kCombineStage>(ss, scratch);
+    float r[kCombineStage];
 #pragma unroll
-  for (int j = 0; j < MAXK; ++j)
-    r[j] = (valid & (1u << j)) ? w[t * top_k + j] / sqrtf(ss[j] / width + 1e-8f) : 0.f;
-  for (int ch = threadIdx.x; ch < chunks; ch += blockDim.x) {
-    const float4 w0 = *reinterpret_cast<const float4*>(post_w + ch * 8);
-    const float4 w1 = *reinterpret_cast<const float4*>(post_w + ch * 8 + 4);
-    const float pw[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    if (addend != nullptr) unpack8(*reinterpret_cast<const uint4*>(addend + t * ld_add + ch * 8), acc);
+    for (int q = 0; q < kCombineStage; ++q)
+      r[q] = q < n_round ? w[t * top_k + route_of[base + q]] / sqrtf(ss[q] / width + 1e-8f) : 0.f;
 #pragma unroll
-    for (int j = 0; j < MAXK; ++j) {
-      if (valid & (1u << j)) {
-        float v[8];
-        unpack8(*reinterpret_cast<const uint4*>(rows_smem + (static_cast<size_t>(j) * width + ch * 8) * 2), v);
+    for (int c = 0; c < MAXC; ++c) {
+      const int ch = threadIdx.x + c * kCombineThreads;
+      if (ch < chunks) {
+        const float4 w0 = *reinterpret_cast<const float4*>(post_w + ch * 8);
+        const float4 w1 = *reinterpret_cast<const float4*>(post_w + ch * 8 + 4);
+        const float pw[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] += v[i] * pw[i] * r[j];
+        for (int q = 0; q < kCombineStage; ++q) {
+          if (q < n_round) {
+            float v[8];
+            unpack8(*reinterpret_cast<const uint4*>(rows_smem + (static_cast<size_t>(q) * width + ch * 8) * 2), v);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[c][i] += v[i] * pw[i] * r[q];
+          }
+        }
       }
     }
-    *reinterpret_cast<uint4*>(out + t * ld_out + ch * 8) = pack8(acc);
+    __syncthreads();                                        // the staging rows are free for the next round
+  }
+#pragma unroll
+  for (int c = 0; c < MAXC; ++c) {
+    const int ch = threadIdx.x + c * kCombineThreads;
+    if (ch < chunks) *reinterpret_cast<uint4*>(out + t * ld_out + ch * 8) = pack8(acc[c]);
   }
 }
 
@@ -570,23 +603,33 @@ extern "C" int msl_boundary(const void* branch, int64_t ld_branch, const float* 
                             float eps_out, void* stream) {
   if (!branch || !stream_in || !alpha || !beta || !norm_w || !stream_out || !hidden_out) return MSL_ERR_ARG;
   if (tokens < 0 || hidden <= 0 || (hidden & 7) || (ld_branch & 7) || (ld_hidden & 7)) return MSL_ERR_ALIGN;
-  if (hidden > 8 * 256 * 4) return MSL_ERR_UNSUPPORTED;
+  if (hidden > 8 * 1024 * 4) return MSL_ERR_UNSUPPORTED;
   if (tokens == 0) return MSL_OK;
   const int chunks = hidden / 8;
-  int threads = std::min(256, ((chunks + 31) / 32) * 32);
-  const int per = (chunks + threads - 1) / threads;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   auto* b = static_cast<const __nv_bfloat16*>(branch);
   auto* h = static_cast<__nv_bfloat16*>(hidden_out);
-  if (per <= 1)
-    boundary_kernel<1><<<tokens, threads, 0, st>>>(b, ld_branch, branch_scale, stream_in, alpha, beta, norm_w,
-                                                   stream_out, h, ld_hidden, hidden, eps_branch, eps_out);
-  else if (per <= 2)
-    boundary_kernel<2><<<tokens, threads, 0, st>>>(b, ld_branch, branch_scale, stream_in, alpha, beta, norm_w,
-                                                   stream_out, h, ld_hidden, hidden, eps_branch, eps_out);
-  else
-    boundary_kernel<4><<<tokens, threads, 0, st>>>(b, ld_branch, branch_scale, stream_in, alpha, beta, norm_w,
-                                                   stream_out, h, ld_hidden, hidden, eps_branch, eps_out);
+  // Rows wider than 4096 spread over more threads rather than more registers per thread.
+  int want = chunks <= 512 ? 256 : (chunks <= 1024 ? 512 : 1024);
+  if (const char* e = getenv("MSL_BOUNDARY_THREADS")) want = atoi(e);
+#define MSL_BOUNDARY(MAXC, THREADS)                                                                              \
+  boundary_kernel<MAXC, THREADS><<<tokens, std::min(THREADS, ((chunks + 31) / 32) * 32), 0, st>>>(               \
+      b, ld_branch, branch_scale, stream_in, alpha, beta, norm_w, stream_out, h, ld_hidden, hidden, eps_branch,  \
+      eps_out)
+  if (want >= 1024) {
+    if (chunks <= 1024) MSL_BOUNDARY(1, 1024);
+    else if (chunks <= 2048) MSL_BOUNDARY(2, 1024);
+    else MSL_BOUNDARY(4, 1024);
+  } else if (want >= 512) {
+    if (chunks <= 512) MSL_BOUNDARY(1, 512);
+    else if (chunks <= 1024) MSL_BOUNDARY(2, 512);
+    else MSL_BOUNDARY(4, 512);
+  } else {
+    if (chunks <= 256) MSL_BOUNDARY(1, 256);
+    else if (chunks <= 512) MSL_BOUNDARY(2, 256);
+    else MSL_BOUNDARY(4, 256);
+  }
+#undef MSL_BOUNDARY
   return cudaGetLastError() == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
 }
 
@@ -634,41 +677,37 @@ static int combine_launch(const void* y, const int* rowmap, const float* weights
                           const void* addend, int64_t ld_addend, void* out, int64_t ld_out, int tokens, int top_k,
                           int width, const void* const* peer_bases, int peer_cap, void* stream) {
   if ((!y && !peer_bases) || !rowmap || !weights || !post_w || !out) return MSL_ERR_ARG;
-  if (tokens < 0 || top_k <= 0 || top_k > 8 || width <= 0) return MSL_ERR_ARG;
+  if (tokens < 0 || top_k <= 0 || top_k > 32 || width <= 0) return MSL_ERR_ARG;
   if ((width & 7) || (ld_out & 7) || (ld_addend & 7)) return MSL_ERR_ALIGN;
-  if (static_cast<int64_t>(top_k) * width * 2 > 200 * 1024) return MSL_ERR_UNSUPPORTED;   // rows staged in smem
+  if (width > 8 * kCombineThreads * kCombineMaxChunks) return MSL_ERR_UNSUPPORTED;
   if (tokens == 0) return MSL_OK;
-  const int threads = std::min(512, ((width / 8 + 31) / 32) * 32);
-  const int smem = top_k * width * 2;
-  static int configured = 0;       // largest dynamic shared-memory size set so far
-  if (smem > 48 * 1024 && smem > configured) {
-    if (cudaFuncSetAttribute(combine_kernel<4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
-        cudaFuncSetAttribute(combine_kernel<8, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
-        cudaFuncSetAttribute(combine_kernel<4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
-        cudaFuncSetAttribute(combine_kernel<8, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+  const int smem = kCombineStage * width * 2;               // <= 64 KB
+  static bool configured = false;
+  if (!configured) {
+    const int most = kCombineStage * 8 * kCombineThreads * kCombineMaxChunks * 2;
+    if (cudaFuncSetAttribute(combine_kernel<false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, most) != cudaSuccess ||
+        cudaFuncSetAttribute(combine_kernel<true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, most) != cudaSuccess ||
+        cudaFuncSetAttribute(combine_kernel<false, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, most) != cudaSuccess ||
+        cudaFuncSetAttribute(combine_kernel<true, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, most) != cudaSuccess)
       return MSL_ERR_CUDA;
-    configured = smem;
+    configured = true;
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   auto* yy = static_cast<const __nv_bfloat16*>(y);
   auto* ad = static_cast<const __nv_bfloat16*>(addend);
   auto* oo = static_cast<__nv_bfloat16*>(out);
   auto* pb = reinterpret_cast<const __nv_bfloat16* const*>(peer_bases);
+  const bool narrow = width <= 8 * kCombineThreads * 2;
+  if (pb != nullptr && peer_cap <= 0) return MSL_ERR_ARG;
+#define MSL_COMBINE(PEER, MAXC)                                                                                   \
+  combine_kernel<PEER, MAXC><<<tokens, kCombineThreads, smem, st>>>(yy, rowmap, weights, post_w, ad, ld_addend, oo, \
+                                                                    ld_out, top_k, width, pb, pb ? peer_cap : 1)
   if (pb != nullptr) {
-    if (peer_cap <= 0) return MSL_ERR_ARG;
-    if (top_k <= 4)
-      combine_kernel<4, true><<<tokens, threads, smem, st>>>(yy, rowmap, weights, post_w, ad, ld_addend, oo, ld_out,
-                                                             top_k, width, pb, peer_cap);
-    else
-      combine_kernel<8, true><<<tokens, threads, smem, st>>>(yy, rowmap, weights, post_w, ad, ld_addend, oo, ld_out,
-                                                             top_k, width, pb, peer_cap);
-  } else if (top_k <= 4) {
-    combine_kernel<4, false><<<tokens, threads, smem, st>>>(yy, rowmap, weights, post_w, ad, ld_addend, oo, ld_out,
-                                                            top_k, width, nullptr, 1);
+    if (narrow) MSL_COMBINE(true, 2); else MSL_COMBINE(true, 4);
   } else {
-    combine_kernel<8, false><<<tokens, threads, smem, st>>>(yy, rowmap, weights, post_w, ad, ld_addend, oo, ld_out,
-                                                            top_k, width, nullptr, 1);
+    if (narrow) MSL_COMBINE(false, 2); else MSL_COMBINE(false, 4);
   }
+#undef MSL_COMBINE
   return cudaGetLastError() == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
 }
 
