@@ -213,7 +213,7 @@ def moe_stage_peer(h, data, st, ctx: ExpertParallel):
                            addend=shared)
     layer._mark(st, "combine")
     if st["pooled"]:
-        moe = ops.gemm(moe, st["unpooler"], status=status)
+        moe = layer.unpool(moe, st)
         layer._mark(st, "gemm_unpooler")
     return moe, ids
 
@@ -270,7 +270,7 @@ def moe_stage(h, data, st, ctx: ExpertParallel):
     moe = ops.combine(send_x, rowmap, tw, st["w_post_exp"], addend=shared)
     layer._mark(st, "combine")
     if st["pooled"]:
-        moe = ops.gemm(moe, st["unpooler"], status=status)
+        moe = layer.unpool(moe, st)
         layer._mark(st, "gemm_unpooler")
     return moe, ids
 

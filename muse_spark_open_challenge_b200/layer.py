@@ -200,9 +200,26 @@ def moe_stage(h, data, st):
     moe = ops.combine(slab_x, rowmap, tw, st["w_post_exp"], addend=shared)
     _mark(st, "combine")
     if st["pooled"]:
-        moe = ops.gemm(moe, st["unpooler"], status=status)
+        moe = unpool(moe, st)
         _mark(st, "gemm_unpooler")
     return moe, ids
+
+
+SLICED_MAX_TOKENS = 8          # reference.py:58
+
+
+def unpool(moe, st):
+    """MoE width back to the hidden size.  Up to 8 tokens (decode steps, verify blocks) this GPU forms
+    only its first hidden/8 columns and leaves the rest zero, as the reference does
+    (reference.py:56-58,468-470: the all-gather it stands for is the identity there)."""
+    tokens = moe.shape[0]
+    if tokens > SLICED_MAX_TOKENS:
+        return ops.gemm(moe, st["unpooler"], status=st["status"])
+    hidden = st["unpooler"].shape[0]
+    cols = hidden // 8
+    f = torch.zeros((tokens, hidden), dtype=torch.bfloat16, device=moe.device)
+    ops.gemm(moe, st["unpooler"][:cols], out=f[:, :cols], status=st["status"])
+    return f
 
 
 def kernel_fn(data: dict, st: dict):

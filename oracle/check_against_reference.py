@@ -32,6 +32,11 @@ CASES = [
     ("tiny", dict(batch=2, ctx=300, layer="sliding", q_len=300, page=16, seed=3, spread="agentic", dist="soft")),
     ("d128", dict(batch=2, ctx=70, layer="full", q_len=90, page=64, seed=4, local_start=8)),
     ("d128", dict(batch=1, ctx=200, layer="sliding", q_len=130, page=1, seed=5, local_start=24, kv_scale=0.5)),
+    # decode steps and verify blocks; up to 8 tokens take the sliced unpooler (reference.py:468-470)
+    ("tiny", dict(batch=4, ctx=200, layer="full", q_len=1, page=64, seed=6)),
+    ("tiny", dict(batch=1, ctx=150, layer="sliding", q_len=8, page=16, seed=7, kv_scale=1 / 64)),
+    ("tiny", dict(batch=3, ctx=120, layer="sliding", q_len=8, page=64, seed=8)),
+    ("d128", dict(batch=9, ctx=90, layer="full", q_len=1, page=64, seed=9, local_start=16)),
 ]
 
 

@@ -28,6 +28,7 @@ RMS_EPS = 1e-5            # reference.py:38
 POST_NORM_EPS = 1e-8      # reference.py:39
 ROUTER_MULTIPLIER = 0.1767766952966369   # reference.py:51
 ROUTE_EPS = 1e-15         # reference.py:53
+SLICED_MAX_TOKENS = 8      # reference.py:58
 RESIDUAL_TEMPERATURE = 0.3   # reference.py:54
 RESIDUAL_GATE_EPS = 1e-3     # reference.py:55
 QUERY_CHUNK = 2048
@@ -281,7 +282,12 @@ def moe_block(h, scores, ids, local_start, weights, d: Dims):
     if d.shared_inter:
         moe = moe + shared_expert(p, weights, d)
     if d.pooled:
-        # the sliced form for <= 8 tokens (reference.py:468-470) never occurs at prefill
+        if len(moe) <= SLICED_MAX_TOKENS:
+            # decode / verify blocks: this GPU forms only its hidden/8 columns (reference.py:56-58,468-470)
+            cols = d.hidden // 8
+            f = torch.zeros((len(moe), d.hidden), dtype=moe.dtype)
+            f[:, :cols] = moe @ weights["unpooler"][:cols].float().T
+            return f
         return moe @ weights["unpooler"].float().T
     return moe
 

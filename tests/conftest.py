@@ -42,7 +42,8 @@ def load_golden_case(name):
     return g, load_golden_weights(shape_name)
 
 
-GOLDEN_CASES = ["case_tiny_full", "case_tiny_sliding", "case_tiny_page1", "case_d128_ep"]
+GOLDEN_CASES = ["case_tiny_full", "case_tiny_sliding", "case_tiny_page1", "case_d128_ep", "case_tiny_decode",
+                "case_tiny_verify"]
 
 
 def to_device(obj, device):

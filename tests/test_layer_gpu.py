@@ -100,6 +100,10 @@ SYNTH_CASES = [
     ("MID_SMALL", [300, 211], [0, 130], 64, 1 / 64, 0),
     ("EP_SMALL", [257], [64], 64, 1.0, 32),
     ("TINY", [5, 64, 1, 130], [0, 3, 700, 64], 16, 0.25, 0),
+    # decode steps (one new token per request) and verify blocks (eight)
+    ("MID_DECODE", [1, 1, 1, 1, 1, 1], [200, 37, 64, 5, 130, 1000], 64, 1 / 64, 0),
+    ("MID_VERIFY", [8, 8, 8], [0, 300, 63], 64, 1 / 64, 0),
+    ("NATIVE_DECODE", [1, 1, 1], [2500, 77, 300], 64, 1.0, 224),
 ]
 
 
@@ -118,6 +122,8 @@ def test_layer_on_synthetic_shapes(case):
         "EP_SMALL": dataclasses.replace(synth.MID, hidden=1024, hq=8, hkv=2, n_experts=64, local_experts=16,
                                         moe_width=1024, inter=256, shared_inter=0),
     }
+    shapes["MID_DECODE"] = shapes["MID_VERIFY"] = shapes["MID_SMALL"]
+    shapes["NATIVE_DECODE"] = shapes["NATIVE_SLIDING"]
     shape = shapes[name]
     weights = synth.make_weights(shape, seed=7)
     data = synth.make_input(shape, lens, ctxs, seed=8, page=page, kv_scale=kv_scale, local_start=local_start)
