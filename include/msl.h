@@ -194,6 +194,24 @@ int msl_attention_fp8(const void* q8, const void* k_cache, const void* v_cache, 
                       int hkv, int head_dim, int page_size, int window, int64_t cache_rows, void* out,
                       int64_t ld_out, const void* gate, int64_t ld_gate, int* status, void* stream);
 
+/* Split-KV form of msl_attention_fp8 for short query blocks over long cached contexts (continuation
+ * chunks, verify blocks, decode steps), where the query blocks alone cannot fill the GPU: every query
+ * block's key tiles are cut into kv_splits slices, each slice runs as its own CTA and leaves an
+ * unnormalised partial result (O, running maximum, row sum) in `workspace`, and a second kernel merges
+ * the slices and applies the same epilogue.  Stands where the reference cuts long contexts into splits
+ * and merges them (submission.py:649-697: pick_splits, split attn_fwd launches; :610 _attn_combine_kernel).
+ * msl_attention_split_plan recommends a slice count from the sizes alone (1 = use msl_attention_fp8);
+ * msl_attention_split_workspace gives the workspace size in bytes (device memory, 16-byte aligned,
+ * owned by the caller, no initialisation needed). */
+int msl_attention_split_plan(int batch, int max_q_len, int hq, int hkv, int max_pages, int page_size, int window);
+int64_t msl_attention_split_workspace(int kv_splits, int tokens, int hq, int head_dim);
+int msl_attention_fp8_split(const void* q8, const void* k_cache, const void* v_cache, const int* page_table,
+                            int max_pages, const int* seq_lens, const int* cu_seqlens_q, const float* k_scale,
+                            const float* v_scale, float softmax_scale, int batch, int max_q_len, int tokens, int hq,
+                            int hkv, int head_dim, int page_size, int window, int64_t cache_rows, void* out,
+                            int64_t ld_out, const void* gate, int64_t ld_gate, int kv_splits, void* workspace,
+                            int* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

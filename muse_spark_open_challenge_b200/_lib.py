@@ -37,6 +37,10 @@ SIGNATURES = {
     "msl_grouped_gemm_nvfp4": (_i, [_p, _i64, _p, _p, _p, _p, _p, _i64, _i, _i, _i, _i, _i, _i, _p, _p]),
     "msl_attention_fp8": (_i, [_p, _p, _p, _p, _i, _p, _p, _p, _p, _f, _i, _i, _i, _i, _i, _i, _i, _i, _i64, _p,
                                _i64, _p, _i64, _p, _p]),
+    "msl_attention_split_plan": (_i, [_i, _i, _i, _i, _i, _i, _i]),
+    "msl_attention_split_workspace": (_i64, [_i, _i, _i, _i]),
+    "msl_attention_fp8_split": (_i, [_p, _p, _p, _p, _i, _p, _p, _p, _p, _f, _i, _i, _i, _i, _i, _i, _i, _i, _i64, _p,
+                                     _i64, _p, _i64, _i, _p, _p, _p]),
 }
 
 

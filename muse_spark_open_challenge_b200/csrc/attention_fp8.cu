@@ -47,6 +47,12 @@ struct AttnArgs {
   const __nv_bfloat16* gate;    // bf16, row pitch ld_gate, column h * D + d; NULL = no norm/gate epilogue
   int64_t ld_gate;
   int* status;
+  // Split-KV mode (kv_splits > 1): every CTA covers one slice of its query block's key tiles and
+  // leaves an unnormalised partial result for merge_splits_kernel.
+  int kv_splits;
+  int tokens;
+  float* part_o;                // [kv_splits][tokens][hq][D] fp32, relative to the slice's own maximum
+  float* part_ml;               // [kv_splits][tokens][hq][2]: running maximum (log2 units), row sum
 };
 
 template <int D>
@@ -56,7 +62,7 @@ struct AttnSmem {
   static constexpr int kP = 2 * kTile;                     // 2 x (128 x 128 bytes)
   static constexpr int kKV = kP + 2 * kAM * kAN;           // stages of (K tile, V tile)
   static constexpr int kBar = kKV + kAStages * 2 * kTile;
-  // q_full, kv_full[4], kv_empty[4], s_full[2], s_free[2], p_full[2], pv_done[2]
+  // q_full, kv_full[stages], kv_empty[stages], s_full[2], s_free[2], p_full[2], pv_done[2]
   static constexpr int kNumBars = 1 + 2 * kAStages + 8;
   static constexpr int kTotal = kBar + kNumBars * 8 + 16;
 };
@@ -104,6 +110,7 @@ __device__ __forceinline__ void softmax_half(const uint32_t (&s0)[32], const uin
   for (int h = 0; h < 2; ++h) {
     const uint32_t(&s)[32] = h ? s1 : s0;
     float e[32];
+    float part[4] = {0.f, 0.f, 0.f, 0.f};                  // independent chains
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
       float x = fmaf(__uint_as_float(s[i]), scale_log2, neg_m);
@@ -112,8 +119,9 @@ __device__ __forceinline__ void softmax_half(const uint32_t (&s0)[32], const uin
         if (!(col <= lim_hi && col > lim_lo)) x = -INFINITY;
       }
       e[i] = ex2_approx(x);
-      l += e[i];
+      part[i & 3] += e[i];
     }
+    l += (part[0] + part[1]) + (part[2] + part[3]);
 #pragma unroll
     for (int q = 0; q < 2; ++q) {
       const uint4 packed = make_uint4(e4m3x4(e[16 * q + 0], e[16 * q + 1], e[16 * q + 2], e[16 * q + 3]),
@@ -169,12 +177,13 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   const int q_begin = p.cu_seqlens_q[b], q_len = p.cu_seqlens_q[b + 1] - q_begin;
   // Longest key ranges first: later query blocks attend to more keys.
   const int n_qblk = (q_len + 2 * TQ - 1) / (2 * TQ);
-  const int qblk = n_qblk - 1 - static_cast<int>(blockIdx.x);
+  const int split = static_cast<int>(blockIdx.x) % p.kv_splits;
+  const int qblk = n_qblk - 1 - static_cast<int>(blockIdx.x) / p.kv_splits;
   if (qblk < 0) return;                                    // uniform for the CTA, before any barrier
   const int q0 = qblk * 2 * TQ;
   const int seq = p.seq_lens[b];
   const int min_qpos = seq + q0;
-  const int kt_begin = p.window ? max(0, min_qpos - p.window + 1) / kAN : 0;
+  int kt_begin = p.window ? max(0, min_qpos - p.window + 1) / kAN : 0;
   // per sub-tile: valid rows, last query position, number of key tiles
   int rows_valid[2], max_qpos[2], n_sub[2];
 #pragma unroll
@@ -184,6 +193,27 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     rows_valid[s] = cnt * G;
     max_qpos[s] = seq + first + cnt - 1;
     n_sub[s] = cnt > 0 ? max_qpos[s] / kAN + 1 - kt_begin : 0;
+  }
+  if (p.kv_splits > 1) {
+    // this CTA's slice of the key tiles; a slice may be empty for one or both sub-tiles
+    const int n_full = max(n_sub[0], n_sub[1]);
+    const int chunk = (n_full + p.kv_splits - 1) / p.kv_splits;
+    const int lo = split * chunk, hi = min(n_full, lo + chunk);
+#pragma unroll
+    for (int s = 0; s < 2; ++s) n_sub[s] = max(0, min(n_sub[s], hi) - lo);
+    kt_begin += lo;
+    if (max(n_sub[0], n_sub[1]) == 0) {                    // uniform for the CTA, before any barrier
+      for (int i = threadIdx.x; i < 2 * kAM; i += blockDim.x) {
+        const int s = i / kAM, r = i % kAM;
+        if (r < rows_valid[s]) {
+          const int64_t idx = (static_cast<int64_t>(split) * p.tokens + q_begin + q0 + s * TQ + r / G) * p.hq +
+                              kvh * G + r % G;
+          p.part_ml[2 * idx] = -INFINITY;
+          p.part_ml[2 * idx + 1] = 0.f;
+        }
+      }
+      return;
+    }
   }
   const int n_tiles = max(n_sub[0], n_sub[1]);
   const int last_qpos = max(max_qpos[0], max_qpos[1]);
@@ -408,7 +438,7 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         m_run = m_new;
       }
       const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
-      // The previous tile's P V must have finished before O is rescaled or P overwritten.
+      // The previous tile's P V must have finished before P is overwritten (or O rescaled).
       if (j > 0) {
         if (*abort_flag || !mbar_wait(&pv_done[sub], (j - 1) & 1)) { ok = false; break; }
         tc_fence_after();
@@ -446,7 +476,31 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     if (ok && n_mine > 0) {
       if (*abort_flag || !mbar_wait(&pv_done[sub], (n_mine - 1) & 1)) ok = false;
     }
-    if (ok && n_mine > 0) {
+    if (p.kv_splits > 1) {
+      // partial result of this key slice: O as it stands in TMEM, with the maximum and sum it refers to
+      const bool have = ok && n_mine > 0;
+      if (have) tc_fence_after();
+      const int64_t idx = (static_cast<int64_t>(split) * p.tokens + q_begin + first_tok + tq) * p.hq + kvh * G + g;
+      if (row_valid) {
+        p.part_ml[2 * idx] = have ? m_run : -INFINITY;
+        p.part_ml[2 * idx + 1] = have ? l_run : 0.f;
+      }
+      if (have) {
+#pragma unroll 1
+        for (int c = 0; c < D; c += 32) {
+          uint32_t o[32];
+          tmem_ld32(tmem_o + c, o);
+          tmem_ld_wait();
+          if (row_valid) {
+            float4* dst = reinterpret_cast<float4*>(p.part_o + idx * D + c);
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              dst[i] = make_float4(__uint_as_float(o[4 * i]), __uint_as_float(o[4 * i + 1]),
+                                   __uint_as_float(o[4 * i + 2]), __uint_as_float(o[4 * i + 3]));
+          }
+        }
+      }
+    } else if (ok && n_mine > 0) {
       tc_fence_after();
       const float c_out = (*p.v_scale) / l_run;             // l_run carries the same power of two as P
       float r_norm = 1.0f;
@@ -508,6 +562,58 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   }
 }
 
+// Merge of the key slices of split-KV attention: one warp per (token, head).  Slice s holds O_s and
+// l_s relative to its own maximum m_s (log2 units); with M = max m_s the result is
+// sum_s O_s 2^(m_s - M) / sum_s l_s 2^(m_s - M), then v_scale, the per-head RMS norm and the sigmoid
+// gate exactly as in the single-pass epilogue.
+template <int D>
+__global__ void __launch_bounds__(256)
+merge_splits_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, int kv_splits, int tokens,
+                    int hq, const float* __restrict__ v_scale, const __nv_bfloat16* __restrict__ gate,
+                    int64_t ld_gate, __nv_bfloat16* __restrict__ out, int64_t ld_out) {
+  constexpr int PER = D / 32;
+  const int lane = threadIdx.x & 31;
+  const int64_t item = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= static_cast<int64_t>(tokens) * hq) return;
+  const int64_t token = item / hq;
+  const int head = static_cast<int>(item % hq);
+  float m_all = -INFINITY;
+  for (int s = 0; s < kv_splits; ++s) {
+    const float* ml = part_ml + 2 * (static_cast<int64_t>(s) * tokens * hq + item);
+    if (ml[1] > 0.f) m_all = fmaxf(m_all, ml[0]);
+  }
+  float acc[PER], l_all = 0.f;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) acc[i] = 0.f;
+  for (int s = 0; s < kv_splits; ++s) {
+    const int64_t at = static_cast<int64_t>(s) * tokens * hq + item;
+    const float l_s = part_ml[2 * at + 1];
+    if (l_s > 0.f) {
+      const float w = ex2_approx(part_ml[2 * at] - m_all);
+      l_all += l_s * w;
+      const float* o = part_o + at * D + lane * PER;
+#pragma unroll
+      for (int i = 0; i < PER; ++i) acc[i] += o[i] * w;
+    }
+  }
+  const float c_out = (*v_scale) / l_all;
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) { acc[i] *= c_out; ss += acc[i] * acc[i]; }
+  __nv_bfloat16* orow = out + token * ld_out + head * D + lane * PER;
+  if (gate != nullptr) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+    const float r_norm = 1.0f / sqrtf(ss / D + 1e-5f);
+    const __nv_bfloat16* grow = gate + token * ld_gate + head * D + lane * PER;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) acc[i] *= r_norm * (1.0f / (1.0f + __expf(-__bfloat162float(grow[i]))));
+  }
+#pragma unroll
+  for (int i = 0; i < PER; i += 2)
+    *reinterpret_cast<uint32_t*>(orow + i) = pack_bf16x2(acc[i], acc[i + 1]);
+}
+
 template <int D>
 static int launch_attention(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnArgs& a,
                             int batch, int max_q_len, cudaStream_t st) {
@@ -521,8 +627,14 @@ static int launch_attention(const CUtensorMap& tq, const CUtensorMap& tk, const 
     configured = true;
   }
   const int G = a.hq / a.hkv, TQ2 = 2 * (kAM / G);
-  dim3 grid((max_q_len + TQ2 - 1) / TQ2, a.hkv, batch);
+  dim3 grid(((max_q_len + TQ2 - 1) / TQ2) * a.kv_splits, a.hkv, batch);
   attention_fp8_kernel<D><<<grid, 384, smem, st>>>(tq, tk, tv, a);
+  if (a.kv_splits > 1) {
+    const int64_t items = static_cast<int64_t>(a.tokens) * a.hq;
+    merge_splits_kernel<D><<<static_cast<unsigned>((items + 7) / 8), 256, 0, st>>>(
+        a.part_o, a.part_ml, a.kv_splits, a.tokens, a.hq, a.v_scale, a.gate, a.ld_gate,
+        static_cast<__nv_bfloat16*>(a.out), a.ld_out);
+  }
   return cudaGetLastError() == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
 }
 
@@ -530,12 +642,14 @@ static int launch_attention(const CUtensorMap& tq, const CUtensorMap& tk, const 
 
 using namespace msl;
 
-extern "C" int msl_attention_fp8(const void* q8, const void* k_cache, const void* v_cache, const int* page_table,
-                                 int max_pages, const int* seq_lens, const int* cu_seqlens_q, const float* k_scale,
-                                 const float* v_scale, float softmax_scale, int batch, int max_q_len, int tokens,
-                                 int hq, int hkv, int head_dim, int page_size, int window, int64_t cache_rows,
-                                 void* out, int64_t ld_out, const void* gate, int64_t ld_gate, int* status,
-                                 void* stream) {
+static int attention_entry(const void* q8, const void* k_cache, const void* v_cache, const int* page_table,
+                           int max_pages, const int* seq_lens, const int* cu_seqlens_q, const float* k_scale,
+                           const float* v_scale, float softmax_scale, int batch, int max_q_len, int tokens, int hq,
+                           int hkv, int head_dim, int page_size, int window, int64_t cache_rows, void* out,
+                           int64_t ld_out, const void* gate, int64_t ld_gate, int kv_splits, void* workspace,
+                           int* status, void* stream) {
+  if (kv_splits < 1 || kv_splits > 64 || (kv_splits > 1 && !workspace)) return MSL_ERR_ARG;
+  if (kv_splits > 1 && (reinterpret_cast<uintptr_t>(workspace) & 15)) return MSL_ERR_ALIGN;
   if (!q8 || !k_cache || !v_cache || !page_table || !seq_lens || !cu_seqlens_q || !k_scale || !v_scale || !out)
     return MSL_ERR_ARG;
   if (batch <= 0 || max_q_len <= 0 || tokens <= 0 || hq <= 0 || hkv <= 0 || hq % hkv || page_size <= 0 ||
@@ -550,7 +664,11 @@ extern "C" int msl_attention_fp8(const void* q8, const void* k_cache, const void
     return MSL_ERR_ALIGN;
   AttnArgs a{static_cast<const uint8_t*>(k_cache), static_cast<const uint8_t*>(v_cache), page_table, max_pages,
              seq_lens, cu_seqlens_q, k_scale, v_scale, softmax_scale, hq, hkv, page_size, window, cache_rows, out,
-             ld_out, static_cast<const __nv_bfloat16*>(gate), ld_gate, status};
+             ld_out, static_cast<const __nv_bfloat16*>(gate), ld_gate, status, kv_splits, tokens, nullptr, nullptr};
+  if (kv_splits > 1) {
+    a.part_o = static_cast<float*>(workspace);
+    a.part_ml = a.part_o + static_cast<int64_t>(kv_splits) * tokens * hq * head_dim;
+  }
   CUtensorMap tq, tk, tv;
   const uint32_t box_t = static_cast<uint32_t>(kAM / G);
   const uint64_t d = static_cast<uint64_t>(head_dim);
@@ -567,4 +685,49 @@ extern "C" int msl_attention_fp8(const void* q8, const void* k_cache, const void
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   return head_dim == 128 ? launch_attention<128>(tq, tk, tv, a, batch, max_q_len, st)
                          : launch_attention<64>(tq, tk, tv, a, batch, max_q_len, st);
+}
+
+extern "C" int msl_attention_fp8(const void* q8, const void* k_cache, const void* v_cache, const int* page_table,
+                                 int max_pages, const int* seq_lens, const int* cu_seqlens_q, const float* k_scale,
+                                 const float* v_scale, float softmax_scale, int batch, int max_q_len, int tokens,
+                                 int hq, int hkv, int head_dim, int page_size, int window, int64_t cache_rows,
+                                 void* out, int64_t ld_out, const void* gate, int64_t ld_gate, int* status,
+                                 void* stream) {
+  return attention_entry(q8, k_cache, v_cache, page_table, max_pages, seq_lens, cu_seqlens_q, k_scale, v_scale,
+                         softmax_scale, batch, max_q_len, tokens, hq, hkv, head_dim, page_size, window, cache_rows,
+                         out, ld_out, gate, ld_gate, 1, nullptr, status, stream);
+}
+
+extern "C" int msl_attention_split_plan(int batch, int max_q_len, int hq, int hkv, int max_pages, int page_size,
+                                        int window) {
+  if (batch <= 0 || max_q_len <= 0 || hq <= 0 || hkv <= 0 || hq % hkv || max_pages <= 0 || page_size <= 0) return 1;
+  const int G = hq / hkv;
+  if (G > 128) return 1;
+  const int tq2 = 2 * (kAM / G);
+  const int64_t ctas = static_cast<int64_t>((max_q_len + tq2 - 1) / tq2) * hkv * batch;
+  // key tiles a CTA may have to walk, from the sizes alone (the lengths live on the device)
+  int64_t keys = static_cast<int64_t>(max_pages) * page_size;
+  if (window > 0) keys = std::min<int64_t>(keys, window + tq2);
+  const int64_t tiles = (keys + kAN - 1) / kAN;
+  const int sms = sm_count();
+  if (ctas >= 2 * sms || tiles < 16) return 1;             // enough CTAs, or too little work to slice
+  // aim at two waves of CTAs, at least eight key tiles per slice
+  return static_cast<int>(std::max<int64_t>(1, std::min<int64_t>({(2 * sms + ctas - 1) / ctas, tiles / 8, 16})));
+}
+
+extern "C" int64_t msl_attention_split_workspace(int kv_splits, int tokens, int hq, int head_dim) {
+  if (kv_splits <= 1) return 0;
+  return static_cast<int64_t>(kv_splits) * tokens * hq * (head_dim + 2) * 4;
+}
+
+extern "C" int msl_attention_fp8_split(const void* q8, const void* k_cache, const void* v_cache,
+                                       const int* page_table, int max_pages, const int* seq_lens,
+                                       const int* cu_seqlens_q, const float* k_scale, const float* v_scale,
+                                       float softmax_scale, int batch, int max_q_len, int tokens, int hq, int hkv,
+                                       int head_dim, int page_size, int window, int64_t cache_rows, void* out,
+                                       int64_t ld_out, const void* gate, int64_t ld_gate, int kv_splits,
+                                       void* workspace, int* status, void* stream) {
+  return attention_entry(q8, k_cache, v_cache, page_table, max_pages, seq_lens, cu_seqlens_q, k_scale, v_scale,
+                         softmax_scale, batch, max_q_len, tokens, hq, hkv, head_dim, page_size, window, cache_rows,
+                         out, ld_out, gate, ld_gate, kv_splits, workspace, status, stream);
 }

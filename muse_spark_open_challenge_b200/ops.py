@@ -66,21 +66,31 @@ def qk_rope_store(qkv, positions, cache_loc, inv_freq, k_scale, v_scale, k_cache
 
 
 def attention(q8, k_cache, v_cache, page_table, seq_lens, cu_seqlens_q, k_scale, v_scale, softmax_scale, batch,
-              max_q_len, hq, hkv, head_dim, page_size, window, gate=None, out=None, status=None):
+              max_q_len, hq, hkv, head_dim, page_size, window, gate=None, out=None, status=None, kv_splits=None):
     """bf16 [T, hq*head_dim]; with `gate` (a bf16 2-D view with the same columns) the per-head RMS
-    norm and sigmoid gate are applied in the epilogue."""
+    norm and sigmoid gate are applied in the epilogue.  When the query blocks are too few to fill the
+    GPU (short blocks over long cached contexts) the keys are cut into `kv_splits` slices that run as
+    separate CTAs and are merged afterwards; None lets the library choose from the sizes."""
     _need(q8, FP8, "q8"), _need(page_table, torch.int32, "page_table"), _need(seq_lens, torch.int32, "seq_lens")
     _need(cu_seqlens_q, torch.int32, "cu_seqlens_q")
     t = q8.shape[0]
     if out is None:
         out = torch.empty((t, hq * head_dim), dtype=torch.bfloat16, device=q8.device)
     cache_rows = k_cache.numel() // (hkv * head_dim)
-    check(_lib.lib().msl_attention_fp8(q8.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), page_table.data_ptr(),
-                                       page_table.shape[1], seq_lens.data_ptr(), cu_seqlens_q.data_ptr(),
-                                       k_scale.data_ptr(), v_scale.data_ptr(), float(softmax_scale), batch, max_q_len,
-                                       t, hq, hkv, head_dim, page_size, window, cache_rows, out.data_ptr(),
-                                       _rows(out, "out"), _ptr(gate), 0 if gate is None else _rows(gate, "gate"),
-                                       _ptr(status), _stream()), "msl_attention_fp8")
+    lib = _lib.lib()
+    if kv_splits is None:
+        kv_splits = int(lib.msl_attention_split_plan(batch, max_q_len, hq, hkv, page_table.shape[1], page_size, window))
+    args = (q8.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), page_table.data_ptr(), page_table.shape[1],
+            seq_lens.data_ptr(), cu_seqlens_q.data_ptr(), k_scale.data_ptr(), v_scale.data_ptr(), float(softmax_scale),
+            batch, max_q_len, t, hq, hkv, head_dim, page_size, window, cache_rows, out.data_ptr(), _rows(out, "out"),
+            _ptr(gate), 0 if gate is None else _rows(gate, "gate"))
+    if kv_splits > 1:
+        work = torch.empty(int(lib.msl_attention_split_workspace(kv_splits, t, hq, head_dim)) // 4, dtype=torch.float32,
+                           device=q8.device)
+        check(lib.msl_attention_fp8_split(*args, kv_splits, work.data_ptr(), _ptr(status), _stream()),
+              "msl_attention_fp8_split")
+    else:
+        check(lib.msl_attention_fp8(*args, _ptr(status), _stream()), "msl_attention_fp8")
     return out
 
 

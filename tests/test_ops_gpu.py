@@ -310,7 +310,7 @@ def test_grouped_gemm_matches_dequantised_matmul(ops, counts, n, k, swiglu, vari
 
 
 # ------------------------------------------------------------------------------ attention
-def _attention_case(ops, shape, lens, ctxs, page, kv_scale, window, seed, zero_q=False):
+def _attention_case(ops, shape, lens, ctxs, page, kv_scale, window, seed, zero_q=False, kv_splits=1):
     from muse_spark_open_challenge_b200 import synth
     import dataclasses
     shape = dataclasses.replace(shape, window=window)
@@ -334,7 +334,8 @@ def _attention_case(ops, shape, lens, ctxs, page, kv_scale, window, seed, zero_q
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     out = ops.attention(q8.cuda(), dev["k_cache"], dev["v_cache"], dev["page_table"], dev["seq_lens"],
                         dev["cu_seqlens_q"], dev["k_scale"], dev["v_scale"], cfg["sm_scale"] * cfg["qk_scale_factor"],
-                        cfg["batch"], cfg["q_len"], shape.hq, shape.hkv, shape.head_dim, page, window, status=status)
+                        cfg["batch"], cfg["q_len"], shape.hq, shape.hkv, shape.head_dim, page, window, status=status,
+                        kv_splits=kv_splits)
     assert int(status.item()) == 0
     return out.float().cpu().view(t, shape.hq, shape.head_dim), ref
 
@@ -361,6 +362,39 @@ def test_attention_matches_oracle(ops, case):
     out, ref = _attention_case(ops, getattr(synth, name), lens, ctxs, page, kv_scale, window, seed=len(lens) + page)
     assert torch.isfinite(out).all()
     assert rel_l2(out, ref) < 3e-2
+
+
+SPLIT_CASES = [
+    # (shape name, new lens, cached lens, page, kv_scale, window, key slices)
+    ("MID", [40], [3000], 64, 1 / 64, 0, 4),
+    ("MID", [1, 1, 1], [2000, 5, 700], 64, 1.0, 0, 3),            # decode: some slices are empty
+    ("MID", [100, 300, 33], [0, 77, 500], 16, 0.5, 0, 2),         # the gather path, ragged requests
+    ("NATIVE", [97], [5000], 64, 1.0, 0, 7),
+    ("NATIVE", [8, 8], [2500, 2400], 1, 1.0, 2048, 5),            # sliding window, verify blocks
+    ("TINY", [80, 80], [100, 100], 64, 1 / 64, 96, 16),           # more slices than key tiles
+]
+
+
+@pytest.mark.parametrize("case", SPLIT_CASES)
+def test_split_kv_attention_matches_oracle(ops, case):
+    """The key range cut into slices that are merged afterwards: same bound as the single pass."""
+    from muse_spark_open_challenge_b200 import synth
+    name, lens, ctxs, page, kv_scale, window, splits = case
+    out, ref = _attention_case(ops, getattr(synth, name), lens, ctxs, page, kv_scale, window, seed=splits + page,
+                               kv_splits=splits)
+    one, _ = _attention_case(ops, getattr(synth, name), lens, ctxs, page, kv_scale, window, seed=splits + page)
+    assert torch.isfinite(out).all()
+    assert rel_l2(out, ref) < 3e-2
+    assert rel_l2(out, one) < 3e-2
+
+
+def test_split_plan_slices_only_short_blocks_over_long_contexts(ops):
+    from muse_spark_open_challenge_b200 import _lib
+    plan = _lib.lib().msl_attention_split_plan
+    assert plan(4, 4096, 32, 8, 64, 64, 0) == 1                   # mid prefill: thousands of CTAs already
+    assert plan(1, 753, 16, 2, 1262, 64, 0) > 1                   # one short chunk after 80000 cached tokens
+    assert plan(1, 1, 16, 2, 2, 64, 0) == 1                       # nothing to slice
+    assert _lib.lib().msl_attention_split_workspace(3, 10, 16, 64) == 3 * 10 * 16 * 66 * 4
 
 
 def test_attention_uniform_weights_average_the_values(ops):
