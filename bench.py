@@ -309,7 +309,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="layer", choices=["layer", "attn", "moe", "native"],
+    ap.add_argument("--workload", default="layer", choices=["layer", "attn", "moe", "native", "long"],
                     help="layer = the headline full-layer step; attn / moe = the op-only configurations")
     ap.add_argument("--small", action="store_true", help="reduced op workload, sized for an ncu capture")
     ap.add_argument("--transport", default="peer", choices=["peer", "collective"],
@@ -342,7 +342,41 @@ def main():
         dist = None
 
     n_exp = 128
-    if world > 1:
+    seq_ctx = None
+    long_lens = None
+    if args.workload == "long":
+        # BASELINE config 4: sequences of about 32768 tokens prefilled in chunks of 8192 +- 7.5 % with odd
+        # tails, one chunk per rank (4 chunks per sequence, 2 sequences on 8 GPUs), 256 experts sharded
+        # over the ranks.  The K/V rows of a sequence's earlier chunks reach a rank by the hand-off.
+        import dataclasses
+        from muse_spark_open_challenge_b200 import synth
+        per_seq = min(4, world)
+        gen = torch.Generator().manual_seed(4)
+        long_lens = [[int(8192 * (1 + 0.075 * (2 * u - 1))) | 1 for u in torch.rand(per_seq, generator=gen).tolist()]
+                     for _ in range(max(world // per_seq, 1))]
+        my_seq, my_chunk = rank // per_seq, rank % per_seq
+        lens = long_lens[my_seq]
+        n_exp = 256
+        shape = dataclasses.replace(synth.LONG_EP, n_experts=n_exp, local_experts=n_exp // world)
+        weights = synth.make_weights(shape, seed=100 * rank, device=dev)
+        data = synth.make_input(shape, [lens[my_chunk]], [sum(lens[:my_chunk])], seed=100 * rank + 1, page=64,
+                                kv_scale=1.0, local_start=rank * (n_exp // world), device=dev, fill_cache=False)
+        if world > 1:
+            for k, v in weights.items():
+                if not k.startswith(("w13", "w2")):
+                    dist.broadcast(v, 0)
+            groups = [dist.new_group(list(range(s0 * per_seq, (s0 + 1) * per_seq))) for s0 in range(world // per_seq)]
+            st = layer.prepare(weights)
+            ctx = ep.ExpertParallel(st, world, rank, n_exp)
+            if args.transport == "peer":
+                most = max(max(l) for l in long_lens)
+                ep.enable_peer(ctx, st, max_tokens=most, top_k=shape.top_k)
+            seq_ctx = ep.ChunkedSequence(groups[my_seq], my_chunk, lens, shape.hkv, shape.head_dim, dev)
+            step = lambda d: ep.kernel_fn(d, st, ctx, seq_ctx)  # noqa: E731
+        else:
+            st = layer.prepare(weights)
+            step = lambda d: layer.kernel_fn(d, st)  # noqa: E731
+    elif world > 1:
         shape, weights, data = make_workload(dev, seed=100 * rank, local_experts=n_exp // world,
                                              local_start=rank * (n_exp // world))
         # dense weights and the router are replicated: take rank 0's
@@ -481,6 +515,9 @@ def main():
     if dist is not None:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     ms, e2e_ms = times.tolist()
+    total_tokens = tokens * world
+    if long_lens is not None:
+        total_tokens = sum(sum(l) for l in long_lens) if world > 1 else tokens
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
@@ -502,13 +539,24 @@ def main():
                 "traffic": 0.92 * algo_bytes, "traffic_unit": "bytes per launch (scaled from an ncu capture)",
                 "peak_source": pk["source"], "launch_ms": gu_ms}
     total_flops = layer_flops(shape, SEQS, SEQ_LEN, routes)
+    workload = ("full decoder layer, mid prefill (BASELINE config 3): 4 x 4096 tokens per GPU, hidden "
+                "4096, 32q/8kv x 128, page 64, 128 experts top-8 x 1536 NVFP4 + shared 4096")
+    if long_lens is not None:
+        workload = ("full decoder layer, long prefill (BASELINE config 4): sequences of ~32768 tokens prefilled as chunks "
+                    f"of 8192 +- 7.5 % with odd tails, one chunk per GPU, chunk lengths {long_lens}; hidden 4096, 32q/8kv x "
+                    "128, page 64, 256 experts top-8 x 1536 NVFP4 sharded over the GPUs + shared 4096; the K/V rows of a "
+                    "sequence's earlier chunks arrive by an all-gather inside the step")
+        hq_d = shape.hq * shape.head_dim
+        attn = sum(4.0 * hq_d * (n * sum(l[:c]) + n * (n + 1) / 2) for l in long_lens for c, n in enumerate(l))
+        total_flops = (2.0 * total_tokens * shape.hidden * (shape.qkv_size + shape.q_size + shape.n_experts) + attn
+                       + 2.0 * total_tokens * shape.top_k * 3 * shape.moe_width * shape.inter
+                       + 2.0 * total_tokens * 3 * shape.moe_width * shape.shared_inter)
     line = {
-        "metric": METRIC, "value": tokens * world / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "metric": METRIC, "value": total_tokens / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16 activations, NVFP4 expert weights (W4A16), fp8 e4m3 attention",
         "data": "synthetic",
-        "config": {"workload": "full decoder layer, mid prefill (BASELINE config 3): 4 x 4096 tokens per GPU, hidden "
-                               "4096, 32q/8kv x 128, page 64, 128 experts top-8 x 1536 NVFP4 + shared 4096",
+        "config": {"workload": workload,
                    "tokens_per_gpu": tokens, "expert_parallel": world,
                    "ep_transport": (args.transport if world > 1 else None),
                    "launch": "CUDA graph replay" if graph is not None else "eager", "l2": "per-step working set (weights 2.6 GB) "
@@ -516,7 +564,7 @@ def main():
         "layer_tflops": total_flops / (ms * 1e-3) / 1e12,
         "stage_ms": {k: round(v, 4) for k, v in stage_ms.items()},
         "roofline": roof,
-        "e2e": {"value": tokens * world / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
+        "e2e": {"value": total_tokens / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": launches,
         "clocks": clocks,

@@ -152,6 +152,14 @@ int msl_combine_peer(const void* const* peer_bases, int peer_cap, const int* row
                      const float* post_w, const void* addend, int64_t ld_addend, void* out, int64_t ld_out,
                      int tokens, int top_k, int width, void* stream);
 
+/* Row gather / scatter for the K/V hand-off of a sequence whose chunks are prefilled on different
+ * ranks: dst[dst_idx ? dst_idx[i] : i] = src[src_idx ? src_idx[i] : i], i < n, rows of row_bytes
+ * (multiple of 16; e.g. hkv * head_dim FP8 bytes).  Indices are device int64 arrays; an index outside
+ * [0, src_rows) / [0, dst_rows) skips the row and sets *status to MSL_ERR_CAPACITY.  The reference runs
+ * one GPU with synthetic cached context (reference.py:195-224) and has no such step. */
+int msl_kv_rows_copy(const void* src, const int64_t* src_idx, int64_t src_rows, void* dst, const int64_t* dst_idx,
+                     int64_t dst_rows, int64_t n, int row_bytes, int* status, void* stream);
+
 /* Rows of a re-tiled NVFP4 bank: `rows` padded to whole 256-row tiles (for a gate/up bank,
  * interleave != 0, each half padded to whole 128-row blocks). */
 int64_t msl_nvfp4_padded_rows(int rows, int interleave);

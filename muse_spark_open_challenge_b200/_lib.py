@@ -32,6 +32,7 @@ SIGNATURES = {
     "msl_peer_barrier": (_i, [_p, _i, _i, _i, _p, _p]),
     "msl_dispatch_peer": (_i, [_p, _i64, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p, _p]),
     "msl_combine_peer": (_i, [_p, _i, _p, _p, _p, _p, _i64, _p, _i64, _i, _i, _i, _p]),
+    "msl_kv_rows_copy": (_i, [_p, _p, _i64, _p, _p, _i64, _i64, _i, _p, _p]),
     "msl_nvfp4_padded_rows": (_i64, [_i, _i]),
     "msl_nvfp4_repack": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _p]),
     "msl_grouped_gemm_nvfp4": (_i, [_p, _i64, _p, _p, _p, _p, _p, _i64, _i, _i, _i, _i, _i, _i, _p, _p]),

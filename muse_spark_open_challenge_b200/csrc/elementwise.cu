@@ -349,6 +349,31 @@ dispatch_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, const float* _
   }
 }
 
+// ============================================================================ K/V row gather / scatter
+// dst[dst_idx ? dst_idx[i] : i] = src[src_idx ? src_idx[i] : i] for rows of row_bytes (a multiple of
+// 16).  Gathers a chunk's new cache rows into a contiguous send buffer and scatters rows received from
+// the ranks that hold the earlier chunks of the same sequence into this rank's paged cache.
+// A negative or out-of-range index skips the row (and is reported).
+__global__ void __launch_bounds__(256)
+kv_rows_copy_kernel(const uint8_t* __restrict__ src, const int64_t* __restrict__ src_idx, int64_t src_rows,
+                    uint8_t* __restrict__ dst, const int64_t* __restrict__ dst_idx, int64_t dst_rows, int64_t n,
+                    int row_bytes, int* status) {
+  const int per_row = row_bytes / 16;
+  const int64_t total = n * per_row;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t row = i / per_row;
+    const int part = static_cast<int>(i - row * per_row);
+    const int64_t from = src_idx ? src_idx[row] : row;
+    const int64_t to = dst_idx ? dst_idx[row] : row;
+    if (from < 0 || from >= src_rows || to < 0 || to >= dst_rows) {
+      if (part == 0) report_error(status, MSL_ERR_CAPACITY);
+      continue;
+    }
+    reinterpret_cast<uint4*>(dst + to * row_bytes)[part] = reinterpret_cast<const uint4*>(src + from * row_bytes)[part];
+  }
+}
+
 // ============================================================================ expert-parallel plan + dispatch
 // counts_all[s][e]: routes of rank s to global expert e (all-gathered).  Rank d owns experts
 // [d * el, (d + 1) * el); its slab holds row groups ordered (source rank, local expert).  For this
@@ -812,5 +837,20 @@ extern "C" int msl_peer_barrier(int* const* flag_bases, int rank, int world, int
   if (!flag_bases || world <= 0 || world > 64 || rank < 0 || rank >= world || timeout_ms <= 0) return MSL_ERR_ARG;
   peer_barrier_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(
       flag_bases, rank, world, static_cast<uint64_t>(timeout_ms) * 1000000ull, status);
+  return cudaGetLastError() == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
+}
+
+extern "C" int msl_kv_rows_copy(const void* src, const int64_t* src_idx, int64_t src_rows, void* dst,
+                                const int64_t* dst_idx, int64_t dst_rows, int64_t n, int row_bytes, int* status,
+                                void* stream) {
+  if (!src || !dst || n < 0 || src_rows <= 0 || dst_rows <= 0 || row_bytes <= 0) return MSL_ERR_ARG;
+  if ((row_bytes & 15) || (reinterpret_cast<uintptr_t>(src) & 15) || (reinterpret_cast<uintptr_t>(dst) & 15))
+    return MSL_ERR_ALIGN;
+  if (n == 0) return MSL_OK;
+  const int64_t total = n * (row_bytes / 16);
+  const int blocks = static_cast<int>(std::min<int64_t>((total + 255) / 256, 8 * static_cast<int64_t>(sm_count())));
+  kv_rows_copy_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint8_t*>(src), src_idx, src_rows, static_cast<uint8_t*>(dst), dst_idx, dst_rows, n,
+      row_bytes, status);
   return cudaGetLastError() == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
 }

@@ -275,10 +275,51 @@ def moe_stage(h, data, st, ctx: ExpertParallel):
     return moe, ids
 
 
-def kernel_fn(data: dict, st: dict, ctx: ExpertParallel):
+class ChunkedSequence:
+    """One sequence prefilled in chunks on several ranks (context parallel): chunk c, `lens[c]` tokens
+    long, runs on rank c of `group`; this rank holds chunk `index` as ONE request whose cached context
+    (`seq_lens[0]`) is the sum of the earlier chunks.  The earlier chunks' K/V rows do not exist on
+    this rank until their owners have computed them in the same layer: `kv_handoff` brings them over.
+    The reference stands a synthetic cached context in for this (reference.py:195-224)."""
+
+    def __init__(self, group, index: int, lens, hkv: int, head_dim: int, device):
+        self.group, self.index, self.lens = group, index, [int(n) for n in lens]
+        self.starts = [sum(self.lens[:c]) for c in range(len(self.lens))]
+        self.row_bytes = hkv * head_dim
+        most = max(self.lens)
+        self.send = torch.empty((2, most, self.row_bytes), dtype=torch.uint8, device=device)
+        self.recv = torch.empty((len(self.lens), 2, most, self.row_bytes), dtype=torch.uint8, device=device)
+
+
+def kv_handoff(data: dict, st: dict, seq: ChunkedSequence):
+    """After this rank's new K/V rows are in its paged cache: all-gather the new rows of every chunk
+    of the sequence and scatter those of the earlier chunks into this rank's cache at the slots its
+    page table gives positions 0 .. context-1."""
+    cfg = data["config"]
+    if cfg["batch"] != 1:
+        raise ValueError("a chunked sequence is one request per rank")
+    n_mine = seq.lens[seq.index]
+    caches = [data[k].view(torch.uint8).view(-1, seq.row_bytes) for k in ("k_cache", "v_cache")]
+    for which, cache in enumerate(caches):
+        ops.kv_rows_copy(cache, seq.send[which], n_mine, src_idx=data["cache_loc"], status=st["status"])
+    dist.all_gather_into_tensor(seq.recv.view(-1), seq.send.view(-1), group=seq.group)
+    ctx_len = seq.starts[seq.index]
+    if ctx_len == 0:
+        return
+    page = cfg["page_size"]
+    pos = torch.arange(ctx_len, device=cache.device)
+    prefix_loc = data["page_table"][0].long()[pos // page] * page + pos % page
+    for c in range(seq.index):
+        idx = prefix_loc[seq.starts[c]:seq.starts[c] + seq.lens[c]]
+        for which, cache in enumerate(caches):
+            ops.kv_rows_copy(seq.recv[c, which], cache, seq.lens[c], dst_idx=idx, status=st["status"])
+
+
+def kernel_fn(data: dict, st: dict, ctx: ExpertParallel, seq: ChunkedSequence = None):
     """Same contract as layer.kernel_fn for this rank's requests; `st` holds this rank's slice of
-    the expert banks."""
-    o_in = layer.attention_stage(data, st)
+    the expert banks.  With `seq` this rank's single request is one chunk of a longer sequence whose
+    earlier chunks run on other ranks in the same call."""
+    o_in = layer.attention_stage(data, st, (lambda: kv_handoff(data, st, seq)) if seq is not None else None)
     a = ops.gemm(o_in, st["o"], status=st["status"])
     layer._mark(st, "gemm_o")
     s1, h = ops.boundary(a, None, data["stream"], st["a1"], st["b1"], st["w_pre_ffn"], layer.POST_NORM_EPS,

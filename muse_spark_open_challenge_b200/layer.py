@@ -113,9 +113,10 @@ def stage_times_ms(marks):
     return [(marks[i][0], marks[i - 1][1].elapsed_time(marks[i][1])) for i in range(1, len(marks))]
 
 
-def attention_stage(data, st):
+def attention_stage(data, st, after_store=None):
     """QKV+gate projection, QK-norm/RoPE/FP8/cache store, attention with the fused per-head norm
-    and gate.  Returns bf16 [T, hq*head_dim]."""
+    and gate.  Returns bf16 [T, hq*head_dim].  `after_store()` runs between the cache store and the
+    attention (the K/V hand-off of a sequence prefilled in chunks on several ranks)."""
     cfg = data["config"]
     hq, hkv, d = cfg["num_q_heads"], cfg["num_kv_heads"], cfg["head_dim"]
     status = st["status"]
@@ -126,6 +127,9 @@ def attention_stage(data, st):
     q8 = ops.qk_rope_store(qkv, data["positions"], data["cache_loc"], inv_freq, data["k_scale"], data["v_scale"],
                            data["k_cache"], data["v_cache"], hq, hkv, d, status=status)
     _mark(st, "qk_rope_store")
+    if after_store is not None:
+        after_store()
+        _mark(st, "kv_handoff")
     gate = qkv[:, (hq + 2 * hkv) * d:]
     out = ops.attention(q8, data["k_cache"], data["v_cache"], data["page_table"], data["seq_lens"],
                          data["cu_seqlens_q"], data["k_scale"], data["v_scale"],

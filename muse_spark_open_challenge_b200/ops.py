@@ -189,6 +189,19 @@ def combine_peer(peer_bases, cap, width, rowmap, weights, post_w, addend=None, o
     return out
 
 
+def kv_rows_copy(src, dst, n, src_idx=None, dst_idx=None, status=None):
+    """dst[dst_idx[i] or i] = src[src_idx[i] or i] for i < n; src and dst are 2-D byte-addressable
+    row tensors with the same row size (a multiple of 16 bytes), indices int64."""
+    row_bytes = src.shape[-1] * src.element_size()
+    if dst.shape[-1] * dst.element_size() != row_bytes or not src.is_contiguous() or not dst.is_contiguous():
+        raise MslError("kv_rows_copy: contiguous row tensors with equal row sizes are required")
+    for idx in (src_idx, dst_idx):
+        if idx is not None:
+            _need(idx, torch.int64, "index")
+    check(_lib.lib().msl_kv_rows_copy(src.data_ptr(), _ptr(src_idx), src.shape[0], dst.data_ptr(), _ptr(dst_idx),
+                                      dst.shape[0], n, row_bytes, _ptr(status), _stream()), "msl_kv_rows_copy")
+
+
 def nvfp4_repack(codes, scales, interleave):
     """Re-tile an NVFP4 bank (codes u8 [E, rows, k/2], scales e4m3 [E, rows, k/16]) for the grouped
     GEMM.  Returns (tiled codes u8, tiled scales u8, padded rows)."""

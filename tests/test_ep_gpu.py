@@ -68,6 +68,34 @@ def _worker(rank, world, port):
         st["status"].zero_()
         ctx.peer.cap = ctx.peer.cap_saved
         dist.barrier()
+        # One sequence prefilled as two chunks, one per rank: the second rank's cached context is the
+        # first rank's new K/V rows, handed over inside the layer call.
+        lens = [190, 131]
+        cdata = synth.make_input(shape, [lens[rank]], [sum(lens[:rank])], seed=50 + rank, page=64, kv_scale=0.5,
+                                 fill_cache=False)
+        cdev = to_device(cdata, f"cuda:{rank}")
+        seq = ep.ChunkedSequence(None, rank, lens, shape.hkv, shape.head_dim, f"cuda:{rank}")
+        c_hidden, c_stream, c_ids = ep.kernel_fn(cdev, st, ctx, seq)
+        torch.cuda.synchronize()
+        layer.check_status(st)
+        c_slots = L.new_slots(cdata).cuda()
+        rows = lambda name, idx: cdev[name].view(torch.uint8).view(-1, d.hkv * d.head_dim)[idx]   # noqa: E731
+        mine = torch.zeros((2, max(lens), d.hkv * d.head_dim), dtype=torch.uint8, device=f"cuda:{rank}")
+        mine[0, :lens[rank]], mine[1, :lens[rank]] = rows("k_cache", c_slots), rows("v_cache", c_slots)
+        both = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(both, mine)
+        if rank == 1:
+            page, pos = 64, torch.arange(lens[0], device="cuda:1")
+            prefix = cdev["page_table"][0].long()[pos // page] * page + pos % page
+            assert torch.equal(rows("k_cache", prefix), both[0][0, :lens[0]]), "handed-over K rows differ"
+            assert torch.equal(rows("v_cache", prefix), both[0][1, :lens[0]]), "handed-over V rows differ"
+        after = dict(cdata)
+        after["k_cache"], after["v_cache"] = cdev["k_cache"].cpu(), cdev["v_cache"].cpu()
+        kc = cdev["k_cache"].view(-1, d.hkv, d.head_dim)[c_slots].cpu()
+        vc = cdev["v_cache"].view(-1, d.hkv, d.head_dim)[c_slots].cpu()
+        ok, msg, _ = L.check_layer(after, weights, c_hidden.cpu(), c_stream.cpu(), c_ids.cpu(), kc, vc)
+        assert ok, f"rank {rank} (chunk {rank} of a split sequence): {msg}"
+        dist.barrier()
     finally:
         dist.destroy_process_group()
 
