@@ -389,7 +389,8 @@ def main():
             ep.enable_peer(ctx, st, max_tokens=data["config"]["tokens"], top_k=shape.top_k)
         step = lambda d: ep.kernel_fn(d, st, ctx)  # noqa: E731
     else:
-        shape, weights, data = make_workload(dev)
+        seqs = 1 if args.small else SEQS                     # --small: one request, sized for an ncu capture
+        shape, weights, data = make_workload(dev, seqs=seqs)
         st = layer.prepare(weights)
         step = lambda d: layer.kernel_fn(d, st)  # noqa: E731
     del weights
@@ -538,9 +539,11 @@ def main():
                 "peak": pk["tflops"], "unit": "TFLOP/s", "frac": achieved / pk["tflops"],
                 "traffic": 0.92 * algo_bytes, "traffic_unit": "bytes per launch (scaled from an ncu capture)",
                 "peak_source": pk["source"], "launch_ms": gu_ms}
-    total_flops = layer_flops(shape, SEQS, SEQ_LEN, routes)
+    total_flops = layer_flops(shape, 1 if (args.small and world == 1) else SEQS, SEQ_LEN, routes)
     workload = ("full decoder layer, mid prefill (BASELINE config 3): 4 x 4096 tokens per GPU, hidden "
                 "4096, 32q/8kv x 128, page 64, 128 experts top-8 x 1536 NVFP4 + shared 4096")
+    if args.small and world == 1:
+        workload = workload.replace("4 x 4096 tokens", "--small: 1 x 4096 tokens")
     if long_lens is not None:
         workload = ("full decoder layer, long prefill (BASELINE config 4): sequences of ~32768 tokens prefilled as chunks "
                     f"of 8192 +- 7.5 % with odd tails, one chunk per GPU, chunk lengths {long_lens}; hidden 4096, 32q/8kv x "

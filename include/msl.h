@@ -54,6 +54,18 @@ int msl_gemm_bf16(const void* a, int64_t lda, const void* b, int64_t ldb, void* 
                   int k, int segs, int a_seg_stride, int b_seg_stride, int out_mode, float alpha, int* status,
                   void* stream);
 
+/* Split-K form of msl_gemm_bf16 for products with few output tiles and a long K (decode steps, verify
+ * blocks, short continuation chunks; the router's two-segment product): every tile's K range is cut into
+ * `splits` slices that run as separate CTAs and leave fp32 planes [splits][m][n] in `workspace`
+ * (splits * m * n * 4 bytes of caller-owned device memory, 16-byte aligned); a second kernel sums the
+ * planes in a fixed order, applies alpha and writes c (MSL_OUT_BF16 or MSL_OUT_F32; n and ldc multiples
+ * of 4).  msl_gemm_splitk_plan recommends the slice count from the sizes alone (1 = call
+ * msl_gemm_bf16).  The reference leaves these products to cuBLAS (submission.py:1082,1096,1113). */
+int msl_gemm_splitk_plan(int m, int n, int k, int segs, int out_mode);
+int msl_gemm_bf16_splitk(const void* a, int64_t lda, const void* b, int64_t ldb, void* c, int64_t ldc, int m, int n,
+                         int k, int segs, int a_seg_stride, int b_seg_stride, int out_mode, float alpha, int splits,
+                         void* workspace, int* status, void* stream);
+
 /* Per-head RMS norm (eps 1e-5, no weight) of q and k, interleaved RoPE when inv_freq != NULL
  * (pairs (2i, 2i+1) rotate by positions[t] * inv_freq[i]), q -> E4M3 [tokens, hq, head_dim],
  * k / *k_scale and v / *v_scale -> E4M3 written to row cache_loc[t] of the paged caches

@@ -21,6 +21,8 @@ SIGNATURES = {
     "msl_abi_version": (_i, []),
     "msl_status_string": (C.c_char_p, [_i]),
     "msl_gemm_bf16": (_i, [_p, _i64, _p, _i64, _p, _i64, _i, _i, _i, _i, _i, _i, _i, _f, _p, _p]),
+    "msl_gemm_splitk_plan": (_i, [_i, _i, _i, _i, _i]),
+    "msl_gemm_bf16_splitk": (_i, [_p, _i64, _p, _i64, _p, _i64, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p, _p, _p]),
     "msl_qk_rope_store": (_i, [_p, _i64, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i64, _p, _p]),
     "msl_boundary": (_i, [_p, _i64, _p, _p, _p, _p, _p, _p, _p, _i64, _i, _i, _f, _f, _p]),
     "msl_route_topk": (_i, [_p, _i64, _i, _p, _f, _p, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p]),

@@ -48,70 +48,101 @@ __device__ __forceinline__ void block_sum(float (&v)[N], float* scratch) {
 }
 
 // ============================================================================ QK-norm + RoPE + FP8 + cache store
-// One group of D/8 lanes per (token, head); each lane owns 8 consecutive channels (one 16-byte load).
-// Heads 0..HQ-1 are queries, the next HKV keys, the next HKV values (the row layout of the QKV+gate
-// projection; the gate columns after them are not read).
+// Block (x, y): tokens [kRopeTok x, +kRopeTok), lanes [256 y, +256) of the token's (HQ + 2 HKV) D / 8
+// lanes; one group of D/8 lanes per head, each lane owning 8 consecutive channels of that head for every
+// token of the block (one 16-byte load and one 8-byte store per token, the loads of all tokens issued
+// before any arithmetic).  Heads 0..HQ-1 are queries, the next HKV keys, the next
+// HKV values (the row layout of the QKV+gate projection; the gate columns after them are not read).
+// A token's D/2 rotation angles are evaluated once per block (not once per head) while the loads are in
+// flight, and shared through shared memory.
+constexpr int kRopeTok = 2;
+
 template <int D>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 6)
 qk_rope_store_kernel(const __nv_bfloat16* __restrict__ qkv, int64_t ld, const int64_t* __restrict__ positions,
                      const int64_t* __restrict__ cache_loc, const float* __restrict__ inv_freq,
                      const float* __restrict__ k_scale_p, const float* __restrict__ v_scale_p,
                      uint8_t* __restrict__ q8, uint8_t* __restrict__ k_cache, uint8_t* __restrict__ v_cache,
                      int tokens, int hq, int hkv, int64_t cache_rows, int* status) {
   constexpr int LPH = D / 8;   // lanes per head
+  __shared__ float2 rot[kRopeTok][D / 2];                   // (cos, sin) of position * inv_freq[j]
   const int nh = hq + 2 * hkv;
-  const int64_t item = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) / LPH;
-  const int sub = threadIdx.x % LPH;
-  const bool live = item < static_cast<int64_t>(tokens) * nh;
-  const int t = live ? static_cast<int>(item / nh) : 0;
-  const int h = live ? static_cast<int>(item % nh) : 0;
-  float v[8];
-  {
-    const uint4 raw = live ? *reinterpret_cast<const uint4*>(qkv + t * ld + h * D + sub * 8) : make_uint4(0, 0, 0, 0);
-    unpack8(raw, v);
-  }
-  const bool is_v = h >= hq + hkv;
-  float ss = 0.f;
+  const int lanes = nh * LPH;
+  const int t0 = blockIdx.x * kRopeTok;
+  const int nt = min(kRopeTok, tokens - t0);
+  uint4 raw[kRopeTok];
+  auto fetch = [&](int idx) {
 #pragma unroll
-  for (int i = 0; i < 8; ++i) ss += v[i] * v[i];
-#pragma unroll
-  for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-  if (!live) return;
-  if (!is_v) {
-    const float r = 1.0f / sqrtf(ss / D + 1e-5f);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] *= r;
-    if (inv_freq != nullptr) {
-      const float pos = static_cast<float>(positions[t]);
-#pragma unroll
-      for (int i = 0; i < 8; i += 2) {
-        const float ang = pos * inv_freq[sub * 4 + i / 2];
+    for (int tt = 0; tt < kRopeTok; ++tt)
+      raw[tt] = (idx < lanes && tt < nt)
+                    ? *reinterpret_cast<const uint4*>(qkv + (t0 + tt) * ld + (idx / LPH) * D + (idx % LPH) * 8)
+                    : make_uint4(0, 0, 0, 0);
+  };
+  const int idx = blockIdx.y * blockDim.x + threadIdx.x;
+  fetch(idx);
+  if (inv_freq != nullptr) {
+    if (threadIdx.x < kRopeTok * (D / 2)) {
+      const int tt = threadIdx.x / (D / 2), j = threadIdx.x % (D / 2);
+      if (tt < nt) {
+        const float ang = static_cast<float>(positions[t0 + tt]) * inv_freq[j];
         float sn, cs;
         sincosf(ang, &sn, &cs);
-        const float e = v[i], o = v[i + 1];
-        v[i] = e * cs - o * sn;
-        v[i + 1] = e * sn + o * cs;
+        rot[tt][j] = make_float2(cs, sn);
       }
     }
+    __syncthreads();
   }
-  uint8_t* dst;
-  if (h < hq) {
-    dst = q8 + (static_cast<int64_t>(t) * hq + h) * D + sub * 8;
-  } else {
-    const float scale = is_v ? *v_scale_p : *k_scale_p;
-    // x / scale as the reference divides (reference.py:181-182); a reciprocal multiply would
-    // round differently when the scale is not a power of two.
+  const float k_scale = *k_scale_p, v_scale = *v_scale_p;
+  {
+    const bool live = idx < lanes;
+    const int h = live ? idx / LPH : 0;
+    const int sub = idx % LPH;
+    const bool is_v = h >= hq + hkv;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = v[i] / scale;
-    const int64_t row = cache_loc[t];
-    if (row < 0 || row >= cache_rows) {
-      report_error(status, MSL_ERR_CAPACITY);
-      return;
+    for (int tt = 0; tt < kRopeTok; ++tt) {
+      float v[8];
+      unpack8(raw[tt], v);
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += v[i] * v[i];
+#pragma unroll
+      for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      if (!live || tt >= nt) continue;
+      const int t = t0 + tt;
+      if (!is_v) {
+        const float r = 1.0f / sqrtf(ss / D + 1e-5f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] *= r;
+        if (inv_freq != nullptr) {
+#pragma unroll
+          for (int i = 0; i < 8; i += 2) {
+            const float2 cs = rot[tt][sub * 4 + i / 2];
+            const float e = v[i], o = v[i + 1];
+            v[i] = e * cs.x - o * cs.y;
+            v[i + 1] = e * cs.y + o * cs.x;
+          }
+        }
+      }
+      uint8_t* dst;
+      if (h < hq) {
+        dst = q8 + (static_cast<int64_t>(t) * hq + h) * D + sub * 8;
+      } else {
+        const int64_t row = cache_loc[t];
+        if (row < 0 || row >= cache_rows) {
+          report_error(status, MSL_ERR_CAPACITY);
+          continue;
+        }
+        const float scale = is_v ? v_scale : k_scale;
+        // x / scale as the reference divides (reference.py:181-182); a reciprocal multiply would
+        // round differently when the scale is not a power of two.
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = v[i] / scale;
+        const int kvh = is_v ? h - hq - hkv : h - hq;
+        dst = (is_v ? v_cache : k_cache) + (row * hkv + kvh) * D + sub * 8;
+      }
+      *reinterpret_cast<uint2*>(dst) = make_uint2(fp8x4(v[0], v[1], v[2], v[3]), fp8x4(v[4], v[5], v[6], v[7]));
     }
-    const int kvh = is_v ? h - hq - hkv : h - hq;
-    dst = (is_v ? v_cache : k_cache) + (row * hkv + kvh) * D + sub * 8;
   }
-  *reinterpret_cast<uint2*>(dst) = make_uint2(fp8x4(v[0], v[1], v[2], v[3]), fp8x4(v[4], v[5], v[6], v[7]));
 }
 
 // ============================================================================ residual boundary
@@ -602,17 +633,17 @@ extern "C" int msl_qk_rope_store(const void* qkv, int64_t ld, const int64_t* pos
       (reinterpret_cast<uintptr_t>(k_cache) & 7) || (reinterpret_cast<uintptr_t>(v_cache) & 7))
     return MSL_ERR_ALIGN;
   if (tokens == 0) return MSL_OK;
-  const int64_t items = static_cast<int64_t>(tokens) * (hq + 2 * hkv);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int lanes = (hq + 2 * hkv) * (head_dim / 8);
+  const int threads = std::max(kRopeTok * (head_dim / 2), std::min(256, ((lanes + 31) / 32) * 32));
+  const dim3 blocks((tokens + kRopeTok - 1) / kRopeTok, (lanes + threads - 1) / threads);
   if (head_dim == 128) {
-    const int64_t blocks = (items * 16 + 255) / 256;
-    qk_rope_store_kernel<128><<<static_cast<unsigned>(blocks), 256, 0, st>>>(
+    qk_rope_store_kernel<128><<<blocks, threads, 0, st>>>(
         static_cast<const __nv_bfloat16*>(qkv), ld, positions, cache_loc, inv_freq, k_scale, v_scale,
         static_cast<uint8_t*>(q8), static_cast<uint8_t*>(k_cache), static_cast<uint8_t*>(v_cache), tokens, hq, hkv,
         cache_rows, status);
   } else if (head_dim == 64) {
-    const int64_t blocks = (items * 8 + 255) / 256;
-    qk_rope_store_kernel<64><<<static_cast<unsigned>(blocks), 256, 0, st>>>(
+    qk_rope_store_kernel<64><<<blocks, threads, 0, st>>>(
         static_cast<const __nv_bfloat16*>(qkv), ld, positions, cache_loc, inv_freq, k_scale, v_scale,
         static_cast<uint8_t*>(q8), static_cast<uint8_t*>(k_cache), static_cast<uint8_t*>(v_cache), tokens, hq, hkv,
         cache_rows, status);

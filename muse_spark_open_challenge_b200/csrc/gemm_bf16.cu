@@ -46,6 +46,9 @@ struct GemmArgs {
   int b_seg_stride;      // B column offset (elements) added per segment
   float alpha;
   int* status;
+  // Split-K (splits > 1, fp32 output only): K slice ks of every tile goes to c + ks * split_stride.
+  int splits;
+  int64_t split_stride;  // elements
 };
 
 // Tile order: groups of 16 M-tiles sweep N together so one wave of CTAs re-uses a band of A and
@@ -128,7 +131,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   const int lane = threadIdx.x & 31;
   const int m_tiles = (p.m + kTileM - 1) / kTileM;
   const int n_tiles = (p.n + BN - 1) / BN;
-  const int total_tiles = m_tiles * n_tiles;
+  const int mn_tiles = m_tiles * n_tiles;
+  const int total_tiles = mn_tiles * p.splits;             // work item t: K slice t / mn_tiles of tile t % mn_tiles
   const int kb_per_seg = (p.k + kBK - 1) / kBK;
   const int k_blocks = kb_per_seg * p.segs;
 
@@ -159,8 +163,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         int mt, nt;
-        tile_coords(t, m_tiles, n_tiles, mt, nt);
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        tile_coords(t % mn_tiles, m_tiles, n_tiles, mt, nt);
+        const int ks = t / mn_tiles;
+        const int kb_lo = static_cast<int>(static_cast<int64_t>(ks) * k_blocks / p.splits);
+        const int kb_hi = static_cast<int>(static_cast<int64_t>(ks + 1) * k_blocks / p.splits);
+        for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (*abort_flag || !mbar_wait(&empty[s], ph ^ 1)) { ok = false; break; }
@@ -192,7 +199,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         if (*abort_flag || !mbar_wait(&tmem_empty[acc], acc_ph ^ 1)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        const int ks = t / mn_tiles;
+        const int kb_lo = static_cast<int>(static_cast<int64_t>(ks) * k_blocks / p.splits);
+        const int kb_hi = static_cast<int>(static_cast<int64_t>(ks + 1) * k_blocks / p.splits);
+        for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (*abort_flag || !mbar_wait(&full[s], ph)) { ok = false; break; }
@@ -205,7 +215,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 #pragma unroll
             for (int sub = 0; sub < SUBS; ++sub)
               tc_mma_f16(d_tmem + sub * BN, make_sdesc(sa + sub * S::kSubBytes + k16 * 32, 16, 1024, 2), db, idesc,
-                         (kb | k16) != 0);
+                         kb != kb_lo || k16 != 0);
           }
           tc_commit(&empty[s]);          // frees the stage once these MMAs have read it
         }
@@ -223,7 +233,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_i) {
       int mt, nt;
-      tile_coords(t, m_tiles, n_tiles, mt, nt);
+      tile_coords(t % mn_tiles, m_tiles, n_tiles, mt, nt);
+      GemmArgs q = p;                                        // this K slice's output plane
+      if constexpr (OUT == MSL_OUT_F32)
+        q.c = reinterpret_cast<float*>(p.c) + static_cast<int64_t>(t / mn_tiles) * p.split_stride;
       const uint32_t acc = SUBS == 2 ? 0u : (tile_i & 1);
       const uint32_t acc_ph = SUBS == 2 ? (tile_i & 1) : ((tile_i >> 1) & 1);
       if (*abort_flag || !mbar_wait(&tmem_full[acc], acc_ph)) { ok = false; break; }
@@ -249,7 +262,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           uint32_t v[32];
           tmem_ld32(taddr + c, v);
           tmem_ld_wait();
-          store_chunk<BN, OUT>(p, row, nt * BN + c, v, v);
+          store_chunk<BN, OUT>(q, row, nt * BN + c, v, v);
         }
       }
       }
@@ -287,11 +300,36 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmA
   }
   const int m_tiles = (args.m + kBM * SUBS - 1) / (kBM * SUBS);
   const int n_tiles = (args.n + BN - 1) / BN;
-  const int grid = std::min(m_tiles * n_tiles, sm_count());
+  const int grid = std::min(m_tiles * n_tiles * args.splits, sm_count());
   gemm_bf16_kernel<BN, STAGES, OUT, SUBS><<<grid, 192, smem, stream>>>(ta, tb, args);
   return cudaGetLastError() == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
 }
 
+
+// Sum of the K slices of a split-K product: out[m][n] = alpha * sum_s part[s][m][n], to bf16 or fp32.
+// Fixed summation order, so the result does not depend on scheduling.
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(const float* __restrict__ part, int splits, int m, int n, float alpha, void* out, int64_t ldc,
+                     int out_f32) {
+  const int64_t quads = static_cast<int64_t>(m) * (n / 4);
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < quads;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t row = i / (n / 4);
+    const int col = static_cast<int>(i - row * (n / 4)) * 4;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < splits; ++s) {
+      const float4 v = *reinterpret_cast<const float4*>(part + (static_cast<int64_t>(s) * m + row) * n + col);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    acc.x *= alpha; acc.y *= alpha; acc.z *= alpha; acc.w *= alpha;
+    if (out_f32) {
+      *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + row * ldc + col) = acc;
+    } else {
+      *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(out) + row * ldc + col) =
+          make_uint2(pack_bf16x2(acc.x, acc.y), pack_bf16x2(acc.z, acc.w));
+    }
+  }
+}
 
 // ============================================================================ CTA-pair variant
 // The same GEMM with two CTAs of a cluster sharing one M=256 x N=256 tcgen05.mma (cta_group::2):
@@ -504,10 +542,18 @@ static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const 
 
 using namespace msl;
 
-extern "C" int msl_gemm_bf16(const void* a, int64_t lda, const void* b, int64_t ldb, void* c, int64_t ldc, int m,
-                             int n, int k, int segs, int a_seg_stride, int b_seg_stride, int out_mode, float alpha,
-                             int* status, void* stream) {
+static int gemm_entry(const void* a, int64_t lda, const void* b, int64_t ldb, void* c, int64_t ldc, int m, int n, int k,
+                      int segs, int a_seg_stride, int b_seg_stride, int out_mode, float alpha, int splits,
+                      void* workspace, int* status, void* stream) {
   if (!a || !b || !c || m < 0 || n <= 0 || k <= 0 || segs < 1) return MSL_ERR_ARG;
+  if (splits < 1 || splits > 64) return MSL_ERR_ARG;
+  if (splits > 1) {
+    if (!workspace || out_mode == MSL_OUT_SWIGLU_BF16) return MSL_ERR_ARG;
+    if ((reinterpret_cast<uintptr_t>(workspace) & 15) || (n & 3) || (ldc & 3) ||
+        (reinterpret_cast<uintptr_t>(c) & 15))
+      return MSL_ERR_ALIGN;
+    if (splits > ((k + kBK - 1) / kBK) * segs) return MSL_ERR_ARG;
+  }
   if ((lda & 7) || (ldb & 7) || (k & 7) || (a_seg_stride & 7) || (b_seg_stride & 7)) return MSL_ERR_ALIGN;
   if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15)) return MSL_ERR_ALIGN;
   if (out_mode == MSL_OUT_SWIGLU_BF16 && (n % 256)) return MSL_ERR_ARG;
@@ -519,8 +565,24 @@ extern "C" int msl_gemm_bf16(const void* a, int64_t lda, const void* b, int64_t 
   int rc = make_tmap_2d(&ta, a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a_cols, m, lda * 2, kBK, kBM,
                         CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc) return rc;
-  GemmArgs args{c, ldc, m, n, k, segs, a_seg_stride, b_seg_stride, alpha, status};
+  GemmArgs args{c, ldc, m, n, k, segs, a_seg_stride, b_seg_stride, alpha, status, 1, 0};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (splits > 1) {
+    // K slices as fp32 planes [splits][m][n] in the workspace, then one reduction into c.
+    GemmArgs part{workspace, n, m, n, k, segs, a_seg_stride, b_seg_stride, 1.0f, status, splits,
+                  static_cast<int64_t>(m) * n};
+    const bool narrow_n = n <= 128 || (n % 256 != 0 && n % 128 == 0);
+    rc = make_tmap_2d(&tb, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, b_cols, n, ldb * 2, kBK, narrow_n ? 128 : 256,
+                      CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    rc = narrow_n ? launch_gemm<128, 6, MSL_OUT_F32>(ta, tb, part, st) : launch_gemm<256, 4, MSL_OUT_F32>(ta, tb, part, st);
+    if (rc) return rc;
+    const int64_t quads = static_cast<int64_t>(m) * (n / 4);
+    const int blocks = static_cast<int>(std::min<int64_t>((quads + 255) / 256, 8 * static_cast<int64_t>(sm_count())));
+    splitk_reduce_kernel<<<blocks, 256, 0, st>>>(static_cast<const float*>(workspace), splits, m, n, alpha, c, ldc,
+                                                 out_mode == MSL_OUT_F32);
+    return cudaGetLastError() == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
+  }
   // Narrow outputs use a 128-column tile so more CTAs share the work.
   const bool narrow = (out_mode != MSL_OUT_SWIGLU_BF16) && (n <= 128 || (n % 256 != 0 && n % 128 == 0));
   const int bn = narrow ? 128 : 256;
@@ -562,4 +624,28 @@ extern "C" int msl_gemm_bf16(const void* a, int64_t lda, const void* b, int64_t 
     default:
       return MSL_ERR_ARG;
   }
+}
+
+extern "C" int msl_gemm_bf16(const void* a, int64_t lda, const void* b, int64_t ldb, void* c, int64_t ldc, int m,
+                             int n, int k, int segs, int a_seg_stride, int b_seg_stride, int out_mode, float alpha,
+                             int* status, void* stream) {
+  return gemm_entry(a, lda, b, ldb, c, ldc, m, n, k, segs, a_seg_stride, b_seg_stride, out_mode, alpha, 1, nullptr,
+                    status, stream);
+}
+
+extern "C" int msl_gemm_splitk_plan(int m, int n, int k, int segs, int out_mode) {
+  if (m <= 0 || n <= 0 || k <= 0 || segs < 1 || out_mode == MSL_OUT_SWIGLU_BF16 || (n & 3)) return 1;
+  const bool narrow_n = n <= 128 || (n % 256 != 0 && n % 128 == 0);
+  const int64_t tiles = static_cast<int64_t>((m + kBM - 1) / kBM) * ((n + (narrow_n ? 127 : 255)) / (narrow_n ? 128 : 256));
+  const int k_blocks = ((k + kBK - 1) / kBK) * segs;
+  const int sms = sm_count();
+  if (tiles * 2 > sms || k_blocks < 16) return 1;            // enough tiles, or too little K to slice
+  return static_cast<int>(std::max<int64_t>(1, std::min<int64_t>({sms / tiles, k_blocks / 8, 16})));
+}
+
+extern "C" int msl_gemm_bf16_splitk(const void* a, int64_t lda, const void* b, int64_t ldb, void* c, int64_t ldc,
+                                    int m, int n, int k, int segs, int a_seg_stride, int b_seg_stride, int out_mode,
+                                    float alpha, int splits, void* workspace, int* status, void* stream) {
+  return gemm_entry(a, lda, b, ldb, c, ldc, m, n, k, segs, a_seg_stride, b_seg_stride, out_mode, alpha, splits,
+                    workspace, status, stream);
 }

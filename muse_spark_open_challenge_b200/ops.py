@@ -35,18 +35,28 @@ def _rows(t, name):
     return t.stride(0)
 
 
-def gemm(a, w, out_mode=OUT_BF16, out=None, k=None, segs=1, a_seg_stride=0, b_seg_stride=0, alpha=1.0, status=None):
+def gemm(a, w, out_mode=OUT_BF16, out=None, k=None, segs=1, a_seg_stride=0, b_seg_stride=0, alpha=1.0, status=None,
+         splits=None):
     """out[m, n] = alpha * sum_s a[:, s*a_seg_stride : +k] @ w[:, s*b_seg_stride : +k].T (bf16 in,
-    fp32 accumulate).  OUT_SWIGLU_BF16 expects w rows interleaved in 128-gate / 128-up blocks."""
+    fp32 accumulate).  OUT_SWIGLU_BF16 expects w rows interleaved in 128-gate / 128-up blocks.
+    Products with few output tiles and a long K run split over K (`splits`; None lets the library
+    choose from the sizes)."""
     _need(a, torch.bfloat16, "a"), _need(w, torch.bfloat16, "w")
     m, n = a.shape[0], w.shape[0]
     k = a.shape[1] if k is None else k
     n_out = n // 2 if out_mode == OUT_SWIGLU_BF16 else n
     if out is None:
         out = torch.empty((m, n_out), dtype=torch.float32 if out_mode == OUT_F32 else torch.bfloat16, device=a.device)
-    check(_lib.lib().msl_gemm_bf16(a.data_ptr(), _rows(a, "a"), w.data_ptr(), _rows(w, "w"), out.data_ptr(),
-                                   _rows(out, "out"), m, n, k, segs, a_seg_stride, b_seg_stride, out_mode,
-                                   float(alpha), _ptr(status), _stream()), "msl_gemm_bf16")
+    lib = _lib.lib()
+    if splits is None:
+        splits = int(lib.msl_gemm_splitk_plan(m, n, k, segs, out_mode)) if m > 0 else 1
+    args = (a.data_ptr(), _rows(a, "a"), w.data_ptr(), _rows(w, "w"), out.data_ptr(), _rows(out, "out"), m, n, k, segs,
+            a_seg_stride, b_seg_stride, out_mode, float(alpha))
+    if splits > 1:
+        work = torch.empty(splits * m * n, dtype=torch.float32, device=a.device)
+        check(lib.msl_gemm_bf16_splitk(*args, splits, work.data_ptr(), _ptr(status), _stream()), "msl_gemm_bf16_splitk")
+    else:
+        check(lib.msl_gemm_bf16(*args, _ptr(status), _stream()), "msl_gemm_bf16")
     return out
 
 

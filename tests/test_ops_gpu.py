@@ -59,6 +59,36 @@ def test_gemm_cta_pair_variant(ops, m, n, k, mode, monkeypatch):
     assert torch.equal(got, want)
 
 
+@pytest.mark.parametrize("m,n,k,segs,splits", [(753, 2304, 8192, 1, 2), (8, 2304, 4096, 1, 16), (100, 256, 2048, 2, 7),
+                                               (24, 64, 1024, 1, 16), (300, 1280, 1024, 1, 3)])
+def test_gemm_split_k(ops, m, n, k, segs, splits):
+    """K cut into slices on separate CTAs, summed in a fixed order: same bound as the one-pass product,
+    repeatable bit for bit, for bf16 and fp32 outputs and for the two-segment (router) form."""
+    g = torch.Generator(device="cuda").manual_seed(m + n + splits)
+    a = torch.randn((m, k), generator=g, device="cuda").to(torch.bfloat16)
+    w = (torch.randn((n, segs * k), generator=g, device="cuda") / math.sqrt(segs * k)).to(torch.bfloat16)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ref = sum(a.float() @ w[:, s * k:(s + 1) * k].float().T for s in range(segs))
+    kw = dict(k=k, segs=segs, a_seg_stride=0, b_seg_stride=k, status=status)
+    out32 = ops.gemm(a, w, out_mode=ops.OUT_F32, splits=splits, **kw)
+    again = ops.gemm(a, w, out_mode=ops.OUT_F32, splits=splits, **kw)
+    one = ops.gemm(a, w, out_mode=ops.OUT_F32, splits=1, **kw)
+    out16 = ops.gemm(a, w, splits=splits, alpha=0.5, **kw)
+    assert int(status.item()) == 0
+    assert torch.equal(out32, again)
+    assert torch.allclose(out32, ref, rtol=1e-4, atol=1e-4) and torch.allclose(out32, one, rtol=1e-4, atol=1e-4)
+    assert torch.allclose(out16.float(), 0.5 * ref, rtol=2 ** -7, atol=2e-3)
+
+
+def test_gemm_split_k_plan(ops):
+    from muse_spark_open_challenge_b200 import _lib
+    plan = _lib.lib().msl_gemm_splitk_plan
+    assert plan(16384, 10240, 4096, 1, 0) == 1                    # prefill-sized: tiles fill the GPU
+    assert plan(753, 256, 8192, 2, 1) > 1                         # the router of a 753-token chunk
+    assert plan(8, 2304, 8192, 1, 0) > 1                          # a decode step's QKV product
+    assert plan(753, 256, 8192, 2, 2) == 1                        # no split-K with the SwiGLU epilogue
+
+
 def test_gemm_two_segment_router_product(ops):
     """fp32 router as BF16 hi + lo: logits within 2e-5 of the fp64 product."""
     t, h, e = 500, 512, 16
