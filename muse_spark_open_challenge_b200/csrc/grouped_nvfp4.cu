@@ -112,6 +112,18 @@ __device__ __forceinline__ TileInfo decode_tile(int g, const int* mt_prefix, con
 // block scale.  The repack put the even elements in the low half-word and the odd ones in the
 // high half-word, element pair j at half-word bits: j=0: 15|8 7 6 (already in place), j=1: 12|5 4 3,
 // j=2: 9|2 1 0, j=3: 14|13 11 10 (sign | e1 e0 m).  Pairs 0-2 need one shift and one mask.
+// E4M3 block scale byte -> bf16(scale * 2^118) in both half-words.  A normal positive code s (exponent
+// field e >= 1) is 2^(e-7) (1 + m/8): its bf16 pattern times 2^118 is ((e + 238) << 7) | (m << 4) =
+// (s << 4) + 0x7700, so no table access (and none of its bank conflicts) is needed; zero, subnormal,
+// negative and NaN codes (not produced by a quantiser, but legal) take the table.
+__device__ __forceinline__ uint32_t scale_pair(const uint32_t* lut, uint32_t s) {
+  if (__builtin_expect(s - 8u < 0x77u, 1)) {                // 0x08 <= s <= 0x7e
+    const uint32_t b = (s << 4) + 0x7700u;
+    return b * 0x10001u;
+  }
+  return lut[s];
+}
+
 __device__ __forceinline__ uint4 dequant8(uint32_t w, uint32_t scale2) {
   constexpr uint32_t kMask = 0x81C081C0u;
   uint32_t b[4];
@@ -419,7 +431,7 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
           const int row = tg + r * kGroupThreads;
 #pragma unroll
           for (int c = 0; c < 8; ++c) {
-            const uint32_t scale2 = lut[(sbuf[u][r] >> (8 * (c >> 1))) & 0xffu];
+            const uint32_t scale2 = scale_pair(lut, (sbuf[u][r] >> (8 * (c >> 1))) & 0xffu);
             *reinterpret_cast<uint4*>(sb + swz128(row, c)) = dequant8(wbuf[u][r][c], scale2);
           }
         }
