@@ -149,7 +149,7 @@ qk_rope_store_kernel(const __nv_bfloat16* __restrict__ qkv, int64_t ld, const in
 // branch' = branch * branch_scale (optional); s_out = alpha * s_in + beta * rms(branch', eps_branch);
 // h_out = rms(s_out, eps_out) * norm_w.  One block per token row; the row stays in registers.
 template <int MAXC, int THREADS>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, (THREADS == 256 && MAXC <= 2) ? 5 : 1)
 boundary_kernel(const __nv_bfloat16* __restrict__ branch, int64_t ld_branch, const float* __restrict__ branch_scale,
                 const float* __restrict__ s_in, const float* __restrict__ alpha, const float* __restrict__ beta,
                 const float* __restrict__ norm_w, float* __restrict__ s_out, __nv_bfloat16* __restrict__ h_out,
@@ -517,48 +517,50 @@ __global__ void peer_barrier_kernel(int* const* __restrict__ flag_bases, int ran
 // copies (no registers held while they are in flight; the small footprint lets many blocks per SM keep
 // bytes outstanding), then read twice from shared memory: once for the sums of squares, once for the
 // weighted accumulation, which stays in registers across the rounds.  Each row crosses HBM exactly once.
-// With PEER the rows live in the expert-owning ranks' slabs: rowmap holds rank * peer_cap + row and the
-// row is read straight from that rank's memory (peer_bases[rank], NVLink) - the combine all-to-all of
-// expert parallelism fused into this kernel.
-constexpr int kCombineStage = 4;        // rows staged per round
+constexpr int kCombineStage = 4;        // rows staged per round from local memory
 constexpr int kCombineThreads = 256;
 constexpr int kCombineMaxChunks = 4;    // 8-element chunks per thread: width <= 8192 (MAXC = 2: <= 4096)
 
-template <bool PEER, int MAXC>
+template <int MAXC>
 __global__ void __launch_bounds__(kCombineThreads, MAXC <= 2 ? 5 : 4)
 combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ rowmap, const float* __restrict__ w,
                const float* __restrict__ post_w, const __nv_bfloat16* __restrict__ addend, int64_t ld_add,
-               __nv_bfloat16* __restrict__ out, int64_t ld_out, int top_k, int width,
-               const __nv_bfloat16* const* __restrict__ peer_bases, int peer_cap) {
-  extern __shared__ __align__(16) uint8_t rows_smem[];      // [kCombineStage][width] bf16
-  __shared__ float scratch[32 * kCombineStage];
-  __shared__ int route_of[32];
+               __nv_bfloat16* __restrict__ out, int64_t ld_out, int top_k, int width) {
+  constexpr int THREADS = kCombineThreads;
+  constexpr int STAGE = kCombineStage;
+  extern __shared__ __align__(16) uint8_t rows_smem[];      // [STAGE][width] bf16
+  __shared__ float scratch[32 * STAGE];
+  __shared__ int route_of[32], row_of[32];
   __shared__ int n_valid_s;
   const int t = blockIdx.x;
   const int chunks = width / 8;
-  if (threadIdx.x == 0) {                                   // compact the routes that have a row, in route order
-    int n = 0;
-    for (int j = 0; j < top_k; ++j)
-      if (rowmap[t * top_k + j] >= 0) route_of[n++] = j;
-    n_valid_s = n;
+  if (threadIdx.x < 32) {                                   // compact the routes that have a row, in route order
+    const int j = threadIdx.x;
+    const int row = j < top_k ? rowmap[t * top_k + j] : -1;
+    const uint32_t have = __ballot_sync(0xffffffffu, row >= 0);
+    if (row >= 0) {
+      const int at = __popc(have & ((1u << j) - 1u));
+      route_of[at] = j;
+      row_of[at] = row;
+    }
+    if (j == 0) n_valid_s = __popc(have);
   }
   __syncthreads();
   const int n_valid = n_valid_s;
+  // acc = sum_j r_j y_j; post_w multiplies once at the end: sum_j w_j rms(y_j post_w) = post_w sum_j r_j y_j
+  // with r_j = w_j / sqrt(mean((y_j post_w)^2) + eps).
   float acc[MAXC][8];
 #pragma unroll
   for (int c = 0; c < MAXC; ++c) {
-    const int ch = threadIdx.x + c * kCombineThreads;
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[c][i] = 0.f;
-    if (addend != nullptr && ch < chunks) unpack8(*reinterpret_cast<const uint4*>(addend + t * ld_add + ch * 8), acc[c]);
   }
-  for (int base = 0; base < n_valid; base += kCombineStage) {
-    const int n_round = min(kCombineStage, n_valid - base);
+  for (int base = 0; base < n_valid; base += STAGE) {
+    const int n_round = min(STAGE, n_valid - base);
     for (int q = 0; q < n_round; ++q) {
-      const int row = rowmap[t * top_k + route_of[base + q]];
-      const __nv_bfloat16* src = PEER ? peer_bases[row / peer_cap] + static_cast<int64_t>(row % peer_cap) * width
-                                      : y + static_cast<int64_t>(row) * width;
-      for (int ch = threadIdx.x; ch < chunks; ch += kCombineThreads) {
+      const int row = row_of[base + q];
+      const __nv_bfloat16* src = y + static_cast<int64_t>(row) * width;
+      for (int ch = threadIdx.x; ch < chunks; ch += THREADS) {
         const uint32_t dst = smem_u32(rows_smem + (static_cast<size_t>(q) * width + ch * 8) * 2);
         asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src + ch * 8) : "memory");
       }
@@ -566,18 +568,18 @@ combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ rowm
     asm volatile("cp.async.commit_group;" ::: "memory");
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
-    float ss[kCombineStage];
+    float ss[STAGE];
 #pragma unroll
-    for (int q = 0; q < kCombineStage; ++q) ss[q] = 0.f;
+    for (int q = 0; q < STAGE; ++q) ss[q] = 0.f;
 #pragma unroll
     for (int c = 0; c < MAXC; ++c) {
-      const int ch = threadIdx.x + c * kCombineThreads;
+      const int ch = threadIdx.x + c * THREADS;
       if (ch < chunks) {
         const float4 w0 = *reinterpret_cast<const float4*>(post_w + ch * 8);
         const float4 w1 = *reinterpret_cast<const float4*>(post_w + ch * 8 + 4);
         const float pw[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
-        for (int q = 0; q < kCombineStage; ++q) {
+        for (int q = 0; q < STAGE; ++q) {
           if (q < n_round) {
             float v[8];
             unpack8(*reinterpret_cast<const uint4*>(rows_smem + (static_cast<size_t>(q) * width + ch * 8) * 2), v);
@@ -587,25 +589,22 @@ combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ rowm
         }
       }
     }
-    block_sum<kCombineStage>(ss, scratch);
-    float r[kCombineStage];
+    block_sum<STAGE>(ss, scratch);
+    float r[STAGE];
 #pragma unroll
-    for (int q = 0; q < kCombineStage; ++q)
+    for (int q = 0; q < STAGE; ++q)
       r[q] = q < n_round ? w[t * top_k + route_of[base + q]] / sqrtf(ss[q] / width + 1e-8f) : 0.f;
 #pragma unroll
     for (int c = 0; c < MAXC; ++c) {
-      const int ch = threadIdx.x + c * kCombineThreads;
+      const int ch = threadIdx.x + c * THREADS;
       if (ch < chunks) {
-        const float4 w0 = *reinterpret_cast<const float4*>(post_w + ch * 8);
-        const float4 w1 = *reinterpret_cast<const float4*>(post_w + ch * 8 + 4);
-        const float pw[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
-        for (int q = 0; q < kCombineStage; ++q) {
+        for (int q = 0; q < STAGE; ++q) {
           if (q < n_round) {
             float v[8];
             unpack8(*reinterpret_cast<const uint4*>(rows_smem + (static_cast<size_t>(q) * width + ch * 8) * 2), v);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) acc[c][i] += v[i] * pw[i] * r[q];
+            for (int i = 0; i < 8; ++i) acc[c][i] += v[i] * r[q];
           }
         }
       }
@@ -614,8 +613,89 @@ combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ rowm
   }
 #pragma unroll
   for (int c = 0; c < MAXC; ++c) {
-    const int ch = threadIdx.x + c * kCombineThreads;
-    if (ch < chunks) *reinterpret_cast<uint4*>(out + t * ld_out + ch * 8) = pack8(acc[c]);
+    const int ch = threadIdx.x + c * THREADS;
+    if (ch < chunks) {
+      const float4 w0 = *reinterpret_cast<const float4*>(post_w + ch * 8);
+      const float4 w1 = *reinterpret_cast<const float4*>(post_w + ch * 8 + 4);
+      const float pw[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+      float o[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      if (addend != nullptr) unpack8(*reinterpret_cast<const uint4*>(addend + t * ld_add + ch * 8), o);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] += acc[c][i] * pw[i];
+      *reinterpret_cast<uint4*>(out + t * ld_out + ch * 8) = pack8(o);
+    }
+  }
+}
+
+// Peer form: the rows live in the expert-owning ranks' slabs (rowmap holds rank * peer_cap + row) and are
+// read straight from that rank's memory (peer_bases[rank], NVLink): the combine all-to-all of expert
+// parallelism fused into this kernel.  All of a token's rows are requested at once, 512 threads per
+// block, each thread pacing its requests by its own rowmap and pointer loads.  (The staged kernel above,
+// given peer pointers, measured 2.0 ms where this one takes 0.77 ms on two GPUs: a burst of requests from
+// every block at once does not suit NVLink reads.)
+template <int MAXK>
+__global__ void __launch_bounds__(512)
+combine_peer_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ rowmap, const float* __restrict__ w,
+               const float* __restrict__ post_w, const __nv_bfloat16* __restrict__ addend, int64_t ld_add,
+               __nv_bfloat16* __restrict__ out, int64_t ld_out, int top_k, int width,
+               const __nv_bfloat16* const* __restrict__ peer_bases, int peer_cap) {
+  extern __shared__ __align__(16) uint8_t rows_smem[];      // [top_k][width] bf16
+  __shared__ float scratch[32 * MAXK];
+  const int t = blockIdx.x;
+  const int chunks = width / 8;
+  uint32_t valid = 0;                                       // bit j: route j has a slab row
+  for (int j = 0; j < top_k; ++j) {
+    const int row = rowmap[t * top_k + j];
+    if (row >= 0) {
+      valid |= 1u << j;
+      const __nv_bfloat16* src = peer_bases[row / peer_cap] + static_cast<int64_t>(row % peer_cap) * width;
+      for (int ch = threadIdx.x; ch < chunks; ch += blockDim.x) {
+        const uint32_t dst = smem_u32(rows_smem + (static_cast<size_t>(j) * width + ch * 8) * 2);
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src + ch * 8) : "memory");
+      }
+    }
+  }
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  __syncthreads();
+  float ss[MAXK];
+#pragma unroll
+  for (int j = 0; j < MAXK; ++j) ss[j] = 0.f;
+  for (int ch = threadIdx.x; ch < chunks; ch += blockDim.x) {
+    const float4 w0 = *reinterpret_cast<const float4*>(post_w + ch * 8);
+    const float4 w1 = *reinterpret_cast<const float4*>(post_w + ch * 8 + 4);
+    const float pw[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+    for (int j = 0; j < MAXK; ++j) {
+      if (valid & (1u << j)) {
+        float v[8];
+        unpack8(*reinterpret_cast<const uint4*>(rows_smem + (static_cast<size_t>(j) * width + ch * 8) * 2), v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { const float x = v[i] * pw[i]; ss[j] += x * x; }
+      }
+    }
+  }
+  block_sum<MAXK>(ss, scratch);
+  float r[MAXK];
+#pragma unroll
+  for (int j = 0; j < MAXK; ++j)
+    r[j] = (valid & (1u << j)) ? w[t * top_k + j] / sqrtf(ss[j] / width + 1e-8f) : 0.f;
+  for (int ch = threadIdx.x; ch < chunks; ch += blockDim.x) {
+    const float4 w0 = *reinterpret_cast<const float4*>(post_w + ch * 8);
+    const float4 w1 = *reinterpret_cast<const float4*>(post_w + ch * 8 + 4);
+    const float pw[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (addend != nullptr) unpack8(*reinterpret_cast<const uint4*>(addend + t * ld_add + ch * 8), acc);
+#pragma unroll
+    for (int j = 0; j < MAXK; ++j) {
+      if (valid & (1u << j)) {
+        float v[8];
+        unpack8(*reinterpret_cast<const uint4*>(rows_smem + (static_cast<size_t>(j) * width + ch * 8) * 2), v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] += v[i] * pw[i] * r[j];
+      }
+    }
+    *reinterpret_cast<uint4*>(out + t * ld_out + ch * 8) = pack8(acc);
   }
 }
 
@@ -666,8 +746,7 @@ extern "C" int msl_boundary(const void* branch, int64_t ld_branch, const float* 
   auto* b = static_cast<const __nv_bfloat16*>(branch);
   auto* h = static_cast<__nv_bfloat16*>(hidden_out);
   // Rows wider than 4096 spread over more threads rather than more registers per thread.
-  int want = chunks <= 512 ? 256 : (chunks <= 1024 ? 512 : 1024);
-  if (const char* e = getenv("MSL_BOUNDARY_THREADS")) want = atoi(e);
+  const int want = chunks <= 512 ? 256 : (chunks <= 1024 ? 512 : 1024);
 #define MSL_BOUNDARY(MAXC, THREADS)                                                                              \
   boundary_kernel<MAXC, THREADS><<<tokens, std::min(THREADS, ((chunks + 31) / 32) * 32), 0, st>>>(               \
       b, ld_branch, branch_scale, stream_in, alpha, beta, norm_w, stream_out, h, ld_hidden, hidden, eps_branch,  \
@@ -737,14 +816,16 @@ static int combine_launch(const void* y, const int* rowmap, const float* weights
   if ((width & 7) || (ld_out & 7) || (ld_addend & 7)) return MSL_ERR_ALIGN;
   if (width > 8 * kCombineThreads * kCombineMaxChunks) return MSL_ERR_UNSUPPORTED;
   if (tokens == 0) return MSL_OK;
-  const int smem = kCombineStage * width * 2;               // <= 64 KB
+  constexpr int kPeerSmemMax = 200 * 1024;
   static bool configured = false;
   if (!configured) {
     const int most = kCombineStage * 8 * kCombineThreads * kCombineMaxChunks * 2;
-    if (cudaFuncSetAttribute(combine_kernel<false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, most) != cudaSuccess ||
-        cudaFuncSetAttribute(combine_kernel<true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, most) != cudaSuccess ||
-        cudaFuncSetAttribute(combine_kernel<false, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, most) != cudaSuccess ||
-        cudaFuncSetAttribute(combine_kernel<true, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, most) != cudaSuccess)
+    if (cudaFuncSetAttribute(combine_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, most) != cudaSuccess ||
+        cudaFuncSetAttribute(combine_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, most) != cudaSuccess ||
+        cudaFuncSetAttribute(combine_peer_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPeerSmemMax) !=
+            cudaSuccess ||
+        cudaFuncSetAttribute(combine_peer_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPeerSmemMax) !=
+            cudaSuccess)
       return MSL_ERR_CUDA;
     configured = true;
   }
@@ -753,17 +834,26 @@ static int combine_launch(const void* y, const int* rowmap, const float* weights
   auto* ad = static_cast<const __nv_bfloat16*>(addend);
   auto* oo = static_cast<__nv_bfloat16*>(out);
   auto* pb = reinterpret_cast<const __nv_bfloat16* const*>(peer_bases);
-  const bool narrow = width <= 8 * kCombineThreads * 2;
-  if (pb != nullptr && peer_cap <= 0) return MSL_ERR_ARG;
-#define MSL_COMBINE(PEER, MAXC)                                                                                   \
-  combine_kernel<PEER, MAXC><<<tokens, kCombineThreads, smem, st>>>(yy, rowmap, weights, post_w, ad, ld_addend, oo, \
-                                                                    ld_out, top_k, width, pb, pb ? peer_cap : 1)
   if (pb != nullptr) {
-    if (narrow) MSL_COMBINE(true, 2); else MSL_COMBINE(true, 4);
+    if (peer_cap <= 0) return MSL_ERR_ARG;
+    if (top_k > 8 || static_cast<int64_t>(top_k) * width * 2 > kPeerSmemMax) return MSL_ERR_UNSUPPORTED;
+    const int threads = std::min(512, ((width / 8 + 31) / 32) * 32);
+    const int smem = top_k * width * 2;                     // all of a token's rows
+    if (top_k <= 4)
+      combine_peer_kernel<4><<<tokens, threads, smem, st>>>(yy, rowmap, weights, post_w, ad, ld_addend, oo, ld_out,
+                                                            top_k, width, pb, peer_cap);
+    else
+      combine_peer_kernel<8><<<tokens, threads, smem, st>>>(yy, rowmap, weights, post_w, ad, ld_addend, oo, ld_out,
+                                                            top_k, width, pb, peer_cap);
   } else {
-    if (narrow) MSL_COMBINE(false, 2); else MSL_COMBINE(false, 4);
+    const int smem = kCombineStage * width * 2;             // <= 64 KB
+    if (width <= 8 * kCombineThreads * 2)
+      combine_kernel<2><<<tokens, kCombineThreads, smem, st>>>(yy, rowmap, weights, post_w, ad, ld_addend, oo, ld_out,
+                                                               top_k, width);
+    else
+      combine_kernel<4><<<tokens, kCombineThreads, smem, st>>>(yy, rowmap, weights, post_w, ad, ld_addend, oo, ld_out,
+                                                               top_k, width);
   }
-#undef MSL_COMBINE
   return cudaGetLastError() == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
 }
 

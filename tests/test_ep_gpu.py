@@ -50,14 +50,17 @@ def _worker(rank, world, port):
         v_rows = dev["v_cache"].view(-1, d.hkv, d.head_dim)[slots].cpu()
         ok, msg, _ = L.check_layer(data, weights, hidden.cpu(), stream.cpu(), ids.cpu(), k_rows, v_rows)
         assert ok, f"rank {rank}: {msg}"
-        # peer-memory transport: same rows, same order, same arithmetic -> identical bits
+        # peer-memory transport: same rows in the same order through the same GEMMs; only the combine
+        # kernel differs (it sums the same terms with another association), so ids are equal and the
+        # outputs agree to fp32 rounding of a bf16 result
         ep.enable_peer(ctx, st, max_tokens=hidden.shape[0], top_k=shape.top_k)
         for _ in range(3):                                               # slab reuse across layers
             hidden3, stream3, ids3 = ep.kernel_fn(dev, st, ctx)
         torch.cuda.synchronize()
         layer.check_status(st)
         assert torch.equal(ids3, ids), f"rank {rank}: peer transport changed the routing"
-        assert torch.equal(hidden3, hidden) and torch.equal(stream3, stream), f"rank {rank}: peer transport differs"
+        assert L.relative_l2(stream3, stream) < 1e-5 and L.relative_l2(hidden3.float(), hidden.float()) < 2e-3, \
+            f"rank {rank}: peer transport differs"
         # a slab too small for the routing is reported, not overrun
         ctx.peer.cap_saved = ctx.peer.cap
         ctx.peer.cap = 256
