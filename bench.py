@@ -302,6 +302,24 @@ def run_native(args):
                       "launch": "CUDA graph replay, L2 flushed before every replay, median", "shapes": rows}))
 
 
+def enable_peer_or_collective(ep, dist, ctx, st, max_tokens, top_k):
+    """Map the ranks' row slabs into one another; when the platform cannot (no peer access between the
+    GPUs, symmetric memory unavailable) every rank keeps the NCCL all-to-all transport and the line says so."""
+    ok = torch.ones(1, device=st["device"])
+    why = ""
+    try:
+        ep.enable_peer(ctx, st, max_tokens=max_tokens, top_k=top_k)
+    except Exception as exc:  # noqa: BLE001 - any failure of the mapping selects the other transport
+        ok.zero_()
+        why = f"{type(exc).__name__}: {exc}"[:200]
+        ctx.peer = None
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    if ok.item() > 0:
+        return "peer"
+    ctx.peer = None
+    return "collective (peer memory unavailable" + (": " + why if why else " on another rank") + ")"
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -352,15 +370,21 @@ def main():
         from muse_spark_open_challenge_b200 import synth
         per_seq = min(4, world)
         gen = torch.Generator().manual_seed(4)
-        long_lens = [[int(8192 * (1 + 0.075 * (2 * u - 1))) | 1 for u in torch.rand(per_seq, generator=gen).tolist()]
+        # 2 * per_seq pieces per sequence; rank c of a sequence takes pieces c and 2 * per_seq - 1 - c, so
+        # every rank has the same causal attention work
+        long_lens = [[int(4096 * (1 + 0.075 * (2 * u - 1))) | 1 for u in torch.rand(2 * per_seq, generator=gen).tolist()]
                      for _ in range(max(world // per_seq, 1))]
         my_seq, my_chunk = rank // per_seq, rank % per_seq
         lens = long_lens[my_seq]
+        owners = list(range(per_seq)) + list(range(per_seq - 1, -1, -1))
+        starts = [sum(lens[:p]) for p in range(len(lens))]
+        my_pieces = [p for p, o in enumerate(owners) if o == my_chunk]
         n_exp = 256
         shape = dataclasses.replace(synth.LONG_EP, n_experts=n_exp, local_experts=n_exp // world)
         weights = synth.make_weights(shape, seed=100 * rank, device=dev)
-        data = synth.make_input(shape, [lens[my_chunk]], [sum(lens[:my_chunk])], seed=100 * rank + 1, page=64,
-                                kv_scale=1.0, local_start=rank * (n_exp // world), device=dev, fill_cache=False)
+        data = synth.make_input(shape, [lens[p] for p in my_pieces], [starts[p] for p in my_pieces],
+                                seed=100 * rank + 1, page=64, kv_scale=1.0, local_start=rank * (n_exp // world),
+                                device=dev, fill_cache=(world == 1))   # one GPU: no hand-off, synthetic context
         if world > 1:
             for k, v in weights.items():
                 if not k.startswith(("w13", "w2")):
@@ -369,9 +393,9 @@ def main():
             st = layer.prepare(weights)
             ctx = ep.ExpertParallel(st, world, rank, n_exp)
             if args.transport == "peer":
-                most = max(max(l) for l in long_lens)
-                ep.enable_peer(ctx, st, max_tokens=most, top_k=shape.top_k)
-            seq_ctx = ep.ChunkedSequence(groups[my_seq], my_chunk, lens, shape.hkv, shape.head_dim, dev)
+                most = max(l[c] + l[2 * per_seq - 1 - c] for l in long_lens for c in range(per_seq))
+                args.transport = enable_peer_or_collective(ep, dist, ctx, st, most, shape.top_k)
+            seq_ctx = ep.ChunkedSequence(groups[my_seq], my_chunk, lens, shape.hkv, shape.head_dim, dev, owners=owners)
             step = lambda d: ep.kernel_fn(d, st, ctx, seq_ctx)  # noqa: E731
         else:
             st = layer.prepare(weights)
@@ -386,7 +410,7 @@ def main():
         st = layer.prepare(weights)
         ctx = ep.ExpertParallel(st, world, rank, shape.n_experts)
         if args.transport == "peer":
-            ep.enable_peer(ctx, st, max_tokens=data["config"]["tokens"], top_k=shape.top_k)
+            args.transport = enable_peer_or_collective(ep, dist, ctx, st, data["config"]["tokens"], shape.top_k)
         step = lambda d: ep.kernel_fn(d, st, ctx)  # noqa: E731
     else:
         seqs = 1 if args.small else SEQS                     # --small: one request, sized for an ncu capture
@@ -545,10 +569,10 @@ def main():
     if args.small and world == 1:
         workload = workload.replace("4 x 4096 tokens", "--small: 1 x 4096 tokens")
     if long_lens is not None:
-        workload = ("full decoder layer, long prefill (BASELINE config 4): sequences of ~32768 tokens prefilled as chunks "
-                    f"of 8192 +- 7.5 % with odd tails, one chunk per GPU, chunk lengths {long_lens}; hidden 4096, 32q/8kv x "
-                    "128, page 64, 256 experts top-8 x 1536 NVFP4 sharded over the GPUs + shared 4096; the K/V rows of a "
-                    "sequence's earlier chunks arrive by an all-gather inside the step")
+        workload = ("full decoder layer, long prefill (BASELINE config 4): sequences of ~32768 tokens prefilled as pieces "
+                    f"of 4096 +- 7.5 % with odd tails, two pieces per GPU in zigzag order, piece lengths {long_lens}; hidden "
+                    "4096, 32q/8kv x 128, page 64, 256 experts top-8 x 1536 NVFP4 sharded over the GPUs + shared 4096; the "
+                    "K/V rows of a sequence's earlier pieces arrive by an all-gather inside the step")
         hq_d = shape.hq * shape.head_dim
         attn = sum(4.0 * hq_d * (n * sum(l[:c]) + n * (n + 1) / 2) for l in long_lens for c, n in enumerate(l))
         total_flops = (2.0 * total_tokens * shape.hidden * (shape.qkv_size + shape.q_size + shape.n_experts) + attn

@@ -276,43 +276,64 @@ def moe_stage(h, data, st, ctx: ExpertParallel):
 
 
 class ChunkedSequence:
-    """One sequence prefilled in chunks on several ranks (context parallel): chunk c, `lens[c]` tokens
-    long, runs on rank c of `group`; this rank holds chunk `index` as ONE request whose cached context
-    (`seq_lens[0]`) is the sum of the earlier chunks.  The earlier chunks' K/V rows do not exist on
-    this rank until their owners have computed them in the same layer: `kv_handoff` brings them over.
+    """One sequence prefilled in pieces on several ranks in the same layer call (context parallel).
+    Piece p, `lens[p]` tokens long, covers positions [sum(lens[:p]), +lens[p]) and runs on rank
+    `owners[p]` of `group`; a rank gives its pieces, in increasing order, as separate requests whose
+    cached context (`seq_lens[b]`) is the sum of all earlier pieces.  The earlier pieces' K/V rows do
+    not exist in a request's pages until their owners have computed them in the same layer:
+    `kv_handoff` brings them over.  `owners` defaults to one piece per rank in order; giving rank c the
+    pieces c and 2 W - 1 - c (`zigzag_owners`) balances the causal attention work.
     The reference stands a synthetic cached context in for this (reference.py:195-224)."""
 
-    def __init__(self, group, index: int, lens, hkv: int, head_dim: int, device):
+    def __init__(self, group, index: int, lens, hkv: int, head_dim: int, device, owners=None):
         self.group, self.index, self.lens = group, index, [int(n) for n in lens]
-        self.starts = [sum(self.lens[:c]) for c in range(len(self.lens))]
+        self.owners = list(range(len(self.lens))) if owners is None else [int(o) for o in owners]
+        if len(self.owners) != len(self.lens):
+            raise ValueError("one owner per piece")
+        self.world = max(self.owners) + 1
+        self.starts = [sum(self.lens[:p]) for p in range(len(self.lens))]
+        self.mine = [p for p, o in enumerate(self.owners) if o == index]          # this rank's requests
+        # offset of piece p among its owner's tokens (requests are laid out in piece order)
+        self.offset_in_owner = []
+        seen = [0] * self.world
+        for p, o in enumerate(self.owners):
+            self.offset_in_owner.append(seen[o])
+            seen[o] += self.lens[p]
         self.row_bytes = hkv * head_dim
-        most = max(self.lens)
+        most = max(seen)
         self.send = torch.empty((2, most, self.row_bytes), dtype=torch.uint8, device=device)
-        self.recv = torch.empty((len(self.lens), 2, most, self.row_bytes), dtype=torch.uint8, device=device)
+        self.recv = torch.empty((self.world, 2, most, self.row_bytes), dtype=torch.uint8, device=device)
+
+
+def zigzag_owners(ranks: int):
+    """Owners of 2 * ranks pieces: rank c takes pieces c and 2 * ranks - 1 - c."""
+    return list(range(ranks)) + list(range(ranks - 1, -1, -1))
 
 
 def kv_handoff(data: dict, st: dict, seq: ChunkedSequence):
-    """After this rank's new K/V rows are in its paged cache: all-gather the new rows of every chunk
-    of the sequence and scatter those of the earlier chunks into this rank's cache at the slots its
-    page table gives positions 0 .. context-1."""
+    """After this rank's new K/V rows are in its paged cache: all-gather the new rows of every rank of
+    the sequence, then, for each of this rank's requests, scatter the rows of all earlier pieces into
+    the slots the request's page table gives their positions."""
     cfg = data["config"]
-    if cfg["batch"] != 1:
-        raise ValueError("a chunked sequence is one request per rank")
-    n_mine = seq.lens[seq.index]
+    if cfg["batch"] != len(seq.mine):
+        raise ValueError("a rank's requests must be its pieces of the sequence, in order")
+    n_mine = sum(seq.lens[p] for p in seq.mine)
     caches = [data[k].view(torch.uint8).view(-1, seq.row_bytes) for k in ("k_cache", "v_cache")]
     for which, cache in enumerate(caches):
         ops.kv_rows_copy(cache, seq.send[which], n_mine, src_idx=data["cache_loc"], status=st["status"])
     dist.all_gather_into_tensor(seq.recv.view(-1), seq.send.view(-1), group=seq.group)
-    ctx_len = seq.starts[seq.index]
-    if ctx_len == 0:
-        return
     page = cfg["page_size"]
-    pos = torch.arange(ctx_len, device=cache.device)
-    prefix_loc = data["page_table"][0].long()[pos // page] * page + pos % page
-    for c in range(seq.index):
-        idx = prefix_loc[seq.starts[c]:seq.starts[c] + seq.lens[c]]
-        for which, cache in enumerate(caches):
-            ops.kv_rows_copy(seq.recv[c, which], cache, seq.lens[c], dst_idx=idx, status=st["status"])
+    for b, p in enumerate(seq.mine):
+        ctx_len = seq.starts[p]
+        if ctx_len == 0:
+            continue
+        pos = torch.arange(ctx_len, device=caches[0].device)
+        prefix_loc = data["page_table"][b].long()[pos // page] * page + pos % page
+        for q in range(p):
+            idx = prefix_loc[seq.starts[q]:seq.starts[q] + seq.lens[q]]
+            rows = seq.recv[seq.owners[q]][:, seq.offset_in_owner[q]:seq.offset_in_owner[q] + seq.lens[q]]
+            for which, cache in enumerate(caches):
+                ops.kv_rows_copy(rows[which], cache, seq.lens[q], dst_idx=idx, status=st["status"])
 
 
 def kernel_fn(data: dict, st: dict, ctx: ExpertParallel, seq: ChunkedSequence = None):

@@ -99,6 +99,33 @@ def _worker(rank, world, port):
         ok, msg, _ = L.check_layer(after, weights, c_hidden.cpu(), c_stream.cpu(), c_ids.cpu(), kc, vc)
         assert ok, f"rank {rank} (chunk {rank} of a split sequence): {msg}"
         dist.barrier()
+        # The same with four pieces in zigzag order (rank 0: pieces 0 and 3, rank 1: pieces 1 and 2), two
+        # requests per rank: balances the causal attention work between the ranks.
+        lens4, owners = [70, 45, 83, 52], ep.zigzag_owners(world)
+        starts4 = [sum(lens4[:p]) for p in range(4)]
+        my = [p for p, o in enumerate(owners) if o == rank]
+        zdata = synth.make_input(shape, [lens4[p] for p in my], [starts4[p] for p in my], seed=70 + rank, page=16,
+                                 kv_scale=0.5, fill_cache=False)
+        zdev = to_device(zdata, f"cuda:{rank}")
+        zseq = ep.ChunkedSequence(None, rank, lens4, shape.hkv, shape.head_dim, f"cuda:{rank}", owners=owners)
+        z_hidden, z_stream, z_ids = ep.kernel_fn(zdev, st, ctx, zseq)
+        torch.cuda.synchronize()
+        layer.check_status(st)
+        z_slots = L.new_slots(zdata).cuda()
+        zafter = dict(zdata)
+        zafter["k_cache"], zafter["v_cache"] = zdev["k_cache"].cpu(), zdev["v_cache"].cpu()
+        zk = zdev["k_cache"].view(-1, d.hkv, d.head_dim)[z_slots].cpu()
+        zv = zdev["v_cache"].view(-1, d.hkv, d.head_dim)[z_slots].cpu()
+        ok, msg, _ = L.check_layer(zafter, weights, z_hidden.cpu(), z_stream.cpu(), z_ids.cpu(), zk, zv)
+        assert ok, f"rank {rank} (pieces {my} of a zigzag-split sequence): {msg}"
+        # every cached context row of a request must be a row some rank computed: none left at zero
+        for b, p in enumerate(my):
+            if starts4[p]:
+                pos = torch.arange(starts4[p], device=f"cuda:{rank}")
+                loc = zdev["page_table"][b].long()[pos // 16] * 16 + pos % 16
+                got = zdev["k_cache"].view(torch.uint8).view(-1, d.hkv * d.head_dim)[loc]
+                assert bool((got != 0).any(dim=1).all()), f"rank {rank}: piece {p} has unfilled context rows"
+        dist.barrier()
     finally:
         dist.destroy_process_group()
 
