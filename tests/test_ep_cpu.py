@@ -72,3 +72,26 @@ def test_expert_parallel_context_rejects_bad_geometry():
         ep.ExpertParallel(st, world=2, rank=0, n_experts=16)
     ctx = ep.ExpertParallel(st, world=4, rank=1, n_experts=16)
     assert ctx.counts.numel() == 16
+
+
+def test_chunked_sequence_bookkeeping():
+    """Pieces, their owners and where each piece sits among its owner's tokens (host logic only)."""
+    from muse_spark_open_challenge_b200 import ep
+    assert ep.zigzag_owners(4) == [0, 1, 2, 3, 3, 2, 1, 0]
+    lens = [5, 7, 3, 9, 4, 6, 8, 2]
+    seqs = [ep.ChunkedSequence(None, r, lens, hkv=2, head_dim=8, device="cpu", owners=ep.zigzag_owners(4))
+            for r in range(4)]
+    assert [s.mine for s in seqs] == [[0, 7], [1, 6], [2, 5], [3, 4]]
+    s = seqs[1]
+    assert s.starts == [0, 5, 12, 15, 24, 28, 34, 42]
+    # rank 1 holds piece 1 (7 tokens) then piece 6 (8 tokens): piece 6 starts at row 7 of its rows
+    assert s.offset_in_owner[1] == 0 and s.offset_in_owner[6] == 7
+    assert s.offset_in_owner[0] == 0 and s.offset_in_owner[7] == 5
+    # buffers hold the busiest rank's rows, K and V, for every rank
+    most = max(lens[p] + lens[7 - p] for p in range(4))
+    assert s.send.shape == (2, most, 16) and s.recv.shape == (4, 2, most, 16)
+    # default: one piece per rank in order
+    plain = ep.ChunkedSequence(None, 2, [4, 4, 4], hkv=1, head_dim=16, device="cpu")
+    assert plain.owners == [0, 1, 2] and plain.mine == [2] and plain.starts == [0, 4, 8]
+    with pytest.raises(ValueError):
+        ep.ChunkedSequence(None, 0, [4, 4], hkv=1, head_dim=16, device="cpu", owners=[0])
