@@ -455,3 +455,70 @@ def test_attention_fused_norm_and_gate(ops):
     ref = (L.rms(plain.float().view(t, shape.hq, shape.head_dim)).reshape(t, -1) * torch.sigmoid(gate_dev.float()))
     # the fused epilogue normalises the fp32 accumulator, the check normalises its bf16 rounding
     assert rel_l2(fused, ref) < 6e-3
+
+
+# ------------------------------------------------------------------------------ multi-GPU plumbing on one GPU
+def test_kv_rows_copy_gathers_scatters_and_reports_bad_rows(ops):
+    g = torch.Generator(device="cuda").manual_seed(3)
+    cache = torch.randint(0, 256, (500, 256), dtype=torch.uint8, generator=g, device="cuda")
+    idx = torch.randperm(500, generator=g, device="cuda")[:123]
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    packed = torch.zeros((200, 256), dtype=torch.uint8, device="cuda")
+    ops.kv_rows_copy(cache, packed, 123, src_idx=idx, status=status)               # gather
+    assert torch.equal(packed[:123], cache[idx]) and not packed[123:].any()
+    other = torch.zeros_like(cache)
+    where = torch.randperm(500, generator=g, device="cuda")[:123]
+    ops.kv_rows_copy(packed, other, 123, dst_idx=where, status=status)             # scatter
+    assert torch.equal(other[where], cache[idx]) and int(status.item()) == 0
+    bad = where.clone()
+    bad[5] = 500                                                                    # past the last row: skipped, reported
+    before = other.clone()
+    ops.kv_rows_copy(packed, other, 123, dst_idx=bad, status=status)
+    assert int(status.item()) == ops._lib.ERR_CAPACITY
+    assert torch.equal(other, before)
+
+
+def test_ep_plan_places_every_rank_and_reports_overflow(ops):
+    world, local = 4, 3
+    g = torch.Generator().manual_seed(1)
+    counts = torch.randint(0, 50, (world, world * local), generator=g, dtype=torch.int32)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    seen = {}
+    for rank in range(world):
+        dest = torch.zeros(world * local, dtype=torch.int32, device="cuda")
+        offs = torch.zeros(world * local + 1, dtype=torch.int32, device="cuda")
+        ops.ep_plan(counts.cuda(), rank, 10 ** 6, dest, offs, status)
+        seen[rank] = (dest.cpu(), offs.cpu())
+    assert int(status.item()) == 0
+    for owner in range(world):
+        # the owner's slab: groups ordered (source rank, local expert); sources write where the owner reads
+        want, at = [], 0
+        for src in range(world):
+            for le in range(local):
+                want.append(at)
+                assert int(seen[src][0][owner * local + le]) == at, (owner, src, le)
+                at += int(counts[src, owner * local + le])
+        assert seen[owner][1].tolist() == want + [at]
+    # a slab smaller than the rows routed to rank 0 is reported
+    ops.ep_plan(counts.cuda(), 0, 8, torch.zeros(world * local, dtype=torch.int32, device="cuda"),
+                torch.zeros(world * local + 1, dtype=torch.int32, device="cuda"), status)
+    assert int(status.item()) == ops._lib.ERR_CAPACITY
+
+
+def test_peer_barrier_gives_up_when_a_rank_never_arrives(ops):
+    """Two ranks' flag words on ONE GPU, only rank 0 runs: its wait for rank 1 runs out after the
+    limit (50 ms here), the kernel sets the status word and returns, and the context stays usable.
+    A second barrier with both ranks' kernels run one after the other cannot be tested on one GPU
+    (kernels that wait on one another must not share a GPU), so rank 1's arrival is written by hand."""
+    flags = torch.zeros((2, 3), dtype=torch.int32, device="cuda")          # [rank][world + 1]
+    bases = torch.tensor([flags[0].data_ptr(), flags[1].data_ptr()], dtype=torch.int64, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ops.peer_barrier(bases.data_ptr(), 0, 2, status, timeout_ms=50)
+    torch.cuda.synchronize()
+    assert int(status.item()) == ops._lib.ERR_DEVICE_TIMEOUT
+    assert flags[1, 0].item() == 1 and flags[0, 0].item() == 1             # rank 0 announced barrier 1 to both
+    status.zero_()
+    flags[0, 1] = 2                                                         # "rank 1" has already reached barrier 2
+    ops.peer_barrier(bases.data_ptr(), 0, 2, status, timeout_ms=50)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0 and flags[0, 2].item() == 2
