@@ -60,7 +60,8 @@ int msl_gemm_bf16(const void* a, int64_t lda, const void* b, int64_t ldb, void* 
  * (splits * m * n * 4 bytes of caller-owned device memory, 16-byte aligned); a second kernel sums the
  * planes in a fixed order, applies alpha and writes c (MSL_OUT_BF16 or MSL_OUT_F32; n and ldc multiples
  * of 4).  msl_gemm_splitk_plan recommends the slice count from the sizes alone (1 = call
- * msl_gemm_bf16).  The reference leaves these products to cuBLAS (submission.py:1082,1096,1113). */
+ * msl_gemm_bf16; always 1 when the environment has MSL_GEMM_SPLITK=0: slicing K changes the order of the
+ * fp32 sums, so a product's low bits then depend on its number of rows).  The reference leaves these products to cuBLAS (submission.py:1082,1096,1113). */
 int msl_gemm_splitk_plan(int m, int n, int k, int segs, int out_mode);
 int msl_gemm_bf16_splitk(const void* a, int64_t lda, const void* b, int64_t ldb, void* c, int64_t ldc, int m, int n,
                          int k, int segs, int a_seg_stride, int b_seg_stride, int out_mode, float alpha, int splits,

@@ -635,6 +635,10 @@ extern "C" int msl_gemm_bf16(const void* a, int64_t lda, const void* b, int64_t 
 
 extern "C" int msl_gemm_splitk_plan(int m, int n, int k, int segs, int out_mode) {
   if (m <= 0 || n <= 0 || k <= 0 || segs < 1 || out_mode == MSL_OUT_SWIGLU_BF16 || (n & 3)) return 1;
+  // Slicing K changes the order of the fp32 sums, so a product's low bits then depend on how many rows
+  // it has; MSL_GEMM_SPLITK=0 keeps every product in one pass for hosts that need batch-invariant bits.
+  const char* env = getenv("MSL_GEMM_SPLITK");
+  if (env && env[0] == '0') return 1;
   const bool narrow_n = n <= 128 || (n % 256 != 0 && n % 128 == 0);
   const int64_t tiles = static_cast<int64_t>((m + kBM - 1) / kBM) * ((n + (narrow_n ? 127 : 255)) / (narrow_n ? 128 : 256));
   const int k_blocks = ((k + kBK - 1) / kBK) * segs;

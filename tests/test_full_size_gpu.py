@@ -1,0 +1,191 @@
+"""BASELINE configuration 3 at its full size (4 x 4096 tokens, hidden 4096, 32q/8kv x 128, 128 experts
+top-8 x 1536 NVFP4 + shared 4096), where the CPU oracle would take minutes: properties that do not
+depend on the size tie the full-size run to runs the oracle does check.
+
+* the layer writes exactly the new tokens' cache rows, is repeatable bit for bit, and gives a request
+  the same bits whether it runs alone or in the full batch;
+* the same full-width layer on one short request passes the oracle's layer check;
+* dispatch is a permutation of the routes, the grouped expert GEMM is linear under exact scalings and
+  agrees with a dense product on sampled experts, top-k ids equal an fp64 top-k wherever the score gap
+  is clear, attention is causal (later tokens cannot change earlier outputs).
+"""
+import dataclasses
+
+import pytest
+import torch
+
+from conftest import to_device
+from oracle import layer_ref as L
+
+pytestmark = pytest.mark.gpu
+
+SEQS, SEQ_LEN = 4, 4096
+
+
+@pytest.fixture(scope="module")
+def full():
+    from muse_spark_open_challenge_b200 import layer, synth
+    shape = synth.MID
+    weights = synth.make_weights(shape, seed=0, device="cuda")
+    data = synth.make_input(shape, [SEQ_LEN] * SEQS, [0] * SEQS, seed=1, page=64, kv_scale=1.0, device="cuda",
+                            fill_cache=False)
+    st = layer.prepare(weights)
+    return shape, weights, data, st
+
+
+def test_full_size_layer_cache_rows_repeatability_and_batch_independence(full, monkeypatch):
+    from muse_spark_open_challenge_b200 import layer, synth
+    # split-K (used for the router product of the 4096-token batch, not of the 16384-token one) sums in
+    # another order: switched off so that both batches run the same arithmetic
+    monkeypatch.setenv("MSL_GEMM_SPLITK", "0")
+    shape, weights, data, st = full
+    t = SEQS * SEQ_LEN
+    hidden, stream, ids = layer.kernel_fn(data, st)
+    torch.cuda.synchronize()
+    layer.check_status(st)
+    assert hidden.shape == (t, shape.hidden) and stream.shape == (t, shape.hidden) and ids.shape == (t, shape.top_k)
+    assert torch.isfinite(hidden.float()).all() and torch.isfinite(stream).all()
+    assert int(ids.min()) >= 0 and int(ids.max()) < shape.n_experts
+    assert (ids.sort(-1).values.diff(dim=-1) > 0).all()                  # k distinct experts per token
+    # exactly the new tokens' rows of the (zero-initialised) caches were written
+    rows = shape.hkv * shape.head_dim
+    for name in ("k_cache", "v_cache"):
+        touched = data[name].view(torch.uint8).view(-1, rows).any(dim=1).nonzero().flatten()
+        assert torch.equal(touched, data["cache_loc"].sort().values), name
+    # repeatable bit for bit (atomics only decide slab positions, never values)
+    again = layer.kernel_fn(data, st)
+    torch.cuda.synchronize()
+    assert all(torch.equal(a, b) for a, b in zip(again, (hidden, stream, ids)))
+    # request 0 alone: the same bits as inside the batch of four
+    one = synth.make_input(shape, [SEQ_LEN], [0], seed=9, page=64, kv_scale=1.0, device="cuda", fill_cache=False)
+    one["stream"], one["attn_input"] = data["stream"][:SEQ_LEN].clone(), data["attn_input"][:SEQ_LEN].clone()
+    h1, s1, i1 = layer.kernel_fn(one, st)
+    torch.cuda.synchronize()
+    layer.check_status(st)
+    assert torch.equal(i1, ids[:SEQ_LEN]), "expert ids depend on the batch"
+    assert torch.equal(s1, stream[:SEQ_LEN]), "the residual stream depends on the batch"
+    assert torch.equal(h1, hidden[:SEQ_LEN]), "the hidden state depends on the batch"
+    new_k = one["k_cache"].view(torch.uint8).view(-1, rows)[one["cache_loc"]]
+    assert torch.equal(new_k, data["k_cache"].view(torch.uint8).view(-1, rows)[data["cache_loc"][:SEQ_LEN]])
+
+
+def test_full_width_layer_on_a_short_request_matches_the_oracle(full):
+    from muse_spark_open_challenge_b200 import layer, synth
+    shape, weights, _, st = full
+    data_cpu = synth.make_input(shape, [300], [84], seed=5, page=64, kv_scale=1.0)
+    weights_cpu = {k: v.cpu() for k, v in weights.items()}
+    data = to_device(data_cpu, "cuda")
+    hidden, stream, ids = layer.kernel_fn(data, st)
+    torch.cuda.synchronize()
+    layer.check_status(st)
+    d = L.dims_of(weights_cpu, data_cpu["config"])
+    slots = L.new_slots(data_cpu).cuda()
+    k_rows = data["k_cache"].view(-1, d.hkv, d.head_dim)[slots].cpu()
+    v_rows = data["v_cache"].view(-1, d.hkv, d.head_dim)[slots].cpu()
+    ok, msg, rep = L.check_layer(data_cpu, weights_cpu, hidden.cpu(), stream.cpu(), ids.cpu(), k_rows, v_rows)
+    print(msg, rep)
+    assert ok, msg
+
+
+def test_full_size_routing_and_dispatch(full):
+    from muse_spark_open_challenge_b200 import layer, ops
+    shape, weights, data, st = full
+    t, k, e = SEQS * SEQ_LEN, shape.top_k, shape.n_experts
+    g = torch.Generator(device="cuda").manual_seed(2)
+    h = torch.randn((t, shape.hidden), generator=g, device="cuda").to(torch.bfloat16)
+    logits = ops.gemm(h, st["router_hilo"], out_mode=ops.OUT_F32, k=shape.hidden, segs=2, a_seg_stride=0,
+                      b_seg_stride=shape.hidden)
+    counts = torch.zeros(e, dtype=torch.int32, device="cuda")
+    zero = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ids, tw, local_ids, slots = ops.route_topk(logits, st["router_bias"], layer.ROUTER_MULTIPLIER, zero, e, k, e, counts)
+    # ids against an fp64 top-k of the fp64 product, wherever the k-th / (k+1)-th gap is clear
+    scores = torch.sigmoid(layer.ROUTER_MULTIPLIER * (h.double() @ weights["router"].double().T))
+    biased = scores + weights["router_bias"].double()
+    top = biased.topk(k + 1, dim=-1)
+    clear = (top.values[:, k - 1] - top.values[:, k]) > 1e-4
+    same = (ids.long().sort(-1).values == top.indices[:, :k].sort(-1).values).all(-1)
+    assert same[clear].all() and float(clear.float().mean()) > 0.97
+    picked = scores.gather(1, ids.long())
+    assert torch.allclose(tw.double(), picked / (picked.sum(-1, keepdim=True) + 1e-15), rtol=1e-5, atol=1e-7)
+    assert int(counts.sum()) == t * k and torch.equal(counts.long(), torch.bincount(ids.flatten().long(), minlength=e))
+    # dispatch: every route's slab row is its token's row; rows of one expert are contiguous
+    slab = torch.empty((t * k, shape.hidden), dtype=torch.bfloat16, device="cuda")
+    offsets = torch.zeros(e + 1, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    rowmap = ops.dispatch(h, None, local_ids, slots, counts, slab, offsets, status)
+    assert int(status.item()) == 0
+    assert torch.equal(rowmap.flatten().long().sort().values, torch.arange(t * k, device="cuda"))       # a permutation
+    assert torch.equal(offsets.long(), torch.cat([torch.zeros(1, dtype=torch.long, device="cuda"), counts.long().cumsum(0)]))
+    owner = torch.bucketize(rowmap.long(), offsets[1:].long(), right=True)
+    assert torch.equal(owner, ids.long())
+    for j in range(k):
+        assert torch.equal(slab[rowmap[:, j].long()], h)
+
+
+def test_full_size_grouped_gemm_linearity_and_sampled_experts(full):
+    from muse_spark_open_challenge_b200 import ops
+    shape, weights, _, st = full
+    e, rows_per = shape.n_experts, 1024
+    total = e * rows_per
+    g = torch.Generator(device="cuda").manual_seed(3)
+    x = torch.randn((total, shape.moe_width), generator=g, device="cuda").to(torch.bfloat16)
+    offsets = torch.arange(0, total + 1, rows_per, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    inter = torch.empty((total, shape.inter), dtype=torch.bfloat16, device="cuda")
+    ops.grouped_gemm_nvfp4(x, st["w13_q"], st["w13_s"], st["w13_gs"], offsets, inter, shape.inter, True, status)
+    y = torch.empty((total, shape.moe_width), dtype=torch.bfloat16, device="cuda")
+    ops.grouped_gemm_nvfp4(inter, st["w2_q"], st["w2_s"], st["w2_gs"], offsets, y, shape.moe_width, False, status)
+    # exact scalings commute with the down product bit for bit (bf16 in, fp32 accumulate, bf16 out)
+    y4 = torch.empty_like(y)
+    ops.grouped_gemm_nvfp4((inter.float() * 4).to(torch.bfloat16), st["w2_q"], st["w2_s"], st["w2_gs"], offsets, y4,
+                           shape.moe_width, False, status)
+    assert int(status.item()) == 0
+    assert torch.equal(y4.float(), y.float() * 4)
+    # sampled experts against dense fp32 products with the oracle's dequantised weights
+    for ex in (0, 37, 127):
+        w13 = L.nvfp4_dequantize(weights["w13"][ex].cpu(), weights["w13_sf"][ex].cpu(), weights["w13_gs"][ex].cpu()).cuda()
+        w2 = L.nvfp4_dequantize(weights["w2"][ex].cpu(), weights["w2_sf"][ex].cpu(), weights["w2_gs"][ex].cpu()).cuda()
+        sl = slice(ex * rows_per, (ex + 1) * rows_per)
+        hh = x[sl].float() @ w13.T
+        ref_inter = torch.nn.functional.silu(hh[:, :shape.inter]) * hh[:, shape.inter:]
+        assert L.relative_l2(inter[sl].float(), ref_inter) < 4e-3, ex
+        assert L.relative_l2(y[sl].float(), inter[sl].float() @ w2.T) < 4e-3, ex
+
+
+def test_full_size_attention_is_causal(full):
+    from muse_spark_open_challenge_b200 import ops
+    shape, _, data, _ = full
+    cfg = data["config"]
+    t = SEQS * SEQ_LEN
+    g = torch.Generator(device="cuda").manual_seed(4)
+    q8 = torch.randn((t, shape.hq, shape.head_dim), generator=g, device="cuda").to(torch.float8_e4m3fn)
+    kc = torch.zeros_like(data["k_cache"])
+    vc = torch.zeros_like(data["v_cache"])
+    rows = lambda c: c.view(-1, shape.hkv, shape.head_dim)                                       # noqa: E731
+    rows(kc)[data["cache_loc"]] = torch.randn((t, shape.hkv, shape.head_dim), generator=g, device="cuda").to(kc.dtype)
+    rows(vc)[data["cache_loc"]] = torch.randn((t, shape.hkv, shape.head_dim), generator=g, device="cuda").to(vc.dtype)
+    run = lambda q, k, v: ops.attention(q, k, v, data["page_table"], data["seq_lens"], data["cu_seqlens_q"],   # noqa: E731
+                                        data["k_scale"], data["v_scale"], cfg["sm_scale"] * cfg["qk_scale_factor"],
+                                        cfg["batch"], cfg["q_len"], shape.hq, shape.hkv, shape.head_dim, 64, 0)
+    base = run(q8, kc, vc)
+    # change everything from position 2000 on in every request: keys, values and queries
+    cut = 2000
+    later = (data["positions"] >= cut)
+    q2, k2, v2 = q8.clone(), kc.clone(), vc.clone()
+    n_later = int(later.sum())
+    q2[later] = torch.randn((n_later, shape.hq, shape.head_dim), generator=g, device="cuda").to(q8.dtype)
+    rows(k2)[data["cache_loc"][later]] = torch.randn((n_later, shape.hkv, shape.head_dim), generator=g, device="cuda").to(kc.dtype)
+    rows(v2)[data["cache_loc"][later]] = torch.randn((n_later, shape.hkv, shape.head_dim), generator=g, device="cuda").to(vc.dtype)
+    moved = run(q2, k2, v2)
+    assert torch.equal(moved[~later], base[~later])
+    assert not torch.equal(moved[later], base[later])
+    # one request, four heads, against an fp32 softmax on the GPU
+    n, heads = SEQ_LEN, 4
+    qf = q8[:n, :heads].float() * cfg["qk_scale_factor"]
+    kf = rows(kc)[data["cache_loc"][:n]][:, 0].float() * float(data["k_scale"])
+    vf = rows(vc)[data["cache_loc"][:n]][:, 0].float() * float(data["v_scale"])
+    s = torch.einsum("qhd,kd->hqk", qf, kf) * cfg["sm_scale"]
+    s = s.masked_fill(torch.ones((n, n), dtype=torch.bool, device="cuda").triu(1), float("-inf"))
+    ref = torch.einsum("hqk,kd->qhd", torch.softmax(s, dim=-1), vf)
+    got = base[:n].view(n, shape.hq, shape.head_dim)[:, :heads].float()
+    assert L.relative_l2(got, ref) < 3e-2
