@@ -363,9 +363,10 @@ def main():
     seq_ctx = None
     long_lens = None
     if args.workload == "long":
-        # BASELINE config 4: sequences of about 32768 tokens prefilled in chunks of 8192 +- 7.5 % with odd
-        # tails, one chunk per rank (4 chunks per sequence, 2 sequences on 8 GPUs), 256 experts sharded
-        # over the ranks.  The K/V rows of a sequence's earlier chunks reach a rank by the hand-off.
+        # Long prefill (configuration 4): sequences of about 32768 tokens prefilled as pieces of 4096 +- 7.5 %
+        # tokens with odd tails, two pieces per rank (4 ranks per sequence, 2 sequences on 8 GPUs), 256
+        # experts sharded over the ranks.  The K/V rows of a sequence's earlier pieces reach a request by
+        # the hand-off inside the step.
         import dataclasses
         from muse_spark_open_challenge_b200 import synth
         per_seq = min(4, world)
