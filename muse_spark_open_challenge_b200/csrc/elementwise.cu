@@ -513,27 +513,38 @@ __global__ void peer_barrier_kernel(int* const* __restrict__ flag_bases, int ran
 // ============================================================================ weighted combine
 // out[t] = sum_j w[t,j] * rms(y[rowmap[t,j]] * post_w, 1e-8) (+ addend[t]).  One block per token.  The
 // routes that have a slab row (rowmap >= 0; under the reference's sharding only the local experts'
-// routes do) are taken kStage at a time: their rows are brought into shared memory with asynchronous
-// copies (no registers held while they are in flight; the small footprint lets many blocks per SM keep
-// bytes outstanding), then read twice from shared memory: once for the sums of squares, once for the
-// weighted accumulation, which stays in registers across the rounds.  Each row crosses HBM exactly once.
-constexpr int kCombineStage = 4;        // rows staged per round from local memory
+// routes do) are compacted in route order and taken kBulkRows at a time: one elected thread moves whole
+// rows global -> shared memory with cp.async.bulk (TMA, completion on an mbarrier) into one of two
+// buffers, so the rows of round r + 1 are in flight while the block reduces round r (sums of squares,
+// then the weighted accumulation, which stays in registers across the rounds; post_w multiplies the sum
+// once at the end: sum_j w_j rms(y_j post_w) = post_w sum_j r_j y_j with r_j = w_j / sqrt(mean((y_j
+// post_w)^2) + eps)).  Each row crosses HBM exactly once; 32 KB of shared memory per block at width 4096
+// lets five blocks per SM keep bytes outstanding.  (Measured at 16384 tokens x 8 rows of 8 KB: two rows
+// per buffer 315 us, one 349 us, four 372 us; the same rounds staged with 16-byte cp.async 335 us.)
 constexpr int kCombineThreads = 256;
 constexpr int kCombineMaxChunks = 4;    // 8-element chunks per thread: width <= 8192 (MAXC = 2: <= 4096)
+constexpr int kBulkRows = 2;
+
+__device__ __forceinline__ void bulk_row_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
 
 template <int MAXC>
-__global__ void __launch_bounds__(kCombineThreads, MAXC <= 2 ? 5 : 4)
+__global__ void __launch_bounds__(kCombineThreads, MAXC <= 2 ? 5 : 3)
 combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ rowmap, const float* __restrict__ w,
-               const float* __restrict__ post_w, const __nv_bfloat16* __restrict__ addend, int64_t ld_add,
-               __nv_bfloat16* __restrict__ out, int64_t ld_out, int top_k, int width) {
+                    const float* __restrict__ post_w, const __nv_bfloat16* __restrict__ addend, int64_t ld_add,
+                    __nv_bfloat16* __restrict__ out, int64_t ld_out, int top_k, int width) {
   constexpr int THREADS = kCombineThreads;
-  constexpr int STAGE = kCombineStage;
-  extern __shared__ __align__(16) uint8_t rows_smem[];      // [STAGE][width] bf16
-  __shared__ float scratch[32 * STAGE];
+  constexpr int R = kBulkRows;
+  extern __shared__ __align__(128) uint8_t rows_smem[];     // [2][R][width] bf16
+  __shared__ __align__(8) uint64_t bars[2];
+  __shared__ float scratch[32 * R];
   __shared__ int route_of[32], row_of[32];
   __shared__ int n_valid_s;
   const int t = blockIdx.x;
   const int chunks = width / 8;
+  const uint32_t row_bytes = static_cast<uint32_t>(width) * 2u;
   if (threadIdx.x < 32) {                                   // compact the routes that have a row, in route order
     const int j = threadIdx.x;
     const int row = j < top_k ? rowmap[t * top_k + j] : -1;
@@ -543,34 +554,41 @@ combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ rowm
       route_of[at] = j;
       row_of[at] = row;
     }
-    if (j == 0) n_valid_s = __popc(have);
+    if (j == 0) {
+      n_valid_s = __popc(have);
+      mbar_init(&bars[0], 1);
+      mbar_init(&bars[1], 1);
+      mbar_fence_init();
+    }
   }
   __syncthreads();
   const int n_valid = n_valid_s;
-  // acc = sum_j r_j y_j; post_w multiplies once at the end: sum_j w_j rms(y_j post_w) = post_w sum_j r_j y_j
-  // with r_j = w_j / sqrt(mean((y_j post_w)^2) + eps).
+  const int n_rounds = (n_valid + R - 1) / R;
+  auto issue = [&](int r) {                                 // thread 0 only
+    const int n = min(R, n_valid - r * R);
+    uint64_t* bar = &bars[r & 1];
+    mbar_expect_tx(bar, n * row_bytes);
+    for (int q = 0; q < n; ++q)
+      bulk_row_load(rows_smem + (static_cast<size_t>((r & 1) * R + q)) * row_bytes,
+                    y + static_cast<int64_t>(row_of[r * R + q]) * width, row_bytes, bar);
+  };
+  if (threadIdx.x == 0) {
+    if (n_rounds > 0) issue(0);
+    if (n_rounds > 1) issue(1);
+  }
   float acc[MAXC][8];
 #pragma unroll
   for (int c = 0; c < MAXC; ++c) {
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[c][i] = 0.f;
   }
-  for (int base = 0; base < n_valid; base += STAGE) {
-    const int n_round = min(STAGE, n_valid - base);
-    for (int q = 0; q < n_round; ++q) {
-      const int row = row_of[base + q];
-      const __nv_bfloat16* src = y + static_cast<int64_t>(row) * width;
-      for (int ch = threadIdx.x; ch < chunks; ch += THREADS) {
-        const uint32_t dst = smem_u32(rows_smem + (static_cast<size_t>(q) * width + ch * 8) * 2);
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src + ch * 8) : "memory");
-      }
-    }
-    asm volatile("cp.async.commit_group;" ::: "memory");
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-    __syncthreads();
-    float ss[STAGE];
+  for (int r = 0; r < n_rounds; ++r) {
+    const int n_round = min(R, n_valid - r * R);
+    const uint8_t* buf = rows_smem + static_cast<size_t>((r & 1) * R) * row_bytes;
+    mbar_wait(&bars[r & 1], (r >> 1) & 1);                  // a bulk copy of mapped memory always lands
+    float ss[R];
 #pragma unroll
-    for (int q = 0; q < STAGE; ++q) ss[q] = 0.f;
+    for (int q = 0; q < R; ++q) ss[q] = 0.f;
 #pragma unroll
     for (int c = 0; c < MAXC; ++c) {
       const int ch = threadIdx.x + c * THREADS;
@@ -579,37 +597,39 @@ combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ rowm
         const float4 w1 = *reinterpret_cast<const float4*>(post_w + ch * 8 + 4);
         const float pw[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
-        for (int q = 0; q < STAGE; ++q) {
+        for (int q = 0; q < R; ++q) {
           if (q < n_round) {
             float v[8];
-            unpack8(*reinterpret_cast<const uint4*>(rows_smem + (static_cast<size_t>(q) * width + ch * 8) * 2), v);
+            unpack8(*reinterpret_cast<const uint4*>(buf + static_cast<size_t>(q) * row_bytes + ch * 16), v);
 #pragma unroll
             for (int i = 0; i < 8; ++i) { const float x = v[i] * pw[i]; ss[q] += x * x; }
           }
         }
       }
     }
-    block_sum<STAGE>(ss, scratch);
-    float r[STAGE];
+    block_sum<R>(ss, scratch);
+    float rr[R];
 #pragma unroll
-    for (int q = 0; q < STAGE; ++q)
-      r[q] = q < n_round ? w[t * top_k + route_of[base + q]] / sqrtf(ss[q] / width + 1e-8f) : 0.f;
+    for (int q = 0; q < R; ++q)
+      rr[q] = q < n_round ? w[t * top_k + route_of[r * R + q]] / sqrtf(ss[q] / width + 1e-8f) : 0.f;
 #pragma unroll
     for (int c = 0; c < MAXC; ++c) {
       const int ch = threadIdx.x + c * THREADS;
       if (ch < chunks) {
 #pragma unroll
-        for (int q = 0; q < STAGE; ++q) {
+        for (int q = 0; q < R; ++q) {
           if (q < n_round) {
             float v[8];
-            unpack8(*reinterpret_cast<const uint4*>(rows_smem + (static_cast<size_t>(q) * width + ch * 8) * 2), v);
+            unpack8(*reinterpret_cast<const uint4*>(buf + static_cast<size_t>(q) * row_bytes + ch * 16), v);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) acc[c][i] += v[i] * r[q];
+            for (int i = 0; i < 8; ++i) acc[c][i] += v[i] * rr[q];
           }
         }
       }
     }
-    __syncthreads();                                        // the staging rows are free for the next round
+    fence_async_smem();                                     // generic reads of the buffer before its next bulk write
+    __syncthreads();
+    if (threadIdx.x == 0 && r + 2 < n_rounds) issue(r + 2);
   }
 #pragma unroll
   for (int c = 0; c < MAXC; ++c) {
@@ -630,9 +650,10 @@ combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ rowm
 // Peer form: the rows live in the expert-owning ranks' slabs (rowmap holds rank * peer_cap + row) and are
 // read straight from that rank's memory (peer_bases[rank], NVLink): the combine all-to-all of expert
 // parallelism fused into this kernel.  All of a token's rows are requested at once, 512 threads per
-// block, each thread pacing its requests by its own rowmap and pointer loads.  (The staged kernel above,
-// given peer pointers, measured 2.0 ms where this one takes 0.77 ms on two GPUs: a burst of requests from
-// every block at once does not suit NVLink reads.)
+// block, every thread copying 16 bytes of each row with cp.async and pacing its requests by its own rowmap
+// and pointer loads.  (A kernel that staged compacted rows in rounds, given peer pointers, measured 2.0 ms
+// where this one takes 0.77 ms on two GPUs: a burst of requests from every block at once does not suit
+// NVLink reads.)
 template <int MAXK>
 __global__ void __launch_bounds__(512)
 combine_peer_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ rowmap, const float* __restrict__ w,
@@ -819,7 +840,7 @@ static int combine_launch(const void* y, const int* rowmap, const float* weights
   constexpr int kPeerSmemMax = 200 * 1024;
   static bool configured = false;
   if (!configured) {
-    const int most = kCombineStage * 8 * kCombineThreads * kCombineMaxChunks * 2;
+    const int most = 2 * kBulkRows * 8 * kCombineThreads * kCombineMaxChunks * 2;
     if (cudaFuncSetAttribute(combine_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, most) != cudaSuccess ||
         cudaFuncSetAttribute(combine_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, most) != cudaSuccess ||
         cudaFuncSetAttribute(combine_peer_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPeerSmemMax) !=
@@ -846,7 +867,8 @@ static int combine_launch(const void* y, const int* rowmap, const float* weights
       combine_peer_kernel<8><<<tokens, threads, smem, st>>>(yy, rowmap, weights, post_w, ad, ld_addend, oo, ld_out,
                                                             top_k, width, pb, peer_cap);
   } else {
-    const int smem = kCombineStage * width * 2;             // <= 64 KB
+    if (reinterpret_cast<uintptr_t>(y) & 15) return MSL_ERR_ALIGN;
+    const int smem = 2 * kBulkRows * width * 2;             // two buffers: 32 KB at width 4096
     if (width <= 8 * kCombineThreads * 2)
       combine_kernel<2><<<tokens, kCombineThreads, smem, st>>>(yy, rowmap, weights, post_w, ad, ld_addend, oo, ld_out,
                                                                top_k, width);
