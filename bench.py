@@ -302,20 +302,20 @@ def run_native(args):
                       "launch": "CUDA graph replay, L2 flushed before every replay, median", "shapes": rows}))
 
 
-def enable_peer_or_collective(ep, dist, ctx, st, max_tokens, top_k):
+def enable_peer_or_collective(ep, dist, ctx, st, max_tokens, top_k, push=False):
     """Map the ranks' row slabs into one another; when the platform cannot (no peer access between the
     GPUs, symmetric memory unavailable) every rank keeps the NCCL all-to-all transport and the line says so."""
     ok = torch.ones(1, device=st["device"])
     why = ""
     try:
-        ep.enable_peer(ctx, st, max_tokens=max_tokens, top_k=top_k)
+        ep.enable_peer(ctx, st, max_tokens=max_tokens, top_k=top_k, push=push)
     except Exception as exc:  # noqa: BLE001 - any failure of the mapping selects the other transport
         ok.zero_()
         why = f"{type(exc).__name__}: {exc}"[:200]
         ctx.peer = None
     dist.all_reduce(ok, op=dist.ReduceOp.MIN)
     if ok.item() > 0:
-        return "peer"
+        return "peer-push" if push else "peer"
     ctx.peer = None
     return "collective (peer memory unavailable" + (": " + why if why else " on another rank") + ")"
 
@@ -330,9 +330,10 @@ def main():
     ap.add_argument("--workload", default="layer", choices=["layer", "attn", "moe", "native", "long"],
                     help="layer = the headline full-layer step; attn / moe = the op-only configurations")
     ap.add_argument("--small", action="store_true", help="reduced op workload, sized for an ncu capture")
-    ap.add_argument("--transport", default="peer", choices=["peer", "collective"],
+    ap.add_argument("--transport", default="peer", choices=["peer", "peer-push", "collective"],
                     help="expert-parallel row exchange (N > 1): peer-memory stores/loads fused into the dispatch and "
-                         "combine kernels, or NCCL all-to-alls")
+                         "combine kernels (peer-push: outputs returned by the down GEMM's epilogue instead), or NCCL "
+                         "all-to-alls")
     ap.add_argument("--eager", action="store_true", help="time eager launches instead of a CUDA-graph replay")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -393,9 +394,10 @@ def main():
             groups = [dist.new_group(list(range(s0 * per_seq, (s0 + 1) * per_seq))) for s0 in range(world // per_seq)]
             st = layer.prepare(weights)
             ctx = ep.ExpertParallel(st, world, rank, n_exp)
-            if args.transport == "peer":
+            if args.transport.startswith("peer"):
                 most = max(l[c] + l[2 * per_seq - 1 - c] for l in long_lens for c in range(per_seq))
-                args.transport = enable_peer_or_collective(ep, dist, ctx, st, most, shape.top_k)
+                args.transport = enable_peer_or_collective(ep, dist, ctx, st, most, shape.top_k,
+                                                           push=args.transport == "peer-push")
             seq_ctx = ep.ChunkedSequence(groups[my_seq], my_chunk, lens, shape.hkv, shape.head_dim, dev, owners=owners)
             step = lambda d: ep.kernel_fn(d, st, ctx, seq_ctx)  # noqa: E731
         else:
@@ -410,8 +412,9 @@ def main():
                 dist.broadcast(v, 0)
         st = layer.prepare(weights)
         ctx = ep.ExpertParallel(st, world, rank, shape.n_experts)
-        if args.transport == "peer":
-            args.transport = enable_peer_or_collective(ep, dist, ctx, st, data["config"]["tokens"], shape.top_k)
+        if args.transport.startswith("peer"):
+            args.transport = enable_peer_or_collective(ep, dist, ctx, st, data["config"]["tokens"], shape.top_k,
+                                                       push=args.transport == "peer-push")
         step = lambda d: ep.kernel_fn(d, st, ctx)  # noqa: E731
     else:
         seqs = 1 if args.small else SEQS                     # --small: one request, sized for an ncu capture

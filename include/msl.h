@@ -155,10 +155,12 @@ int msl_peer_barrier(int* const* flag_bases, int rank, int world, int timeout_ms
  * ranks' bf16 [cap, width] slabs; ids i32 [tokens, top_k] are global expert ids, slots the ranks
  * within (this rank, expert) from msl_route_topk.  The row of route (t, j) lands at
  * peer_bases[e / local_experts] + (dest_base[e] + slot) * width; rowmap receives
- * rank * cap + row (or -1 for a row beyond cap).  Optional RMS norm as in msl_dispatch. */
+ * rank * cap + row (or -1 for a row beyond cap).  Optional RMS norm as in msl_dispatch.  With
+ * index_bases != NULL (a DEVICE array of `world` pointers to the ranks' i32 [cap] arrays) the owner also
+ * learns where to return the route's output: index_bases[owner][row] = t * top_k + j. */
 int msl_dispatch_peer(const void* x, int64_t ldx, const float* norm_w, const int* ids, const int* slots,
                       const int* dest_base, void* const* peer_bases, int local_experts, int cap, int tokens,
-                      int top_k, int width, int* rowmap, void* stream);
+                      int top_k, int width, int* rowmap, int* const* index_bases, void* stream);
 
 /* msl_combine with the rows read from the owning ranks' slabs (rowmap from msl_dispatch_peer). */
 int msl_combine_peer(const void* const* peer_bases, int peer_cap, const int* rowmap, const float* weights,
@@ -198,6 +200,18 @@ int msl_nvfp4_repack(const void* src_codes, const void* src_scales, void* dst_co
 int msl_grouped_gemm_nvfp4(const void* x, int64_t slab_rows, const void* codes, const void* scales,
                            const float* global_scales, const int* offsets, void* out, int64_t ld_out, int experts,
                            int weight_experts, int n_padded, int k, int n_out, int swiglu, int* status, void* stream);
+
+/* msl_grouped_gemm_nvfp4 (no SwiGLU) whose output rows are scattered, possibly into other GPUs: row r
+ * of group g is stored to scatter_bases[g / scatter_div] + scatter_index[r] * ld_out.  scatter_bases is
+ * a DEVICE array of bf16 row-buffer pointers (peer-mapped for the other ranks), scatter_index i32 [slab
+ * rows] as filled by msl_dispatch_peer.  Under expert parallelism (groups = (source rank, expert),
+ * scatter_div = local experts) the down projection thus returns every output row to the rank that owns
+ * its token while the GEMM runs: the combine exchange rides on the epilogue.  No counterpart in the
+ * reference (its cross-GPU steps are identities, reference.py:438,451,467). */
+int msl_grouped_gemm_nvfp4_scatter(const void* x, int64_t slab_rows, const void* codes, const void* scales,
+                                   const float* global_scales, const int* offsets, int64_t ld_out, int experts,
+                                   int weight_experts, int n_padded, int k, int n_out, void* const* scatter_bases,
+                                   const int* scatter_index, int scatter_div, int* status, void* stream);
 
 /* Causal attention of the new tokens over the paged FP8 cache (which already holds the new
  * tokens' K/V rows): q8 e4m3 [tokens, hq, head_dim]; caches e4m3 [cache_rows, hkv, head_dim];

@@ -32,12 +32,13 @@ SIGNATURES = {
     "msl_combine": (_i, [_p, _p, _p, _p, _p, _i64, _p, _i64, _i, _i, _i, _p]),
     "msl_ep_plan": (_i, [_p, _i, _i, _i, _i, _p, _p, _p, _p]),
     "msl_peer_barrier": (_i, [_p, _i, _i, _i, _p, _p]),
-    "msl_dispatch_peer": (_i, [_p, _i64, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p, _p]),
+    "msl_dispatch_peer": (_i, [_p, _i64, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p, _p, _p]),
     "msl_combine_peer": (_i, [_p, _i, _p, _p, _p, _p, _i64, _p, _i64, _i, _i, _i, _p]),
     "msl_kv_rows_copy": (_i, [_p, _p, _i64, _p, _p, _i64, _i64, _i, _p, _p]),
     "msl_nvfp4_padded_rows": (_i64, [_i, _i]),
     "msl_nvfp4_repack": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _p]),
     "msl_grouped_gemm_nvfp4": (_i, [_p, _i64, _p, _p, _p, _p, _p, _i64, _i, _i, _i, _i, _i, _i, _p, _p]),
+    "msl_grouped_gemm_nvfp4_scatter": (_i, [_p, _i64, _p, _p, _p, _p, _i64, _i, _i, _i, _i, _i, _p, _p, _i, _p, _p]),
     "msl_attention_fp8": (_i, [_p, _p, _p, _p, _i, _p, _p, _p, _p, _f, _i, _i, _i, _i, _i, _i, _i, _i, _i64, _p,
                                _i64, _p, _i64, _p, _p]),
     "msl_attention_split_plan": (_i, [_i, _i, _i, _i, _i, _i, _i]),

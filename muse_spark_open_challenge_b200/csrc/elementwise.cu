@@ -441,7 +441,7 @@ __global__ void __launch_bounds__(256)
 dispatch_peer_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, const float* __restrict__ norm_w,
                      const int* __restrict__ ids, const int* __restrict__ slots, const int* __restrict__ dest_base,
                      __nv_bfloat16* const* __restrict__ peer_bases, int el, int cap, int top_k, int width,
-                     int* __restrict__ rowmap) {
+                     int* __restrict__ rowmap, int* const* __restrict__ index_bases) {
   __shared__ float scratch[32];
   const int t = blockIdx.x;
   const int chunks = width / 8;
@@ -463,7 +463,11 @@ dispatch_peer_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, const flo
     const int d = e / el;
     const int row = dest_base[e] + slots[t * top_k + j];
     const bool ok = row < cap;                 // an overflowing slab was already reported by the plan
-    if (threadIdx.x == 0) rowmap[t * top_k + j] = ok ? d * cap + row : -1;
+    if (threadIdx.x == 0) {
+      rowmap[t * top_k + j] = ok ? d * cap + row : -1;
+      // where the owner's down projection returns this route's output row: row t * top_k + j of this rank
+      if (ok && index_bases != nullptr) index_bases[d][row] = t * top_k + j;
+    }
     if (ok) dst[nr++] = peer_bases[d] + static_cast<int64_t>(row) * width;
   }
   for (int ch = threadIdx.x; ch < chunks; ch += blockDim.x) {
@@ -963,7 +967,8 @@ extern "C" int msl_ep_plan(const int* counts_all, int world, int local_experts, 
 
 extern "C" int msl_dispatch_peer(const void* x, int64_t ldx, const float* norm_w, const int* ids, const int* slots,
                                  const int* dest_base, void* const* peer_bases, int local_experts, int cap,
-                                 int tokens, int top_k, int width, int* rowmap, void* stream) {
+                                 int tokens, int top_k, int width, int* rowmap, int* const* index_bases,
+                                 void* stream) {
   if (!x || !ids || !slots || !dest_base || !peer_bases || !rowmap) return MSL_ERR_ARG;
   if (tokens < 0 || local_experts <= 0 || cap <= 0 || top_k <= 0 || top_k > 16 || width <= 0) return MSL_ERR_ARG;
   if ((width & 7) || (ldx & 7) || (reinterpret_cast<uintptr_t>(x) & 15)) return MSL_ERR_ALIGN;
@@ -971,7 +976,7 @@ extern "C" int msl_dispatch_peer(const void* x, int64_t ldx, const float* norm_w
   const int threads = std::min(256, ((width / 8 + 31) / 32) * 32);
   dispatch_peer_kernel<<<tokens, threads, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), ldx, norm_w, ids, slots, dest_base,
-      reinterpret_cast<__nv_bfloat16* const*>(peer_bases), local_experts, cap, top_k, width, rowmap);
+      reinterpret_cast<__nv_bfloat16* const*>(peer_bases), local_experts, cap, top_k, width, rowmap, index_bases);
   return cudaGetLastError() == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
 }
 

@@ -80,6 +80,12 @@ struct GroupedArgs {
   int n_out;               // valid output columns (after the SwiGLU halving when fused)
   int swiglu;
   int* status;
+  // Scattered output (expert parallelism): row r of group g is stored to
+  // scatter_bases[g / scatter_div] + scatter_index[r] * ld_out instead of out + r * ld_out.  The bases may
+  // point into other GPUs' memory: the combine exchange then rides on this kernel's epilogue.
+  void* const* scatter_bases;
+  const int* scatter_index;
+  int scatter_div;
 };
 
 struct TileInfo {
@@ -147,6 +153,9 @@ __device__ __forceinline__ void store_rows(const GroupedArgs& p, const TileInfo&
   // One thread owns row r of the tile: 128 accumulator columns -> 128 (or 64 fused) outputs.
   const bool valid = r < ti.rows;
   __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<int64_t>(ti.row0 + r) * p.ld_out;
+  if (p.scatter_bases != nullptr && valid)
+    orow = reinterpret_cast<__nv_bfloat16*>(p.scatter_bases[ti.expert / p.scatter_div]) +
+           static_cast<int64_t>(p.scatter_index[ti.row0 + r]) * p.ld_out;
   constexpr int kOutCols = SWIGLU ? kGN / 2 : kGN;
 #pragma unroll 1
   for (int c = 0; c < kOutCols; c += 32) {
@@ -545,11 +554,12 @@ extern "C" int msl_nvfp4_repack(const void* src_codes, const void* src_scales, v
   return cudaGetLastError() == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
 }
 
-extern "C" int msl_grouped_gemm_nvfp4(const void* x, int64_t slab_rows, const void* codes, const void* scales,
-                                      const float* global_scales, const int* offsets, void* out, int64_t ld_out,
-                                      int experts, int weight_experts, int n_padded, int k, int n_out, int swiglu,
-                                      int* status, void* stream) {
+static int grouped_entry(const void* x, int64_t slab_rows, const void* codes, const void* scales,
+                         const float* global_scales, const int* offsets, void* out, int64_t ld_out, int experts,
+                         int weight_experts, int n_padded, int k, int n_out, int swiglu, void* const* scatter_bases,
+                         const int* scatter_index, int scatter_div, int* status, void* stream) {
   if (!x || !codes || !scales || !global_scales || !offsets || !out) return MSL_ERR_ARG;
+  if (scatter_bases != nullptr && (!scatter_index || scatter_div <= 0)) return MSL_ERR_ARG;
   if (experts <= 0 || experts > kMaxLocal || weight_experts <= 0 || n_padded <= 0 || k <= 0 || n_out <= 0 ||
       slab_rows < 0)
     return MSL_ERR_ARG;
@@ -562,7 +572,8 @@ extern "C" int msl_grouped_gemm_nvfp4(const void* x, int64_t slab_rows, const vo
                         kSubM, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc) return rc;
   GroupedArgs a{static_cast<const uint8_t*>(codes), static_cast<const uint8_t*>(scales), global_scales, offsets, out,
-                ld_out, experts, n_padded, k, weight_experts, n_out, swiglu, status};
+                ld_out, experts, n_padded, k, weight_experts, n_out, swiglu, status, scatter_bases, scatter_index,
+                scatter_div};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const char* pair_env = getenv("MSL_GROUPED_PAIR");
   const char* wide_env = getenv("MSL_GROUPED_WIDE");
@@ -626,4 +637,23 @@ extern "C" int msl_grouped_gemm_nvfp4(const void* x, int64_t slab_rows, const vo
   const int grid = static_cast<int>(std::min<int64_t>(max_tiles, sm_count()));
   grouped_nvfp4_kernel<kNarrow><<<grid, 448, smem, st>>>(tx, a);
   return cudaGetLastError() == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
+}
+
+extern "C" int msl_grouped_gemm_nvfp4(const void* x, int64_t slab_rows, const void* codes, const void* scales,
+                                      const float* global_scales, const int* offsets, void* out, int64_t ld_out,
+                                      int experts, int weight_experts, int n_padded, int k, int n_out, int swiglu,
+                                      int* status, void* stream) {
+  return grouped_entry(x, slab_rows, codes, scales, global_scales, offsets, out, ld_out, experts, weight_experts,
+                       n_padded, k, n_out, swiglu, nullptr, nullptr, 1, status, stream);
+}
+
+extern "C" int msl_grouped_gemm_nvfp4_scatter(const void* x, int64_t slab_rows, const void* codes, const void* scales,
+                                              const float* global_scales, const int* offsets, int64_t ld_out,
+                                              int experts, int weight_experts, int n_padded, int k, int n_out,
+                                              void* const* scatter_bases, const int* scatter_index, int scatter_div,
+                                              int* status, void* stream) {
+  if (!scatter_bases) return MSL_ERR_ARG;
+  // `out` is unused when every row is scattered; x stands in so that the common checks pass
+  return grouped_entry(x, slab_rows, codes, scales, global_scales, offsets, const_cast<void*>(x), ld_out, experts,
+                       weight_experts, n_padded, k, n_out, 0, scatter_bases, scatter_index, scatter_div, status, stream);
 }

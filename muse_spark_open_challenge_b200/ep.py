@@ -103,6 +103,7 @@ class ExpertParallel:
         self.cap = 0
         self.recv_x = self.recv_i = None
         self.peer = None                       # set by enable_peer
+        self.push = False
         self.side = torch.cuda.Stream(st["device"]) if torch.device(st["device"]).type == "cuda" else None
 
     def buffers(self, st, rows):
@@ -115,20 +116,24 @@ class ExpertParallel:
 
 
 class PeerSlabs:
-    """Peer-mapped memory of one rank: a bf16 [cap, width] row slab plus the barrier's flag words,
-    allocated as symmetric memory and exchanged once; holds the device arrays of every rank's slab
-    and flag pointers."""
+    """Peer-mapped memory of one rank, allocated as symmetric memory and exchanged once: a bf16
+    [cap, width] row slab (what the other ranks dispatch into), the barrier's flag words, an i32 [cap]
+    return index (for every slab row, where its owner wants the output row back) and a bf16
+    [ret_rows, width] return buffer (where the other ranks' down projections store this rank's output
+    rows); plus the device arrays of every rank's pointers to each of them."""
 
     FLAG_BYTES = 4096
 
-    def __init__(self, ctx: "ExpertParallel", st: dict, cap: int):
+    def __init__(self, ctx: "ExpertParallel", st: dict, cap: int, ret_rows: int = 0):
         import torch.distributed._symmetric_memory as symm
 
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # plain peer loads/stores only
         dev = torch.device(st["device"])
         width = st["moe_width"]
         slab_bytes = cap * width * 2
-        self.raw = symm.empty(slab_bytes + self.FLAG_BYTES, dtype=torch.uint8, device=dev)
+        index_at = slab_bytes + self.FLAG_BYTES
+        ret_at = index_at + (cap * 4 + 255) // 256 * 256
+        self.raw = symm.empty(ret_at + ret_rows * width * 2, dtype=torch.uint8, device=dev)
         self.raw.zero_()
         group = ctx.group if ctx.group is not None else dist.group.WORLD
         self.handle = symm.rendezvous(self.raw, group)
@@ -136,21 +141,35 @@ class PeerSlabs:
         self.slab = self.raw[:slab_bytes].view(torch.bfloat16).view(cap, width)
         self.slab_ptrs = torch.tensor(bases, dtype=torch.int64, device=dev)
         self.flag_ptrs = torch.tensor([b + slab_bytes for b in bases], dtype=torch.int64, device=dev)
+        self.ret_index = self.raw[index_at:index_at + cap * 4].view(torch.int32)
+        self.index_ptrs = torch.tensor([b + index_at for b in bases], dtype=torch.int64, device=dev)
+        self.ret_rows = ret_rows
+        if ret_rows:
+            self.ret = self.raw[ret_at:].view(torch.bfloat16).view(ret_rows, width)
+            self.ret_ptrs = torch.tensor([b + ret_at for b in bases], dtype=torch.int64, device=dev)
         self.cap = cap
         torch.cuda.synchronize(dev)
         dist.barrier(group=ctx.group)          # every rank's flag words are zero before the first barrier
 
 
-def enable_peer(ctx: "ExpertParallel", st: dict, max_tokens: int, top_k: int, capacity_factor: float = 2.0):
+def enable_peer(ctx: "ExpertParallel", st: dict, max_tokens: int, top_k: int, capacity_factor: float = 2.0,
+                push: bool = False):
     """Switch `ctx` to the peer-memory transport.  Every rank's slab holds up to
     capacity_factor * max_tokens * top_k rows (never more than the worst case world * max_tokens *
-    top_k); a layer whose routing needs more sets MSL_ERR_CAPACITY in the status word."""
+    top_k); a layer whose routing needs more sets MSL_ERR_CAPACITY in the status word.  By default the
+    combine kernel loads the expert outputs from the owners' slabs.  With `push` the down projection
+    stores every output row straight into the token owner's return buffer instead (the exchange rides
+    on the GEMM's epilogue): correct, but its 64-byte stores cross NVLink at a fraction of the link rate
+    (down projection 1.9 -> 5.7 ms on two GPUs), so it is opt-in."""
     dev = st["device"]
     most = torch.tensor([max_tokens], dtype=torch.int64, device=dev)
     dist.all_reduce(most, op=dist.ReduceOp.MAX, group=ctx.group)       # slabs have one size on every rank
     cap = int(min(ctx.world, capacity_factor) * int(most.item()) * top_k)
     cap = (cap + 255) // 256 * 256
-    ctx.peer = PeerSlabs(ctx, st, cap)
+    most_tokens = int(most.item())
+    ctx.peer = PeerSlabs(ctx, st, cap, most_tokens * top_k if push else 0)
+    ctx.push = push
+    ctx.ident = torch.arange(most_tokens * top_k, dtype=torch.int32, device=dev).view(most_tokens, top_k)
     ctx.recv_i = torch.empty((cap, st["inter"]), dtype=torch.bfloat16, device=dev)
     ctx.counts_all = torch.zeros((ctx.world, ctx.n_experts), dtype=torch.int32, device=dev)
     ctx.dest_base = torch.zeros(ctx.n_experts, dtype=torch.int32, device=dev)
@@ -182,13 +201,14 @@ def moe_stage_peer(h, data, st, ctx: ExpertParallel):
         # every rank has finished reading this rank's slab (the previous layer's combine) before new rows land
         ops.peer_barrier(peer.flag_ptrs.data_ptr(), ctx.rank, ctx.world, status)
         layer._mark(st, "plan")
+        index_bases = peer.index_ptrs.data_ptr() if ctx.push else 0
         if st["pooled"]:
             p = ops.gemm(h, st["pooler"], status=status)
             rowmap = ops.dispatch_peer(p, st["w_pre_exp"], ids, slots, ctx.dest_base, peer.slab_ptrs.data_ptr(),
-                                       local, peer.cap)
+                                       local, peer.cap, index_bases=index_bases)
         else:
             rowmap = ops.dispatch_peer(h, None, ids, slots, ctx.dest_base, peer.slab_ptrs.data_ptr(), local,
-                                       peer.cap)
+                                       peer.cap, index_bases=index_bases)
         layer._mark(st, "dispatch")
     shared = None
     if st["shared"]:                           # also absorbs the skew between ranks ahead of the barrier
@@ -203,14 +223,24 @@ def moe_stage_peer(h, data, st, ctx: ExpertParallel):
     ops.grouped_gemm_nvfp4(peer.slab, st["w13_q"], st["w13_s"], st["w13_gs"], ctx.group_offsets, ctx.recv_i,
                            st["inter"], True, status)
     layer._mark(st, "experts_gate_up")
-    ops.grouped_gemm_nvfp4(ctx.recv_i, st["w2_q"], st["w2_s"], st["w2_gs"], ctx.group_offsets, peer.slab,
-                           st["moe_width"], False, status)
+    if ctx.push:
+        # every output row goes straight to the return buffer of the rank that owns its token
+        ops.grouped_gemm_nvfp4_scatter(ctx.recv_i, st["w2_q"], st["w2_s"], st["w2_gs"], ctx.group_offsets,
+                                       st["moe_width"], peer.ret_ptrs.data_ptr(), peer.ret_index, local, status)
+    else:
+        ops.grouped_gemm_nvfp4(ctx.recv_i, st["w2_q"], st["w2_s"], st["w2_gs"], ctx.group_offsets, peer.slab,
+                               st["moe_width"], False, status)
     layer._mark(st, "experts_down")
     st["offsets"][-1:] = ctx.group_offsets[-1:]             # rows computed on this rank (for the bench's FLOP count)
     ops.peer_barrier(peer.flag_ptrs.data_ptr(), ctx.rank, ctx.world, status)      # all expert outputs are written
     layer._mark(st, "barrier_outputs")
-    moe = ops.combine_peer(peer.slab_ptrs.data_ptr(), peer.cap, st["moe_width"], rowmap, tw, st["w_post_exp"],
-                           addend=shared)
+    if ctx.push:
+        tokens = h.shape[0]
+        back = torch.where(rowmap >= 0, ctx.ident[:tokens], rowmap)              # a route without a slab row has none
+        moe = ops.combine(peer.ret[:tokens * top_k], back, tw, st["w_post_exp"], addend=shared)
+    else:
+        moe = ops.combine_peer(peer.slab_ptrs.data_ptr(), peer.cap, st["moe_width"], rowmap, tw, st["w_post_exp"],
+                               addend=shared)
     layer._mark(st, "combine")
     if st["pooled"]:
         moe = layer.unpool(moe, st)

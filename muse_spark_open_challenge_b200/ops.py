@@ -174,16 +174,18 @@ def peer_barrier(flag_bases, rank, world, status, timeout_ms=20000):
           "msl_peer_barrier")
 
 
-def dispatch_peer(x, norm_w, ids, slots, dest_base, peer_bases, local_experts, cap, rowmap=None):
+def dispatch_peer(x, norm_w, ids, slots, dest_base, peer_bases, local_experts, cap, rowmap=None, index_bases=0):
     """Token rows written straight into the owning ranks' slabs (peer_bases: device array of slab
-    pointers, one per rank)."""
+    pointers, one per rank); with index_bases (device array of the ranks' i32 [cap] arrays) the owner
+    also learns the return row t * top_k + j of every slab row."""
     _need(x, torch.bfloat16, "x"), _need(ids, torch.int32, "ids"), _need(slots, torch.int32, "slots")
     t, top_k = ids.shape
     if rowmap is None:
         rowmap = torch.empty((t, top_k), dtype=torch.int32, device=x.device)
     check(_lib.lib().msl_dispatch_peer(x.data_ptr(), _rows(x, "x"), _ptr(norm_w), ids.data_ptr(), slots.data_ptr(),
                                        dest_base.data_ptr(), int(peer_bases), local_experts, cap, t, top_k,
-                                       x.shape[1], rowmap.data_ptr(), _stream()), "msl_dispatch_peer")
+                                       x.shape[1], rowmap.data_ptr(), int(index_bases) or None, _stream()),
+          "msl_dispatch_peer")
     return rowmap
 
 
@@ -241,6 +243,21 @@ def grouped_gemm_nvfp4(x, codes_t, scales_t, global_scales, offsets, out, n_out,
                                             n_out, int(swiglu),
                                             _ptr(status), _stream()), "msl_grouped_gemm_nvfp4")
     return out
+
+
+def grouped_gemm_nvfp4_scatter(x, codes_t, scales_t, global_scales, offsets, n_out, scatter_bases, scatter_index,
+                               scatter_div, status=None):
+    """The grouped GEMM with every output row stored to scatter_bases[g // scatter_div] +
+    scatter_index[r] * n_out (device array of row-buffer pointers, possibly other GPUs' memory)."""
+    _need(x, torch.bfloat16, "x"), _need(offsets, torch.int32, "offsets"), _need(scatter_index, torch.int32, "index")
+    e, n_tiles, k_blocks = codes_t.shape[:3]
+    if not x.is_contiguous():
+        raise MslError("x must be contiguous")
+    check(_lib.lib().msl_grouped_gemm_nvfp4_scatter(x.data_ptr(), x.shape[0], codes_t.data_ptr(), scales_t.data_ptr(),
+                                                    global_scales.data_ptr(), offsets.data_ptr(), n_out,
+                                                    offsets.numel() - 1, e, n_tiles * TILE_N, k_blocks * 64, n_out,
+                                                    int(scatter_bases), scatter_index.data_ptr(), scatter_div,
+                                                    _ptr(status), _stream()), "msl_grouped_gemm_nvfp4_scatter")
 
 
 def interleave_gate_up(w13: torch.Tensor) -> torch.Tensor:

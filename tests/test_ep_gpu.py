@@ -54,6 +54,7 @@ def _worker(rank, world, port):
         # kernel differs (it sums the same terms with another association), so ids are equal and the
         # outputs agree to fp32 rounding of a bf16 result
         ep.enable_peer(ctx, st, max_tokens=hidden.shape[0], top_k=shape.top_k)
+        assert not ctx.push
         for _ in range(3):                                               # slab reuse across layers
             hidden3, stream3, ids3 = ep.kernel_fn(dev, st, ctx)
         torch.cuda.synchronize()
@@ -61,6 +62,15 @@ def _worker(rank, world, port):
         assert torch.equal(ids3, ids), f"rank {rank}: peer transport changed the routing"
         assert L.relative_l2(stream3, stream) < 1e-5 and L.relative_l2(hidden3.float(), hidden.float()) < 2e-3, \
             f"rank {rank}: peer transport differs"
+        # the same with the down projection storing every output row into the token owner's return buffer
+        push = ep.ExpertParallel(st, world, rank, shape.n_experts)
+        ep.enable_peer(push, st, max_tokens=hidden.shape[0], top_k=shape.top_k, push=True)
+        for _ in range(2):
+            hidden4, stream4, ids4 = ep.kernel_fn(dev, st, push)
+        torch.cuda.synchronize()
+        layer.check_status(st)
+        assert torch.equal(ids4, ids)
+        assert L.relative_l2(stream4, stream) < 1e-5 and L.relative_l2(hidden4.float(), hidden.float()) < 2e-3
         # a slab too small for the routing is reported, not overrun
         ctx.peer.cap_saved = ctx.peer.cap
         ctx.peer.cap = 256
