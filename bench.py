@@ -481,7 +481,7 @@ def main():
         for name, t in layer.stage_times_ms(st["marks"]):
             per_stage.setdefault(name, []).append(t)
     st["marks"] = None
-    stage_ms = {k: sum(v) / len(v) for k, v in per_stage.items()}
+    stage_ms = {k: sorted(v)[len(v) // 2] for k, v in per_stage.items()}     # median: one slow launch does not count
 
     # ---- end to end through kernel_fn with host buffers: every step copies its inputs from pinned
     # host memory and its three outputs back to pinned host memory inside the timed region.  The
