@@ -221,7 +221,7 @@ def run_moe_op(args):
     layer.moe_stage(h, data, st)
     torch.cuda.synchronize()
     stages = dict(layer.stage_times_ms(st["marks"]))
-    counts = st["counts"].cpu()
+    counts = st["offsets"].cpu().diff()                       # the kernel leaves its counters at zero
     routes = int(counts.sum())
     flops = 2.0 * routes * 3 * shape.moe_width * shape.inter
     pk = peaks()
@@ -237,7 +237,7 @@ def run_moe_op(args):
         "roofline": {"kernel": "grouped_nvfp4_kernel (gate/up + SiLU*up)", "bound": "tensor", "achieved": gu,
                      "peak": pk["tflops"], "unit": "TFLOP/s", "frac": gu / pk["tflops"], "traffic": None,
                      "peak_source": pk["source"]},
-        "gpu_launches": 6 * args.steps}))
+        "gpu_launches": 5 * args.steps}))
 
 
 # The reference's eight scored shapes on its native per-GPU shard (hidden 8192, 16q/2kv x 64, pooler to
@@ -302,22 +302,100 @@ def run_native(args):
                       "launch": "CUDA graph replay, L2 flushed before every replay, median", "shapes": rows}))
 
 
-def enable_peer_or_collective(ep, dist, ctx, st, max_tokens, top_k, push=False):
+def enable_peer_or_collective(ep, dist, ctx, st, max_tokens, top_k):
     """Map the ranks' row slabs into one another; when the platform cannot (no peer access between the
     GPUs, symmetric memory unavailable) every rank keeps the NCCL all-to-all transport and the line says so."""
     ok = torch.ones(1, device=st["device"])
     why = ""
     try:
-        ep.enable_peer(ctx, st, max_tokens=max_tokens, top_k=top_k, push=push)
+        ep.enable_peer(ctx, st, max_tokens=max_tokens, top_k=top_k)
     except Exception as exc:  # noqa: BLE001 - any failure of the mapping selects the other transport
         ok.zero_()
         why = f"{type(exc).__name__}: {exc}"[:200]
         ctx.peer = None
     dist.all_reduce(ok, op=dist.ReduceOp.MIN)
     if ok.item() > 0:
-        return "peer-push" if push else "peer"
+        return "peer"
     ctx.peer = None
     return "collective (peer memory unavailable" + (": " + why if why else " on another rank") + ")"
+
+
+def ep_parity(dist, rank, world, dev, peer, handoff):
+    """Before anything is timed at N > 1: one small expert-parallel layer (hidden 1024, 16 experts sharded
+    over the ranks, two ragged requests per rank with a cached context) through the transport about to be
+    timed, judged on every rank by the CPU oracle evaluated with ALL experts local (the reference's
+    acceptance check, reference.py:640-672); with `handoff` also one sequence prefilled as one piece per
+    rank, whose handed-over K/V rows must be byte-identical to the rows their owners wrote.  Returns the
+    verdict reduced over the ranks (worst figures)."""
+    import dataclasses
+    from muse_spark_open_challenge_b200 import ep, layer, synth
+    from oracle import layer_ref as L
+    shape = dataclasses.replace(synth.MID, hidden=1024, hq=8, hkv=2, n_experts=16, local_experts=16, moe_width=1024,
+                                inter=256, shared_inter=512)
+    weights = synth.make_weights(shape, seed=5)                       # identical on every rank
+    local = shape.n_experts // world
+    mine = dict(weights)
+    for k in ("w13", "w13_sf", "w13_gs", "w2", "w2_sf", "w2_gs"):
+        mine[k] = weights[k][rank * local:(rank + 1) * local]
+    st = layer.prepare({k: v.to(dev) for k, v in mine.items()})
+    ctx = ep.ExpertParallel(st, world, rank, shape.n_experts)
+
+    def judge(data, seq=None):
+        on_dev = {k: (v.to(dev) if isinstance(v, torch.Tensor) else v) for k, v in data.items()}
+        hidden, stream, ids = ep.kernel_fn(on_dev, st, ctx, seq)
+        torch.cuda.synchronize()
+        layer.check_status(st)
+        d = L.dims_of(weights, data["config"])
+        slots = L.new_slots(data).to(dev)
+        after = dict(data)
+        after["k_cache"], after["v_cache"] = on_dev["k_cache"].cpu(), on_dev["v_cache"].cpu()
+        k_rows = on_dev["k_cache"].view(-1, d.hkv, d.head_dim)[slots].cpu()
+        v_rows = on_dev["v_cache"].view(-1, d.hkv, d.head_dim)[slots].cpu()
+        ok, msg, rep = L.check_layer(after, weights, hidden.cpu(), stream.cpu(), ids.cpu(), k_rows, v_rows)
+        ref_ids = L.topk_ids(L.ref_front(data, weights)["biased"], d.top_k)
+        same = float((ids.cpu().long().sort(-1).values == ref_ids.long().sort(-1).values).all(-1).float().mean())
+        return ok, msg, rep, same, on_dev
+
+    if peer:
+        ep.enable_peer(ctx, st, max_tokens=150 + 40 * world + 77 + 17 * world, top_k=shape.top_k)
+    data = synth.make_input(shape, [150 + 40 * rank, 77], [30, 0], seed=20 + rank, page=64, kv_scale=0.5)
+    ok, msg, rep, same, _ = judge(data)
+    figures = [0.0 if ok else 1.0, rep.get("update_vs_fp32", {}).get("rel_l2", 9.0),
+               rep.get("hidden_vs_fp8q", {}).get("rel_l2", 9.0), 1.0 - same, 0.0]
+    if handoff:
+        lens = [190 + 17 * r for r in range(world)]
+        cdata = synth.make_input(shape, [lens[rank]], [sum(lens[:rank])], seed=50 + rank, page=64, kv_scale=0.5,
+                                 fill_cache=False)
+        seq = ep.ChunkedSequence(None, rank, lens, shape.hkv, shape.head_dim, dev)
+        c_ok, c_msg, _, _, c_dev = judge(cdata, seq)
+        row_bytes = shape.hkv * shape.head_dim
+        c_slots = L.new_slots(cdata).to(dev)
+        mine_rows = torch.zeros((2, max(lens), row_bytes), dtype=torch.uint8, device=dev)
+        for which, name in enumerate(("k_cache", "v_cache")):
+            mine_rows[which, :lens[rank]] = c_dev[name].view(torch.uint8).view(-1, row_bytes)[c_slots]
+        everyone = [torch.empty_like(mine_rows) for _ in range(world)]
+        dist.all_gather(everyone, mine_rows)
+        identical = True
+        for q in range(rank):                                         # every earlier piece, row for row
+            pos = torch.arange(sum(lens[:q]), sum(lens[:q + 1]), device=dev)
+            loc = c_dev["page_table"][0].long()[pos // 64] * 64 + pos % 64
+            for which, name in enumerate(("k_cache", "v_cache")):
+                got = c_dev[name].view(torch.uint8).view(-1, row_bytes)[loc]
+                identical = identical and bool(torch.equal(got, everyone[q][which, :lens[q]]))
+        figures[0] = max(figures[0], 0.0 if c_ok else 1.0)
+        figures[4] = 0.0 if identical else 1.0
+        if not c_ok:
+            msg = "chunked sequence: " + c_msg
+    worst = torch.tensor(figures, dtype=torch.float64, device=dev)
+    dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+    w = worst.tolist()
+    out = {"ok": w[0] == 0.0 and w[4] == 0.0, "update_rel_l2": w[1], "hidden_rel_l2": w[2], "ids_equal": w[3] == 0.0,
+           "ids_mismatch_fraction": w[3], "case": "hidden 1024, 16 experts sharded, 2 ragged requests per rank, judged "
+           "by the CPU oracle with all experts local", "transport": "peer" if peer else "collective",
+           "rank0_message": msg}
+    if handoff:
+        out["handoff_rows_identical"] = w[4] == 0.0
+    return out
 
 
 def main():
@@ -330,10 +408,9 @@ def main():
     ap.add_argument("--workload", default="layer", choices=["layer", "attn", "moe", "native", "long"],
                     help="layer = the headline full-layer step; attn / moe = the op-only configurations")
     ap.add_argument("--small", action="store_true", help="reduced op workload, sized for an ncu capture")
-    ap.add_argument("--transport", default="peer", choices=["peer", "peer-push", "collective"],
+    ap.add_argument("--transport", default="peer", choices=["peer", "collective"],
                     help="expert-parallel row exchange (N > 1): peer-memory stores/loads fused into the dispatch and "
-                         "combine kernels (peer-push: outputs returned by the down GEMM's epilogue instead), or NCCL "
-                         "all-to-alls")
+                         "combine kernels, or NCCL all-to-alls")
     ap.add_argument("--eager", action="store_true", help="time eager launches instead of a CUDA-graph replay")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -396,8 +473,7 @@ def main():
             ctx = ep.ExpertParallel(st, world, rank, n_exp)
             if args.transport.startswith("peer"):
                 most = max(l[c] + l[2 * per_seq - 1 - c] for l in long_lens for c in range(per_seq))
-                args.transport = enable_peer_or_collective(ep, dist, ctx, st, most, shape.top_k,
-                                                           push=args.transport == "peer-push")
+                args.transport = enable_peer_or_collective(ep, dist, ctx, st, most, shape.top_k)
             seq_ctx = ep.ChunkedSequence(groups[my_seq], my_chunk, lens, shape.hkv, shape.head_dim, dev, owners=owners)
             step = lambda d: ep.kernel_fn(d, st, ctx, seq_ctx)  # noqa: E731
         else:
@@ -413,8 +489,7 @@ def main():
         st = layer.prepare(weights)
         ctx = ep.ExpertParallel(st, world, rank, shape.n_experts)
         if args.transport.startswith("peer"):
-            args.transport = enable_peer_or_collective(ep, dist, ctx, st, data["config"]["tokens"], shape.top_k,
-                                                       push=args.transport == "peer-push")
+            args.transport = enable_peer_or_collective(ep, dist, ctx, st, data["config"]["tokens"], shape.top_k)
         step = lambda d: ep.kernel_fn(d, st, ctx)  # noqa: E731
     else:
         seqs = 1 if args.small else SEQS                     # --small: one request, sized for an ncu capture
@@ -423,6 +498,15 @@ def main():
         step = lambda d: layer.kernel_fn(d, st)  # noqa: E731
     del weights
     tokens = data["config"]["tokens"]
+    parity = None
+    if world > 1:
+        parity = ep_parity(dist, rank, world, dev, peer=ctx.peer is not None, handoff=args.workload == "long")
+        if not parity["ok"]:
+            if rank == 0:
+                print(json.dumps({"metric": METRIC, "parity": parity, "error": "expert-parallel parity check failed; "
+                                  "nothing was timed"}))
+            dist.destroy_process_group()
+            raise SystemExit(1)
 
     def barrier():
         if dist is not None:
@@ -600,6 +684,8 @@ def main():
         "gpu_launches": launches,
         "clocks": clocks,
     }
+    if parity is not None:
+        line["parity"] = parity
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline_leg()
     print(json.dumps(line))

@@ -20,7 +20,7 @@
 extern "C" {
 #endif
 
-#define MSL_ABI_VERSION 1
+#define MSL_ABI_VERSION 2
 
 enum {
   MSL_OK = 0,
@@ -44,6 +44,21 @@ enum {
 int msl_abi_version(void);
 const char* msl_status_string(int code);
 
+/* Run-time options (process-wide, 0 or 1).  Their defaults are read from the environment once, at the
+ * first use of any option (variable of the same name as the comment gives, "0" switches off), so a
+ * later change of the environment never changes what a launch does; msl_set_option is the way to change
+ * one afterwards.  A CUDA graph keeps the choice that was in force when it was captured.  The reference
+ * has no such switches (its tile choices are compile-time constants of its Triton kernels). */
+enum {
+  MSL_OPT_GEMM_SPLITK = 0,  /* MSL_GEMM_SPLITK: msl_gemm_splitk_plan may recommend slicing K (default 1).  Off:
+                               every product runs in one pass and its low bits do not depend on its row count */
+  MSL_OPT_GEMM_WIDE = 1,    /* MSL_GEMM_WIDE: 256 x 256 tiles in the dense GEMM when the problem fills them (1) */
+  MSL_OPT_GROUPED_WIDE = 2, /* MSL_GROUPED_WIDE: 256-row tiles in the grouped GEMM when groups average >= 256 rows (1) */
+  MSL_OPT_COUNT = 3
+};
+int msl_set_option(int option, int value);
+int msl_get_option(int option);
+
 /* Dense BF16 GEMM, fp32 accumulate: c[m, n] = alpha * sum_{s < segs} A_s * B_s^T with
  * A_s = a[:, s*a_seg_stride : s*a_seg_stride + k] and B_s = b[:, s*b_seg_stride : ... + k];
  * a is bf16 [m, lda] row-major, b is bf16 [n, ldb] row-major (a weight matrix as stored).
@@ -60,8 +75,9 @@ int msl_gemm_bf16(const void* a, int64_t lda, const void* b, int64_t ldb, void* 
  * (splits * m * n * 4 bytes of caller-owned device memory, 16-byte aligned); a second kernel sums the
  * planes in a fixed order, applies alpha and writes c (MSL_OUT_BF16 or MSL_OUT_F32; n and ldc multiples
  * of 4).  msl_gemm_splitk_plan recommends the slice count from the sizes alone (1 = call
- * msl_gemm_bf16; always 1 when the environment has MSL_GEMM_SPLITK=0: slicing K changes the order of the
- * fp32 sums, so a product's low bits then depend on its number of rows).  The reference leaves these products to cuBLAS (submission.py:1082,1096,1113). */
+ * msl_gemm_bf16; always 1 while MSL_OPT_GEMM_SPLITK is off: slicing K changes the order of the fp32 sums,
+ * so a product's low bits then depend on its number of rows).  The reference leaves these products to
+ * cuBLAS (submission.py:1082,1096,1113). */
 int msl_gemm_splitk_plan(int m, int n, int k, int segs, int out_mode);
 int msl_gemm_bf16_splitk(const void* a, int64_t lda, const void* b, int64_t ldb, void* c, int64_t ldc, int m, int n,
                          int k, int segs, int a_seg_stride, int b_seg_stride, int out_mode, float alpha, int splits,
@@ -109,27 +125,59 @@ int msl_dispatch(const void* x, int64_t ldx, const float* norm_w, const int* loc
                  const int* counts, int tokens, int n_local, int top_k, int width, void* slab, int64_t slab_rows,
                  int* rowmap, int* offsets_out, int* status, void* stream);
 
+/* msl_route_topk and msl_dispatch as ONE kernel launch (the reference launches _routing_kernel and
+ * _dispatch_kernel separately after zeroing its counters, submission.py:859-899,1114-1123): persistent
+ * blocks route all tokens, meet at a grid-wide barrier, form the offsets from the final counts and copy
+ * the rows.  Same outputs as the two calls.  `counts` i32 [n_local] and `sync` i32 [2] are zeroed ONCE by
+ * their owner; the kernel returns both to zero before it ends (the per-expert counts of a call are
+ * offsets_out[e + 1] - offsets_out[e]), so calls on one stream need no memset between them.  offsets_out
+ * is required.  The launch is cooperative (all blocks resident); its barrier wait is bounded and reports
+ * MSL_ERR_DEVICE_TIMEOUT in *status.  Calls that share `counts` / `sync` must not overlap on the GPU. */
+int msl_route_dispatch(const float* logits, int64_t ld, int hilo, const float* bias, float multiplier,
+                       const int* local_start, const void* x, int64_t ldx, const float* norm_w, int tokens,
+                       int n_experts, int top_k, int n_local, int width, int* ids, float* weights, int* local_ids,
+                       int* slots, int* counts, int* sync, void* slab, int64_t slab_rows, int* rowmap,
+                       int* offsets_out, int* status, void* stream);
+
 /* Routing and dispatch in one call that needs no scratch memory from the caller: the same
  * results as msl_route_topk followed by msl_dispatch (ids, weights, rowmap, offsets_out, slab),
  * with the per-expert counters and per-route expert/slot arrays kept in a fixed array inside the
  * library.  No counterpart in the reference.  It exists for hosts that cannot allocate when they
  * call in: a server whose memory pool already owns all of HBM, or a request path that cannot take
  * the device-wide synchronisation cudaMalloc implies.  It calls no allocator of any kind.
- * Limits: n_local <= 1024 and tokens * top_k <= 262144, otherwise MSL_ERR_CAPACITY; the array
- * (about 2 MiB) stays resident on every GPU that loads the library.  The first call on a device
+ * Limits: tokens * top_k <= 262144, otherwise MSL_ERR_CAPACITY (the array also has room for 1024
+ * local experts, more than msl_route_topk's own limit of 512 experts allows); the array (about
+ * 2 MiB) stays resident on every GPU that loads the library.  The first call on a device
  * looks up the array's device address (cudaGetSymbolAddress); make that first call outside any
  * stream capture.  All calls share the one array, so two calls whose kernels overlap on the GPU
- * (different streams, or different host threads on one device) race: serialise them. */
+ * (different streams, or different host threads on one device) race: serialise them.  All arguments
+ * are checked before anything is enqueued or the array is touched (same rules as msl_route_topk and
+ * msl_dispatch: top_k <= 16, n_experts <= 512, 1 <= n_local <= n_experts, width and ldx multiples of 8,
+ * x and slab 16-byte aligned); a rejected call changes nothing. */
 int msl_route_dispatch_static(const float* logits, int64_t ld, int hilo, const float* bias, float multiplier,
                               const int* local_start, const void* x, int64_t ldx, const float* norm_w, int tokens,
                               int n_experts, int top_k, int n_local, int width, int* ids, float* weights, void* slab,
                               int64_t slab_rows, int* rowmap, int* offsets_out, int* status, void* stream);
 
 /* Weighted combine: out[t] = sum_j weights[t, j] * rms(y[rowmap[t, j]] * post_w, eps 1e-8)
- * (+ addend[t] when not NULL); rowmap < 0 contributes nothing.  y: bf16 [slab rows, width].
- * Replaces _combine_kernel (submission.py:917-928, launch :1132). */
+ * (+ addend[t] when not NULL); rowmap < 0 contributes nothing.  y: bf16 [slab rows, width].  The rows are
+ * staged by bulk copies whose bounded wait reports MSL_ERR_DEVICE_TIMEOUT in *status (may be NULL); a
+ * block whose wait ran out writes nothing.  Replaces _combine_kernel (submission.py:917-928, launch :1132). */
 int msl_combine(const void* y, const int* rowmap, const float* weights, const float* post_w, const void* addend,
-                int64_t ld_addend, void* out, int64_t ld_out, int tokens, int top_k, int width, void* stream);
+                int64_t ld_addend, void* out, int64_t ld_out, int tokens, int top_k, int width, int* status,
+                void* stream);
+
+/* msl_combine fused with the residual boundary that follows it in a layer without an unpooler (width =
+ * hidden size): the combined row f, rounded to bf16 exactly as msl_combine would store it, goes straight
+ * into msl_boundary's arithmetic (b = f * branch_scale; stream_out = alpha * stream_in + beta * rms(b,
+ * eps_branch); hidden_out = bf16(rms(stream_out, eps_out) * norm_w)) without being written to memory.
+ * Same bits as msl_combine followed by msl_boundary for width <= 4096.  Replaces _combine_kernel +
+ * _ffn_boundary_kernel (submission.py:917-928, 832-855; launches :1132, :1138). */
+int msl_combine_boundary(const void* y, const int* rowmap, const float* weights, const float* post_w,
+                         const void* addend, int64_t ld_addend, int tokens, int top_k, int width,
+                         const float* branch_scale, const float* stream_in, const float* alpha, const float* beta,
+                         const float* norm_w, float* stream_out, void* hidden_out, int64_t ld_hidden,
+                         float eps_branch, float eps_out, int* status, void* stream);
 
 /* Expert parallelism over peer memory (one process per GPU, every rank's row slab mapped into every
  * other rank's address space).  These three calls stand where the reference leaves identities for
@@ -139,8 +187,10 @@ int msl_combine(const void* y, const int* rowmap, const float* weights, const fl
  * msl_ep_plan: counts_all i32 [world, world * local_experts] (row s = routes of rank s per global
  * expert, all-gathered).  Writes dest_base i32 [world * local_experts] (first row, in the owning
  * rank's slab, of this rank's rows for each expert) and group_offsets i32 [world * local_experts + 1]
- * (row ranges of this rank's own slab, groups ordered (source rank, local expert)).  Sets *status to
- * MSL_ERR_CAPACITY when this rank's slab would need more than `cap` rows. */
+ * (row ranges of this rank's own slab, groups ordered (source rank, local expert)), clamped to `cap`.
+ * Sets *status to MSL_ERR_CAPACITY when this rank's slab would need more than `cap` rows: the groups
+ * beyond the end then come out empty and msl_dispatch_peer skips the same rows, so no kernel that
+ * consumes the plan addresses a row at or beyond `cap`. */
 int msl_ep_plan(const int* counts_all, int world, int local_experts, int rank, int cap, int* dest_base,
                 int* group_offsets, int* status, void* stream);
 
@@ -155,12 +205,10 @@ int msl_peer_barrier(int* const* flag_bases, int rank, int world, int timeout_ms
  * ranks' bf16 [cap, width] slabs; ids i32 [tokens, top_k] are global expert ids, slots the ranks
  * within (this rank, expert) from msl_route_topk.  The row of route (t, j) lands at
  * peer_bases[e / local_experts] + (dest_base[e] + slot) * width; rowmap receives
- * rank * cap + row (or -1 for a row beyond cap).  Optional RMS norm as in msl_dispatch.  With
- * index_bases != NULL (a DEVICE array of `world` pointers to the ranks' i32 [cap] arrays) the owner also
- * learns where to return the route's output: index_bases[owner][row] = t * top_k + j. */
+ * rank * cap + row (or -1 for a row beyond cap).  Optional RMS norm as in msl_dispatch. */
 int msl_dispatch_peer(const void* x, int64_t ldx, const float* norm_w, const int* ids, const int* slots,
                       const int* dest_base, void* const* peer_bases, int local_experts, int cap, int tokens,
-                      int top_k, int width, int* rowmap, int* const* index_bases, void* stream);
+                      int top_k, int width, int* rowmap, void* stream);
 
 /* msl_combine with the rows read from the owning ranks' slabs (rowmap from msl_dispatch_peer). */
 int msl_combine_peer(const void* const* peer_bases, int peer_cap, const int* rowmap, const float* weights,
@@ -195,23 +243,12 @@ int msl_nvfp4_repack(const void* src_codes, const void* src_scales, void* dst_co
  * group is (source rank, expert), source-major); x bf16 [slab_rows, k]; out bf16 [slab_rows,
  * ld_out] with n_out valid columns; experts = number of row groups (<= 256); with swiglu != 0
  * the bank is an interleaved gate/up bank and out = silu(gate) * up (n_out = intermediate size).
- * offsets is device memory [experts + 1]; no host synchronisation.  Replaces the two grouped GEMM
+ * offsets is device memory [experts + 1]; no host synchronisation; rows at or beyond slab_rows (offsets
+ * that overrun the buffers) are neither read nor written.  Replaces the two grouped GEMM
  * launches and _silu_mul_kernel (submission.py:956-1002, 903-913; launches :1128-1130). */
 int msl_grouped_gemm_nvfp4(const void* x, int64_t slab_rows, const void* codes, const void* scales,
                            const float* global_scales, const int* offsets, void* out, int64_t ld_out, int experts,
                            int weight_experts, int n_padded, int k, int n_out, int swiglu, int* status, void* stream);
-
-/* msl_grouped_gemm_nvfp4 (no SwiGLU) whose output rows are scattered, possibly into other GPUs: row r
- * of group g is stored to scatter_bases[g / scatter_div] + scatter_index[r] * ld_out.  scatter_bases is
- * a DEVICE array of bf16 row-buffer pointers (peer-mapped for the other ranks), scatter_index i32 [slab
- * rows] as filled by msl_dispatch_peer.  Under expert parallelism (groups = (source rank, expert),
- * scatter_div = local experts) the down projection thus returns every output row to the rank that owns
- * its token while the GEMM runs: the combine exchange rides on the epilogue.  No counterpart in the
- * reference (its cross-GPU steps are identities, reference.py:438,451,467). */
-int msl_grouped_gemm_nvfp4_scatter(const void* x, int64_t slab_rows, const void* codes, const void* scales,
-                                   const float* global_scales, const int* offsets, int64_t ld_out, int experts,
-                                   int weight_experts, int n_padded, int k, int n_out, void* const* scatter_bases,
-                                   const int* scatter_index, int scatter_div, int* status, void* stream);
 
 /* Causal attention of the new tokens over the paged FP8 cache (which already holds the new
  * tokens' K/V rows): q8 e4m3 [tokens, hq, head_dim]; caches e4m3 [cache_rows, hkv, head_dim];

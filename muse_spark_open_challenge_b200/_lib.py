@@ -13,6 +13,8 @@ LIB_PATH = os.path.join(HERE, "libmsl.so")
 
 OUT_BF16, OUT_F32, OUT_SWIGLU_BF16 = 0, 1, 2
 ERR_DEVICE_TIMEOUT, ERR_CAPACITY = -5, -6
+OPTIONS = {"gemm_splitk": 0, "gemm_wide": 1, "grouped_wide": 2}     # MSL_OPT_* of include/msl.h
+ABI_VERSION = 2
 
 _p, _i, _i64, _f = C.c_void_p, C.c_int, C.c_int64, C.c_float
 
@@ -20,6 +22,8 @@ _p, _i, _i64, _f = C.c_void_p, C.c_int, C.c_int64, C.c_float
 SIGNATURES = {
     "msl_abi_version": (_i, []),
     "msl_status_string": (C.c_char_p, [_i]),
+    "msl_set_option": (_i, [_i, _i]),
+    "msl_get_option": (_i, [_i]),
     "msl_gemm_bf16": (_i, [_p, _i64, _p, _i64, _p, _i64, _i, _i, _i, _i, _i, _i, _i, _f, _p, _p]),
     "msl_gemm_splitk_plan": (_i, [_i, _i, _i, _i, _i]),
     "msl_gemm_bf16_splitk": (_i, [_p, _i64, _p, _i64, _p, _i64, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p, _p, _p]),
@@ -27,18 +31,21 @@ SIGNATURES = {
     "msl_boundary": (_i, [_p, _i64, _p, _p, _p, _p, _p, _p, _p, _i64, _i, _i, _f, _f, _p]),
     "msl_route_topk": (_i, [_p, _i64, _i, _p, _f, _p, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p]),
     "msl_dispatch": (_i, [_p, _i64, _p, _p, _p, _p, _i, _i, _i, _i, _p, _i64, _p, _p, _p, _p]),
+    "msl_route_dispatch": (_i, [_p, _i64, _i, _p, _f, _p, _p, _i64, _p, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _p,
+                                _i64, _p, _p, _p, _p]),
     "msl_route_dispatch_static": (_i, [_p, _i64, _i, _p, _f, _p, _p, _i64, _p, _i, _i, _i, _i, _i, _p, _p, _p, _i64,
                                        _p, _p, _p, _p]),
-    "msl_combine": (_i, [_p, _p, _p, _p, _p, _i64, _p, _i64, _i, _i, _i, _p]),
+    "msl_combine": (_i, [_p, _p, _p, _p, _p, _i64, _p, _i64, _i, _i, _i, _p, _p]),
+    "msl_combine_boundary": (_i, [_p, _p, _p, _p, _p, _i64, _i, _i, _i, _p, _p, _p, _p, _p, _p, _p, _i64, _f, _f, _p,
+                                  _p]),
     "msl_ep_plan": (_i, [_p, _i, _i, _i, _i, _p, _p, _p, _p]),
     "msl_peer_barrier": (_i, [_p, _i, _i, _i, _p, _p]),
-    "msl_dispatch_peer": (_i, [_p, _i64, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p, _p, _p]),
+    "msl_dispatch_peer": (_i, [_p, _i64, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p, _p]),
     "msl_combine_peer": (_i, [_p, _i, _p, _p, _p, _p, _i64, _p, _i64, _i, _i, _i, _p]),
     "msl_kv_rows_copy": (_i, [_p, _p, _i64, _p, _p, _i64, _i64, _i, _p, _p]),
     "msl_nvfp4_padded_rows": (_i64, [_i, _i]),
     "msl_nvfp4_repack": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _p]),
     "msl_grouped_gemm_nvfp4": (_i, [_p, _i64, _p, _p, _p, _p, _p, _i64, _i, _i, _i, _i, _i, _i, _p, _p]),
-    "msl_grouped_gemm_nvfp4_scatter": (_i, [_p, _i64, _p, _p, _p, _p, _i64, _i, _i, _i, _i, _i, _p, _p, _i, _p, _p]),
     "msl_attention_fp8": (_i, [_p, _p, _p, _p, _i, _p, _p, _p, _p, _f, _i, _i, _i, _i, _i, _i, _i, _i, _i64, _p,
                                _i64, _p, _i64, _p, _p]),
     "msl_attention_split_plan": (_i, [_i, _i, _i, _i, _i, _i, _i]),
@@ -71,6 +78,14 @@ def lib() -> C.CDLL:
     if _LIB is None:
         _LIB = load()
     return _LIB
+
+
+def set_option(name: str, value: bool) -> bool:
+    """Set a run-time option of the library (see MSL_OPT_* in include/msl.h); returns the old value."""
+    old = bool(lib().msl_get_option(OPTIONS[name]))
+    if lib().msl_set_option(OPTIONS[name], int(bool(value))) != 0:
+        raise MslError(f"msl_set_option({name}) was rejected")
+    return old
 
 
 LAUNCHES = 0     # kernels of this library launched by this process (each successful entry point = one launch)

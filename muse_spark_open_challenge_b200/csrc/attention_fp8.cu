@@ -619,13 +619,8 @@ static int launch_attention(const CUtensorMap& tq, const CUtensorMap& tk, const 
                             int batch, int max_q_len, cudaStream_t st) {
   using S = AttnSmem<D>;
   const int smem = S::kTotal + 1024;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(attention_fp8_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
-        cudaSuccess)
-      return MSL_ERR_CUDA;
-    configured = true;
-  }
+  static SmemConfig config;
+  if (int rc = config.ensure(attention_fp8_kernel<D>, smem)) return rc;
   const int G = a.hq / a.hkv, TQ2 = 2 * (kAM / G);
   dim3 grid(((max_q_len + TQ2 - 1) / TQ2) * a.kv_splits, a.hkv, batch);
   attention_fp8_kernel<D><<<grid, 384, smem, st>>>(tq, tk, tv, a);

@@ -2,7 +2,7 @@
 // the two residual boundaries, the router's top-k with slot assignment, token dispatch and the
 // weighted combine.  All use 128-bit global accesses and keep a row in registers so each tensor
 // crosses HBM once.
-#include <cstdlib>
+#include <atomic>
 #include <mutex>
 
 #include "msl_common.cuh"
@@ -224,16 +224,40 @@ boundary_kernel(const __nv_bfloat16* __restrict__ branch, int64_t ld_branch, con
 // lowest index winning exact ties; weights = score / (sum of picked + 1e-15).  Routes to experts
 // [local_start, local_start + n_local) (modulo n_experts) get a slot from a per-expert counter:
 // a shared-memory histogram per block, then one global atomic per (block, expert).
+struct RouteArgs {
+  const float* logits;
+  int64_t ld;
+  int hilo;
+  const float* bias;
+  float multiplier;
+  const int* local_start;
+  int tokens, n_experts, top_k, n_local;
+  int* ids;
+  float* weights;
+  int* local_ids;
+  int* slots;
+  int* counts;
+};
+
+// Routes the tokens [group * warps, (group + 1) * warps) of one block (one warp per token).  hist:
+// shared memory, [n_local] counts then [n_local] global bases.  Called by every thread of the block.
 template <int MAXPL>   // experts per lane, n_experts <= 32 * MAXPL
-__global__ void __launch_bounds__(256)
-route_topk_kernel(const float* __restrict__ logits, int64_t ld, int hilo, const float* __restrict__ bias,
-                  float multiplier, const int* __restrict__ local_start_p, int tokens, int n_experts, int top_k,
-                  int n_local, int* __restrict__ ids, float* __restrict__ weights, int* __restrict__ local_ids,
-                  int* __restrict__ slots, int* __restrict__ counts) {
-  extern __shared__ int hist[];          // [n_local] counts, then [n_local] global bases
+__device__ __forceinline__ void route_group(const RouteArgs& a, int group, int* hist) {
+  const float* __restrict__ logits = a.logits;
+  const float* __restrict__ bias = a.bias;
+  const int64_t ld = a.ld;
+  const int hilo = a.hilo, tokens = a.tokens, n_experts = a.n_experts, top_k = a.top_k, n_local = a.n_local;
+  const float multiplier = a.multiplier;
+  const int* local_start_p = a.local_start;
+  int* __restrict__ ids = a.ids;
+  float* __restrict__ weights = a.weights;
+  int* __restrict__ local_ids = a.local_ids;
+  int* __restrict__ slots = a.slots;
+  int* __restrict__ counts = a.counts;
   int* base = hist + n_local;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+  const int t = group * (blockDim.x >> 5) + warp;
+  __syncthreads();                       // the previous group's bases have been read
   for (int i = threadIdx.x; i < n_local; i += blockDim.x) hist[i] = 0;
   __syncthreads();
 
@@ -302,25 +326,42 @@ route_topk_kernel(const float* __restrict__ logits, int64_t ld, int hilo, const 
   }
 }
 
+template <int MAXPL>
+__global__ void __launch_bounds__(256) route_topk_kernel(RouteArgs a) {
+  extern __shared__ int hist[];
+  route_group<MAXPL>(a, blockIdx.x, hist);
+}
+
 // ============================================================================ dispatch
 // Copies each token's row to one slab row per local route: row = offset[expert] + slot, offsets
 // being the exclusive prefix sum of the per-expert counts (recomputed per block; block 0 also
 // publishes it for the grouped GEMM).  With norm_w the row is RMS-normalised (eps 1e-5) and
 // scaled first (the pooled layer's pre-expert norm, submission.py:890-899).
-__global__ void __launch_bounds__(256)
-dispatch_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, const float* __restrict__ norm_w,
-                const int* __restrict__ local_ids, const int* __restrict__ slots, const int* __restrict__ counts,
-                int n_local, int top_k, int width, __nv_bfloat16* __restrict__ slab, int64_t slab_rows,
-                int* __restrict__ rowmap, int* __restrict__ offsets_out, int* status) {
-  extern __shared__ int offs[];          // [n_local + 1]
-  __shared__ float scratch[32];
-  const int t = blockIdx.x;
+struct DispatchArgs {
+  const __nv_bfloat16* x;
+  int64_t ldx;
+  const float* norm_w;
+  const int* local_ids;
+  const int* slots;
+  const int* counts;
+  int n_local, top_k, width;
+  __nv_bfloat16* slab;
+  int64_t slab_rows;
+  int* rowmap;
+  int* offsets_out;
+  int* status;
+};
+
+// Exclusive prefix sum of counts[n_local] into offs[n_local + 1] (shared memory) by the block's first warp.
+// The counters (and, in dispatch_token, the per-route expert/slot arrays) may have been written earlier in
+// the same launch by other blocks: they are read with L2-only loads.
+__device__ __forceinline__ void scan_counts(const int* counts, int n_local, int* offs) {
   if (threadIdx.x < 32) {
     // exclusive scan by one warp, n_local <= 1024
     int carry = 0;
     for (int b0 = 0; b0 < n_local; b0 += 32) {
       const int i = b0 + threadIdx.x;
-      const int c = i < n_local ? counts[i] : 0;
+      const int c = i < n_local ? __ldcg(counts + i) : 0;
       int inc = c;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
@@ -333,9 +374,19 @@ dispatch_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, const float* _
     if (threadIdx.x == 0) offs[n_local] = carry;
   }
   __syncthreads();
-  if (t == 0 && offsets_out != nullptr)
-    for (int i = threadIdx.x; i <= n_local; i += blockDim.x) offsets_out[i] = offs[i];
+}
 
+// Copies token t's row to the slab rows of its local routes.  Called by every thread of the block.
+__device__ __forceinline__ void dispatch_token(const DispatchArgs& a, int t, const int* offs, float* scratch) {
+  const __nv_bfloat16* __restrict__ x = a.x;
+  const float* __restrict__ norm_w = a.norm_w;
+  const int* local_ids = a.local_ids;
+  const int* slots = a.slots;
+  __nv_bfloat16* __restrict__ slab = a.slab;
+  int* __restrict__ rowmap = a.rowmap;
+  const int64_t ldx = a.ldx, slab_rows = a.slab_rows;
+  const int top_k = a.top_k, width = a.width;
+  int* status = a.status;
   const int chunks = width / 8;
   float ss[1] = {0.f};
   if (norm_w != nullptr) {
@@ -351,10 +402,10 @@ dispatch_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, const float* _
   int rows[16];
   int nr = 0;
   for (int j = 0; j < top_k && j < 16; ++j) {
-    const int le = local_ids[t * top_k + j];
+    const int le = __ldcg(local_ids + t * top_k + j);
     int row = -1;
     if (le >= 0) {
-      row = offs[le] + slots[t * top_k + j];
+      row = offs[le] + __ldcg(slots + t * top_k + j);
       if (row >= slab_rows) {
         if (threadIdx.x == 0) report_error(status, MSL_ERR_CAPACITY);
         row = -1;
@@ -377,6 +428,73 @@ dispatch_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, const float* _
     }
     for (int j = 0; j < nr; ++j)
       *reinterpret_cast<uint4*>(slab + static_cast<int64_t>(rows[j]) * width + ch * 8) = raw;
+  }
+}
+
+__global__ void __launch_bounds__(256) dispatch_kernel(DispatchArgs a) {
+  extern __shared__ int offs[];          // [n_local + 1]
+  __shared__ float scratch[32];
+  scan_counts(a.counts, a.n_local, offs);
+  if (blockIdx.x == 0 && a.offsets_out != nullptr)
+    for (int i = threadIdx.x; i <= a.n_local; i += blockDim.x) a.offsets_out[i] = offs[i];
+  dispatch_token(a, blockIdx.x, offs, scratch);
+}
+
+// Routing, slot assignment and dispatch as ONE launch (the reference runs two kernels,
+// submission.py:859-886 and :890-899, after zeroing its counters).  Persistent blocks, launched
+// cooperatively so that all of them are resident:
+//   phase 1  groups of 8 tokens round-robin over the blocks: top-k, weights, slots (route_group);
+//   barrier  over the grid (sync[0] counts arrivals; bounded wait);
+//   phase 2  every block forms the offsets from the now final counts, then tokens round-robin over the
+//            blocks: each row copied to its routes' slab rows (dispatch_token);
+//   cleanup  the last block to finish (sync[1] counts them) zeroes the counters and both sync words, so
+//            the next launch needs no memset: `counts` and `sync` are zeroed once by their owner and are
+//            zero again whenever this kernel is not running.
+template <int MAXPL>
+__global__ void __launch_bounds__(256) route_dispatch_kernel(RouteArgs ra, DispatchArgs da, int* sync) {
+  extern __shared__ int sh[];            // phase 1: hist + base [2 n_local]; phase 2: offs [n_local + 1]
+  __shared__ float scratch[32];
+  __shared__ int give_up;
+  const int warps = blockDim.x >> 5;
+  const int n_groups = (ra.tokens + warps - 1) / warps;
+  for (int g = blockIdx.x; g < n_groups; g += gridDim.x) route_group<MAXPL>(ra, g, sh);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    give_up = 0;
+    __threadfence();
+    atomicAdd(&sync[0], 1);
+    const uint64_t t0 = global_ns();
+    for (uint32_t i = 0;; ++i) {
+      int seen;
+      asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(sync) : "memory");
+      if (seen >= static_cast<int>(gridDim.x)) break;
+      if ((i & 255u) == 255u && global_ns() - t0 > kWaitLimitNs) {
+        report_error(da.status, MSL_ERR_DEVICE_TIMEOUT);
+        give_up = 1;
+        break;
+      }
+      __nanosleep(32);
+    }
+  }
+  __syncthreads();
+  if (!give_up) {
+    scan_counts(da.counts, da.n_local, sh);
+    if (blockIdx.x == 0 && da.offsets_out != nullptr)
+      for (int i = threadIdx.x; i <= da.n_local; i += blockDim.x) da.offsets_out[i] = sh[i];
+    for (int t = blockIdx.x; t < ra.tokens; t += gridDim.x) {
+      dispatch_token(da, t, sh, scratch);
+      __syncthreads();                   // scratch is reused by the next token's norm
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    give_up = atomicAdd(&sync[1], 1) == static_cast<int>(gridDim.x) - 1;   // reused: "this block is the last"
+  }
+  __syncthreads();
+  if (give_up) {
+    for (int i = threadIdx.x; i < ra.n_local; i += blockDim.x) ra.counts[i] = 0;
+    if (threadIdx.x == 0) { sync[0] = 0; sync[1] = 0; }
   }
 }
 
@@ -409,8 +527,9 @@ kv_rows_copy_kernel(const uint8_t* __restrict__ src, const int64_t* __restrict__
 // counts_all[s][e]: routes of rank s to global expert e (all-gathered).  Rank d owns experts
 // [d * el, (d + 1) * el); its slab holds row groups ordered (source rank, local expert).  For this
 // rank `me`: dest_base[e] = first row, in the owner's slab, of the group (me, e); group_offsets =
-// row ranges of this rank's own slab (consumed by the grouped GEMM).  A slab that would need more than
-// `cap` rows is reported in *status.
+// row ranges of this rank's own slab (consumed by the grouped GEMM), clamped to `cap`: a routing that
+// would need more than `cap` rows is reported in *status, the groups past the end come out empty (the
+// dispatch skips the same rows), and nothing downstream addresses a row at or beyond `cap`.
 __global__ void ep_plan_kernel(const int* __restrict__ counts_all, int world, int el, int me, int cap,
                                int* __restrict__ dest_base, int* __restrict__ group_offsets, int* status) {
   const int n_experts = world * el;
@@ -426,10 +545,10 @@ __global__ void ep_plan_kernel(const int* __restrict__ counts_all, int world, in
     int run = 0;
     for (int s = 0; s < world; ++s)
       for (int le = 0; le < el; ++le) {
-        group_offsets[s * el + le] = run;
+        group_offsets[s * el + le] = min(run, cap);
         run += counts_all[s * n_experts + me * el + le];
       }
-    group_offsets[world * el] = run;
+    group_offsets[world * el] = min(run, cap);
     if (run > cap) report_error(status, MSL_ERR_CAPACITY);
   }
 }
@@ -441,7 +560,7 @@ __global__ void __launch_bounds__(256)
 dispatch_peer_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, const float* __restrict__ norm_w,
                      const int* __restrict__ ids, const int* __restrict__ slots, const int* __restrict__ dest_base,
                      __nv_bfloat16* const* __restrict__ peer_bases, int el, int cap, int top_k, int width,
-                     int* __restrict__ rowmap, int* const* __restrict__ index_bases) {
+                     int* __restrict__ rowmap) {
   __shared__ float scratch[32];
   const int t = blockIdx.x;
   const int chunks = width / 8;
@@ -463,11 +582,7 @@ dispatch_peer_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, const flo
     const int d = e / el;
     const int row = dest_base[e] + slots[t * top_k + j];
     const bool ok = row < cap;                 // an overflowing slab was already reported by the plan
-    if (threadIdx.x == 0) {
-      rowmap[t * top_k + j] = ok ? d * cap + row : -1;
-      // where the owner's down projection returns this route's output row: row t * top_k + j of this rank
-      if (ok && index_bases != nullptr) index_bases[d][row] = t * top_k + j;
-    }
+    if (threadIdx.x == 0) rowmap[t * top_k + j] = ok ? d * cap + row : -1;
     if (ok) dst[nr++] = peer_bases[d] + static_cast<int64_t>(row) * width;
   }
   for (int ch = threadIdx.x; ch < chunks; ch += blockDim.x) {
@@ -534,18 +649,34 @@ __device__ __forceinline__ void bulk_row_load(void* dst, const void* src, uint32
                ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
 
-template <int MAXC>
-__global__ void __launch_bounds__(kCombineThreads, MAXC <= 2 ? 5 : 3)
+// Residual boundary applied to the combined row while it is still in registers (FUSED instantiation): the
+// row f = bf16(sum) is what the unfused path would have written and re-read, so both paths give the same
+// bits; then b = f * branch_scale, s_out = alpha * s_in + beta * rms(b, eps_branch),
+// h_out = bf16(rms(s_out, eps_out) * norm_w), exactly as boundary_kernel.
+struct BoundaryTail {
+  const float* branch_scale;   // may be NULL
+  const float* s_in;           // fp32 [tokens, width]
+  const float* alpha;
+  const float* beta;
+  const float* norm_w;
+  float* s_out;                // fp32 [tokens, width]
+  __nv_bfloat16* h_out;        // bf16 [tokens, ld_h]
+  int64_t ld_h;
+  float eps_branch, eps_out;
+};
+
+template <int MAXC, bool FUSED>
+__global__ void __launch_bounds__(kCombineThreads, MAXC <= 2 ? (FUSED ? 4 : 5) : (FUSED ? 2 : 3))
 combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ rowmap, const float* __restrict__ w,
-                    const float* __restrict__ post_w, const __nv_bfloat16* __restrict__ addend, int64_t ld_add,
-                    __nv_bfloat16* __restrict__ out, int64_t ld_out, int top_k, int width) {
+               const float* __restrict__ post_w, const __nv_bfloat16* __restrict__ addend, int64_t ld_add,
+               __nv_bfloat16* __restrict__ out, int64_t ld_out, int top_k, int width, BoundaryTail bt, int* status) {
   constexpr int THREADS = kCombineThreads;
   constexpr int R = kBulkRows;
   extern __shared__ __align__(128) uint8_t rows_smem[];     // [2][R][width] bf16
   __shared__ __align__(8) uint64_t bars[2];
   __shared__ float scratch[32 * R];
   __shared__ int route_of[32], row_of[32];
-  __shared__ int n_valid_s;
+  __shared__ int n_valid_s, failed_s;
   const int t = blockIdx.x;
   const int chunks = width / 8;
   const uint32_t row_bytes = static_cast<uint32_t>(width) * 2u;
@@ -560,6 +691,7 @@ combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ rowm
     }
     if (j == 0) {
       n_valid_s = __popc(have);
+      failed_s = 0;
       mbar_init(&bars[0], 1);
       mbar_init(&bars[1], 1);
       mbar_fence_init();
@@ -589,7 +721,12 @@ combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ rowm
   for (int r = 0; r < n_rounds; ++r) {
     const int n_round = min(R, n_valid - r * R);
     const uint8_t* buf = rows_smem + static_cast<size_t>((r & 1) * R) * row_bytes;
-    mbar_wait(&bars[r & 1], (r >> 1) & 1);                  // a bulk copy of mapped memory always lands
+    // A bulk copy of mapped memory always lands; should the bounded wait run out all the same, the
+    // block reports it and, after the next block-wide barrier, leaves without writing its token.
+    if (!mbar_wait(&bars[r & 1], (r >> 1) & 1)) {
+      report_error(status, MSL_ERR_DEVICE_TIMEOUT);
+      failed_s = 1;
+    }
     float ss[R];
 #pragma unroll
     for (int q = 0; q < R; ++q) ss[q] = 0.f;
@@ -612,6 +749,11 @@ combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ rowm
       }
     }
     block_sum<R>(ss, scratch);
+    if (failed_s) {                                         // uniform: written before the barriers inside block_sum
+      if (threadIdx.x == 0) drain_pause();                  // copies still in flight target this block's memory
+      __syncthreads();
+      return;
+    }
     float rr[R];
 #pragma unroll
     for (int q = 0; q < R; ++q)
@@ -635,6 +777,7 @@ combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ rowm
     __syncthreads();
     if (threadIdx.x == 0 && r + 2 < n_rounds) issue(r + 2);
   }
+  // f = addend + post_w * sum, rounded to bf16
 #pragma unroll
   for (int c = 0; c < MAXC; ++c) {
     const int ch = threadIdx.x + c * THREADS;
@@ -646,7 +789,70 @@ combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ rowm
       if (addend != nullptr) unpack8(*reinterpret_cast<const uint4*>(addend + t * ld_add + ch * 8), o);
 #pragma unroll
       for (int i = 0; i < 8; ++i) o[i] += acc[c][i] * pw[i];
-      *reinterpret_cast<uint4*>(out + t * ld_out + ch * 8) = pack8(o);
+      const uint4 packed = pack8(o);
+      if constexpr (FUSED) unpack8(packed, acc[c]);          // the bf16-rounded row, as the unfused path re-reads it
+      else *reinterpret_cast<uint4*>(out + t * ld_out + ch * 8) = packed;
+    }
+  }
+  if constexpr (FUSED) {
+    const int64_t row = t;
+    float s[MAXC][8];
+    float ss[1] = {0.f};
+#pragma unroll
+    for (int c = 0; c < MAXC; ++c) {
+      const int ch = threadIdx.x + c * THREADS;
+      if (ch < chunks) {
+        if (bt.branch_scale != nullptr) {
+          const float4 w0 = *reinterpret_cast<const float4*>(bt.branch_scale + ch * 8);
+          const float4 w1 = *reinterpret_cast<const float4*>(bt.branch_scale + ch * 8 + 4);
+          acc[c][0] *= w0.x; acc[c][1] *= w0.y; acc[c][2] *= w0.z; acc[c][3] *= w0.w;
+          acc[c][4] *= w1.x; acc[c][5] *= w1.y; acc[c][6] *= w1.z; acc[c][7] *= w1.w;
+        }
+        const float4 s0 = *reinterpret_cast<const float4*>(bt.s_in + row * width + ch * 8);
+        const float4 s1 = *reinterpret_cast<const float4*>(bt.s_in + row * width + ch * 8 + 4);
+        s[c][0] = s0.x; s[c][1] = s0.y; s[c][2] = s0.z; s[c][3] = s0.w;
+        s[c][4] = s1.x; s[c][5] = s1.y; s[c][6] = s1.z; s[c][7] = s1.w;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss[0] += acc[c][i] * acc[c][i];
+      }
+    }
+    block_sum<1>(ss, scratch);
+    const float rb = 1.0f / sqrtf(ss[0] / width + bt.eps_branch);
+    float s2[1] = {0.f};
+#pragma unroll
+    for (int c = 0; c < MAXC; ++c) {
+      const int ch = threadIdx.x + c * THREADS;
+      if (ch < chunks) {
+        const float4 a0 = *reinterpret_cast<const float4*>(bt.alpha + ch * 8);
+        const float4 a1 = *reinterpret_cast<const float4*>(bt.alpha + ch * 8 + 4);
+        const float4 b0 = *reinterpret_cast<const float4*>(bt.beta + ch * 8);
+        const float4 b1 = *reinterpret_cast<const float4*>(bt.beta + ch * 8 + 4);
+        const float al[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+        const float be[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          s[c][i] = al[i] * s[c][i] + be[i] * (acc[c][i] * rb);
+          s2[0] += s[c][i] * s[c][i];
+        }
+        float* dst = bt.s_out + row * width + ch * 8;
+        *reinterpret_cast<float4*>(dst) = make_float4(s[c][0], s[c][1], s[c][2], s[c][3]);
+        *reinterpret_cast<float4*>(dst + 4) = make_float4(s[c][4], s[c][5], s[c][6], s[c][7]);
+      }
+    }
+    block_sum<1>(s2, scratch);
+    const float rs = 1.0f / sqrtf(s2[0] / width + bt.eps_out);
+#pragma unroll
+    for (int c = 0; c < MAXC; ++c) {
+      const int ch = threadIdx.x + c * THREADS;
+      if (ch < chunks) {
+        const float4 w0 = *reinterpret_cast<const float4*>(bt.norm_w + ch * 8);
+        const float4 w1 = *reinterpret_cast<const float4*>(bt.norm_w + ch * 8 + 4);
+        const float nw[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+        float o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = s[c][i] * rs * nw[i];
+        *reinterpret_cast<uint4*>(bt.h_out + row * bt.ld_h + ch * 8) = pack8(o);
+      }
     }
   }
 }
@@ -664,7 +870,7 @@ combine_peer_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__
                const float* __restrict__ post_w, const __nv_bfloat16* __restrict__ addend, int64_t ld_add,
                __nv_bfloat16* __restrict__ out, int64_t ld_out, int top_k, int width,
                const __nv_bfloat16* const* __restrict__ peer_bases, int peer_cap) {
-  extern __shared__ __align__(16) uint8_t rows_smem[];      // [top_k][width] bf16
+  extern __shared__ __align__(16) uint8_t peer_rows_smem[];      // [top_k][width] bf16
   __shared__ float scratch[32 * MAXK];
   const int t = blockIdx.x;
   const int chunks = width / 8;
@@ -675,7 +881,7 @@ combine_peer_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__
       valid |= 1u << j;
       const __nv_bfloat16* src = peer_bases[row / peer_cap] + static_cast<int64_t>(row % peer_cap) * width;
       for (int ch = threadIdx.x; ch < chunks; ch += blockDim.x) {
-        const uint32_t dst = smem_u32(rows_smem + (static_cast<size_t>(j) * width + ch * 8) * 2);
+        const uint32_t dst = smem_u32(peer_rows_smem + (static_cast<size_t>(j) * width + ch * 8) * 2);
         asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src + ch * 8) : "memory");
       }
     }
@@ -694,7 +900,7 @@ combine_peer_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__
     for (int j = 0; j < MAXK; ++j) {
       if (valid & (1u << j)) {
         float v[8];
-        unpack8(*reinterpret_cast<const uint4*>(rows_smem + (static_cast<size_t>(j) * width + ch * 8) * 2), v);
+        unpack8(*reinterpret_cast<const uint4*>(peer_rows_smem + (static_cast<size_t>(j) * width + ch * 8) * 2), v);
 #pragma unroll
         for (int i = 0; i < 8; ++i) { const float x = v[i] * pw[i]; ss[j] += x * x; }
       }
@@ -715,7 +921,7 @@ combine_peer_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__
     for (int j = 0; j < MAXK; ++j) {
       if (valid & (1u << j)) {
         float v[8];
-        unpack8(*reinterpret_cast<const uint4*>(rows_smem + (static_cast<size_t>(j) * width + ch * 8) * 2), v);
+        unpack8(*reinterpret_cast<const uint4*>(peer_rows_smem + (static_cast<size_t>(j) * width + ch * 8) * 2), v);
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[i] += v[i] * pw[i] * r[j];
       }
@@ -793,109 +999,207 @@ extern "C" int msl_boundary(const void* branch, int64_t ld_branch, const float* 
   return cudaGetLastError() == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
 }
 
-extern "C" int msl_route_topk(const float* logits, int64_t ld, int hilo, const float* bias, float multiplier,
-                              const int* local_start, int tokens, int n_experts, int top_k, int n_local, int* ids,
-                              float* weights, int* local_ids, int* slots, int* counts, void* stream) {
-  if (!logits || !bias || !local_start || !ids || !weights || !local_ids || !slots || !counts) return MSL_ERR_ARG;
+// Host-side argument checks shared by the routing / dispatch entry points (nothing is launched before
+// every check of an entry point has passed).
+static int check_route(const float* logits, const float* bias, const int* local_start, int tokens, int n_experts,
+                       int top_k, int n_local, const int* ids, const float* weights) {
+  if (!logits || !bias || !local_start || !ids || !weights) return MSL_ERR_ARG;
   if (tokens < 0 || n_experts <= 0 || top_k <= 0 || top_k > 32 || top_k > n_experts || n_local <= 0 ||
       n_local > n_experts)
     return MSL_ERR_ARG;
   if (n_experts > 512) return MSL_ERR_UNSUPPORTED;
-  if (tokens == 0) return MSL_OK;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int blocks = (tokens + 7) / 8;
-  const size_t smem = 2 * static_cast<size_t>(n_local) * sizeof(int);
-  if (n_experts <= 128)
-    route_topk_kernel<4><<<blocks, 256, smem, st>>>(logits, ld, hilo, bias, multiplier, local_start, tokens,
-                                                    n_experts, top_k, n_local, ids, weights, local_ids, slots, counts);
-  else if (n_experts <= 256)
-    route_topk_kernel<8><<<blocks, 256, smem, st>>>(logits, ld, hilo, bias, multiplier, local_start, tokens,
-                                                    n_experts, top_k, n_local, ids, weights, local_ids, slots, counts);
-  else
-    route_topk_kernel<16><<<blocks, 256, smem, st>>>(logits, ld, hilo, bias, multiplier, local_start, tokens,
-                                                     n_experts, top_k, n_local, ids, weights, local_ids, slots,
-                                                     counts);
+  return MSL_OK;
+}
+
+static int check_dispatch(const void* x, int64_t ldx, int tokens, int n_local, int top_k, int width, const void* slab,
+                          int64_t slab_rows, const int* rowmap) {
+  if (!x || !slab || !rowmap) return MSL_ERR_ARG;
+  if (tokens < 0 || n_local <= 0 || n_local > 1024 || top_k <= 0 || top_k > 16 || width <= 0 || slab_rows < 0)
+    return MSL_ERR_ARG;
+  if ((width & 7) || (ldx & 7) || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(slab) & 15))
+    return MSL_ERR_ALIGN;
+  return MSL_OK;
+}
+
+static int launch_route(const RouteArgs& a, cudaStream_t st) {
+  const int blocks = (a.tokens + 7) / 8;
+  const size_t smem = 2 * static_cast<size_t>(a.n_local) * sizeof(int);
+  if (a.n_experts <= 128) route_topk_kernel<4><<<blocks, 256, smem, st>>>(a);
+  else if (a.n_experts <= 256) route_topk_kernel<8><<<blocks, 256, smem, st>>>(a);
+  else route_topk_kernel<16><<<blocks, 256, smem, st>>>(a);
   return cudaGetLastError() == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
+}
+
+static int launch_dispatch(const DispatchArgs& a, int tokens, cudaStream_t st) {
+  const int threads = std::min(256, ((a.width / 8 + 31) / 32) * 32);
+  dispatch_kernel<<<tokens, threads, (a.n_local + 1) * sizeof(int), st>>>(a);
+  return cudaGetLastError() == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
+}
+
+extern "C" int msl_route_topk(const float* logits, int64_t ld, int hilo, const float* bias, float multiplier,
+                              const int* local_start, int tokens, int n_experts, int top_k, int n_local, int* ids,
+                              float* weights, int* local_ids, int* slots, int* counts, void* stream) {
+  if (!local_ids || !slots || !counts) return MSL_ERR_ARG;
+  if (int rc = check_route(logits, bias, local_start, tokens, n_experts, top_k, n_local, ids, weights)) return rc;
+  if (tokens == 0) return MSL_OK;
+  return launch_route(RouteArgs{logits, ld, hilo, bias, multiplier, local_start, tokens, n_experts, top_k, n_local, ids,
+                                weights, local_ids, slots, counts},
+                      static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int msl_dispatch(const void* x, int64_t ldx, const float* norm_w, const int* local_ids, const int* slots,
                             const int* counts, int tokens, int n_local, int top_k, int width, void* slab,
                             int64_t slab_rows, int* rowmap, int* offsets_out, int* status, void* stream) {
-  if (!x || !local_ids || !slots || !counts || !slab || !rowmap) return MSL_ERR_ARG;
-  if (tokens < 0 || n_local <= 0 || n_local > 1024 || top_k <= 0 || top_k > 16 || width <= 0) return MSL_ERR_ARG;
-  if ((width & 7) || (ldx & 7) || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(slab) & 15))
-    return MSL_ERR_ALIGN;
+  if (!local_ids || !slots || !counts) return MSL_ERR_ARG;
+  if (int rc = check_dispatch(x, ldx, tokens, n_local, top_k, width, slab, slab_rows, rowmap)) return rc;
   if (tokens == 0) return MSL_OK;
-  const int threads = std::min(256, ((width / 8 + 31) / 32) * 32);
-  dispatch_kernel<<<tokens, threads, (n_local + 1) * sizeof(int), static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(x), ldx, norm_w, local_ids, slots, counts, n_local, top_k, width,
-      static_cast<__nv_bfloat16*>(slab), slab_rows, rowmap, offsets_out, status);
-  return cudaGetLastError() == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
+  return launch_dispatch(DispatchArgs{static_cast<const __nv_bfloat16*>(x), ldx, norm_w, local_ids, slots, counts,
+                                      n_local, top_k, width, static_cast<__nv_bfloat16*>(slab), slab_rows, rowmap,
+                                      offsets_out, status},
+                         tokens, static_cast<cudaStream_t>(stream));
+}
+
+// Resident blocks of the fused routing + dispatch kernel on the current device (cooperative launches
+// may not exceed it), looked up once per device.
+template <int MAXPL>
+static int route_dispatch_max_blocks(size_t smem) {
+  static std::atomic<int> cached[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  int v = cached[dev].load(std::memory_order_relaxed);
+  if (v == 0) {
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, route_dispatch_kernel<MAXPL>, 256, smem) !=
+            cudaSuccess || per_sm <= 0)
+      return 0;
+    v = per_sm * sm_count();
+    cached[dev].store(v, std::memory_order_relaxed);
+  }
+  return v;
+}
+
+template <int MAXPL>
+static int launch_route_dispatch(RouteArgs ra, DispatchArgs da, int* sync, cudaStream_t st) {
+  // shared memory: the larger of phase 1's two histograms and phase 2's offsets (sized for the worst case
+  // so that the occupancy look-up holds for every call)
+  const size_t smem = 2 * 1024 * sizeof(int) + sizeof(int);
+  const int most = route_dispatch_max_blocks<MAXPL>(smem);
+  if (most <= 0) return MSL_ERR_CUDA;
+  const int grid = std::max(1, std::min(most, ra.tokens));
+  void* args[] = {&ra, &da, &sync};
+  return cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(route_dispatch_kernel<MAXPL>), dim3(grid),
+                                     dim3(256), args, smem, st) == cudaSuccess
+             ? MSL_OK
+             : MSL_ERR_CUDA;
+}
+
+extern "C" int msl_route_dispatch(const float* logits, int64_t ld, int hilo, const float* bias, float multiplier,
+                                  const int* local_start, const void* x, int64_t ldx, const float* norm_w,
+                                  int tokens, int n_experts, int top_k, int n_local, int width, int* ids,
+                                  float* weights, int* local_ids, int* slots, int* counts, int* sync, void* slab,
+                                  int64_t slab_rows, int* rowmap, int* offsets_out, int* status, void* stream) {
+  if (!local_ids || !slots || !counts || !sync || !offsets_out) return MSL_ERR_ARG;
+  if (int rc = check_route(logits, bias, local_start, tokens, n_experts, top_k, n_local, ids, weights)) return rc;
+  if (int rc = check_dispatch(x, ldx, tokens, n_local, top_k, width, slab, slab_rows, rowmap)) return rc;
+  if (tokens == 0) return MSL_OK;
+  const RouteArgs ra{logits, ld, hilo, bias, multiplier, local_start, tokens, n_experts, top_k, n_local, ids, weights,
+                     local_ids, slots, counts};
+  const DispatchArgs da{static_cast<const __nv_bfloat16*>(x), ldx, norm_w, local_ids, slots, counts, n_local, top_k,
+                        width, static_cast<__nv_bfloat16*>(slab), slab_rows, rowmap, offsets_out, status};
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (n_experts <= 128) return launch_route_dispatch<4>(ra, da, sync, st);
+  if (n_experts <= 256) return launch_route_dispatch<8>(ra, da, sync, st);
+  return launch_route_dispatch<16>(ra, da, sync, st);
 }
 
 static int combine_launch(const void* y, const int* rowmap, const float* weights, const float* post_w,
                           const void* addend, int64_t ld_addend, void* out, int64_t ld_out, int tokens, int top_k,
-                          int width, const void* const* peer_bases, int peer_cap, void* stream) {
-  if ((!y && !peer_bases) || !rowmap || !weights || !post_w || !out) return MSL_ERR_ARG;
+                          int width, const void* const* peer_bases, int peer_cap, const BoundaryTail* tail,
+                          int* status, void* stream) {
+  if ((!y && !peer_bases) || !rowmap || !weights || !post_w || (!out && !tail)) return MSL_ERR_ARG;
   if (tokens < 0 || top_k <= 0 || top_k > 32 || width <= 0) return MSL_ERR_ARG;
   if ((width & 7) || (ld_out & 7) || (ld_addend & 7)) return MSL_ERR_ALIGN;
   if (width > 8 * kCombineThreads * kCombineMaxChunks) return MSL_ERR_UNSUPPORTED;
   if (tokens == 0) return MSL_OK;
   constexpr int kPeerSmemMax = 200 * 1024;
-  static bool configured = false;
-  if (!configured) {
-    const int most = 2 * kBulkRows * 8 * kCombineThreads * kCombineMaxChunks * 2;
-    if (cudaFuncSetAttribute(combine_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, most) != cudaSuccess ||
-        cudaFuncSetAttribute(combine_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, most) != cudaSuccess ||
-        cudaFuncSetAttribute(combine_peer_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPeerSmemMax) !=
-            cudaSuccess ||
-        cudaFuncSetAttribute(combine_peer_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPeerSmemMax) !=
-            cudaSuccess)
-      return MSL_ERR_CUDA;
-    configured = true;
-  }
+  const int most = 2 * kBulkRows * 8 * kCombineThreads * kCombineMaxChunks * 2;
+  static SmemConfig c2, c4, c2f, c4f, p4, p8;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   auto* yy = static_cast<const __nv_bfloat16*>(y);
   auto* ad = static_cast<const __nv_bfloat16*>(addend);
   auto* oo = static_cast<__nv_bfloat16*>(out);
   auto* pb = reinterpret_cast<const __nv_bfloat16* const*>(peer_bases);
   if (pb != nullptr) {
-    if (peer_cap <= 0) return MSL_ERR_ARG;
+    if (peer_cap <= 0 || tail != nullptr) return MSL_ERR_ARG;
     if (top_k > 8 || static_cast<int64_t>(top_k) * width * 2 > kPeerSmemMax) return MSL_ERR_UNSUPPORTED;
     const int threads = std::min(512, ((width / 8 + 31) / 32) * 32);
     const int smem = top_k * width * 2;                     // all of a token's rows
-    if (top_k <= 4)
+    if (top_k <= 4) {
+      if (int rc = p4.ensure(combine_peer_kernel<4>, kPeerSmemMax)) return rc;
       combine_peer_kernel<4><<<tokens, threads, smem, st>>>(yy, rowmap, weights, post_w, ad, ld_addend, oo, ld_out,
                                                             top_k, width, pb, peer_cap);
-    else
+    } else {
+      if (int rc = p8.ensure(combine_peer_kernel<8>, kPeerSmemMax)) return rc;
       combine_peer_kernel<8><<<tokens, threads, smem, st>>>(yy, rowmap, weights, post_w, ad, ld_addend, oo, ld_out,
                                                             top_k, width, pb, peer_cap);
+    }
+    return cudaGetLastError() == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
+  }
+  if (reinterpret_cast<uintptr_t>(y) & 15) return MSL_ERR_ALIGN;
+  const int smem = 2 * kBulkRows * width * 2;               // two buffers: 32 KB at width 4096
+  const bool small = width <= 8 * kCombineThreads * 2;
+  if (tail != nullptr) {
+    if (small) {
+      if (int rc = c2f.ensure(combine_kernel<2, true>, most)) return rc;
+      combine_kernel<2, true><<<tokens, kCombineThreads, smem, st>>>(yy, rowmap, weights, post_w, ad, ld_addend, oo,
+                                                                      ld_out, top_k, width, *tail, status);
+    } else {
+      if (int rc = c4f.ensure(combine_kernel<4, true>, most)) return rc;
+      combine_kernel<4, true><<<tokens, kCombineThreads, smem, st>>>(yy, rowmap, weights, post_w, ad, ld_addend, oo,
+                                                                      ld_out, top_k, width, *tail, status);
+    }
   } else {
-    if (reinterpret_cast<uintptr_t>(y) & 15) return MSL_ERR_ALIGN;
-    const int smem = 2 * kBulkRows * width * 2;             // two buffers: 32 KB at width 4096
-    if (width <= 8 * kCombineThreads * 2)
-      combine_kernel<2><<<tokens, kCombineThreads, smem, st>>>(yy, rowmap, weights, post_w, ad, ld_addend, oo, ld_out,
-                                                               top_k, width);
-    else
-      combine_kernel<4><<<tokens, kCombineThreads, smem, st>>>(yy, rowmap, weights, post_w, ad, ld_addend, oo, ld_out,
-                                                               top_k, width);
+    const BoundaryTail none{};
+    if (small) {
+      if (int rc = c2.ensure(combine_kernel<2, false>, most)) return rc;
+      combine_kernel<2, false><<<tokens, kCombineThreads, smem, st>>>(yy, rowmap, weights, post_w, ad, ld_addend, oo,
+                                                                       ld_out, top_k, width, none, status);
+    } else {
+      if (int rc = c4.ensure(combine_kernel<4, false>, most)) return rc;
+      combine_kernel<4, false><<<tokens, kCombineThreads, smem, st>>>(yy, rowmap, weights, post_w, ad, ld_addend, oo,
+                                                                       ld_out, top_k, width, none, status);
+    }
   }
   return cudaGetLastError() == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
 }
 
 extern "C" int msl_combine(const void* y, const int* rowmap, const float* weights, const float* post_w,
                            const void* addend, int64_t ld_addend, void* out, int64_t ld_out, int tokens, int top_k,
-                           int width, void* stream) {
+                           int width, int* status, void* stream) {
+  if (!out) return MSL_ERR_ARG;
   return combine_launch(y, rowmap, weights, post_w, addend, ld_addend, out, ld_out, tokens, top_k, width, nullptr, 0,
-                        stream);
+                        nullptr, status, stream);
+}
+
+extern "C" int msl_combine_boundary(const void* y, const int* rowmap, const float* weights, const float* post_w,
+                                    const void* addend, int64_t ld_addend, int tokens, int top_k, int width,
+                                    const float* branch_scale, const float* stream_in, const float* alpha,
+                                    const float* beta, const float* norm_w, float* stream_out, void* hidden_out,
+                                    int64_t ld_hidden, float eps_branch, float eps_out, int* status, void* stream) {
+  if (!stream_in || !alpha || !beta || !norm_w || !stream_out || !hidden_out) return MSL_ERR_ARG;
+  if (ld_hidden & 7) return MSL_ERR_ALIGN;
+  const BoundaryTail tail{branch_scale, stream_in, alpha, beta, norm_w, stream_out,
+                          static_cast<__nv_bfloat16*>(hidden_out), ld_hidden, eps_branch, eps_out};
+  return combine_launch(y, rowmap, weights, post_w, addend, ld_addend, nullptr, 0, tokens, top_k, width, nullptr, 0,
+                        &tail, status, stream);
 }
 
 extern "C" int msl_combine_peer(const void* const* peer_bases, int peer_cap, const int* rowmap, const float* weights,
                                 const float* post_w, const void* addend, int64_t ld_addend, void* out, int64_t ld_out,
                                 int tokens, int top_k, int width, void* stream) {
-  if (!peer_bases) return MSL_ERR_ARG;
+  if (!peer_bases || !out) return MSL_ERR_ARG;
   return combine_launch(nullptr, rowmap, weights, post_w, addend, ld_addend, out, ld_out, tokens, top_k, width,
-                        peer_bases, peer_cap, stream);
+                        peer_bases, peer_cap, nullptr, nullptr, stream);
 }
 
 
@@ -936,22 +1240,29 @@ extern "C" int msl_route_dispatch_static(const float* logits, int64_t ld, int hi
                                          const float* norm_w, int tokens, int n_experts, int top_k, int n_local,
                                          int width, int* ids, float* weights, void* slab, int64_t slab_rows,
                                          int* rowmap, int* offsets_out, int* status, void* stream) {
-  if (tokens < 0 || top_k <= 0) return MSL_ERR_ARG;
+  // Every argument is checked before the scratch is touched or anything is enqueued, so a rejected call
+  // leaves the outputs and the shared array as they were.
+  if (int rc = check_route(logits, bias, local_start, tokens, n_experts, top_k, n_local, ids, weights)) return rc;
   if (n_local > kStaticMaxLocal || static_cast<int64_t>(tokens) * top_k > kStaticMaxRoutes) return MSL_ERR_CAPACITY;
+  if (int rc = check_dispatch(x, ldx, tokens, n_local, top_k, width, slab, slab_rows, rowmap)) return rc;
+  if (tokens == 0) return MSL_OK;
   int* scratch = route_scratch_ptr();
   if (scratch == nullptr) return MSL_ERR_CUDA;
   int* counts = scratch;
   int* local_ids = scratch + kStaticMaxLocal;
   int* slots = local_ids + kStaticMaxRoutes;
-  if (tokens == 0) return MSL_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
   // The counters keep the previous call's totals: clear them on the stream before counting again.
-  zero_ints_kernel<<<(n_local + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(counts, n_local);
+  zero_ints_kernel<<<(n_local + 255) / 256, 256, 0, st>>>(counts, n_local);
   if (cudaGetLastError() != cudaSuccess) return MSL_ERR_CUDA;
-  int rc = msl_route_topk(logits, ld, hilo, bias, multiplier, local_start, tokens, n_experts, top_k, n_local, ids,
-                          weights, local_ids, slots, counts, stream);
+  int rc = launch_route(RouteArgs{logits, ld, hilo, bias, multiplier, local_start, tokens, n_experts, top_k, n_local,
+                                  ids, weights, local_ids, slots, counts},
+                        st);
   if (rc != MSL_OK) return rc;
-  return msl_dispatch(x, ldx, norm_w, local_ids, slots, counts, tokens, n_local, top_k, width, slab, slab_rows, rowmap,
-                      offsets_out, status, stream);
+  return launch_dispatch(DispatchArgs{static_cast<const __nv_bfloat16*>(x), ldx, norm_w, local_ids, slots, counts,
+                                      n_local, top_k, width, static_cast<__nv_bfloat16*>(slab), slab_rows, rowmap,
+                                      offsets_out, status},
+                         tokens, st);
 }
 
 
@@ -967,8 +1278,7 @@ extern "C" int msl_ep_plan(const int* counts_all, int world, int local_experts, 
 
 extern "C" int msl_dispatch_peer(const void* x, int64_t ldx, const float* norm_w, const int* ids, const int* slots,
                                  const int* dest_base, void* const* peer_bases, int local_experts, int cap,
-                                 int tokens, int top_k, int width, int* rowmap, int* const* index_bases,
-                                 void* stream) {
+                                 int tokens, int top_k, int width, int* rowmap, void* stream) {
   if (!x || !ids || !slots || !dest_base || !peer_bases || !rowmap) return MSL_ERR_ARG;
   if (tokens < 0 || local_experts <= 0 || cap <= 0 || top_k <= 0 || top_k > 16 || width <= 0) return MSL_ERR_ARG;
   if ((width & 7) || (ldx & 7) || (reinterpret_cast<uintptr_t>(x) & 15)) return MSL_ERR_ALIGN;
@@ -976,7 +1286,7 @@ extern "C" int msl_dispatch_peer(const void* x, int64_t ldx, const float* norm_w
   const int threads = std::min(256, ((width / 8 + 31) / 32) * 32);
   dispatch_peer_kernel<<<tokens, threads, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), ldx, norm_w, ids, slots, dest_base,
-      reinterpret_cast<__nv_bfloat16* const*>(peer_bases), local_experts, cap, top_k, width, rowmap, index_bases);
+      reinterpret_cast<__nv_bfloat16* const*>(peer_bases), local_experts, cap, top_k, width, rowmap);
   return cudaGetLastError() == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
 }
 

@@ -10,10 +10,10 @@
 //   warp 1     allocates tensor memory and issues tcgen05.mma (M=128, N=BN, K=16), 4 per stage
 //   warps 2-5  epilogue: tcgen05.ld the fp32 accumulator (one row per thread), convert, store
 // Two accumulator buffers (2 x BN columns of TMEM) let the epilogue of one tile overlap the main
-// loop of the next.  Every mbarrier wait is bounded; a wait that runs out records
+// loop of the next.  (A cta_group::2 form of this kernel, two CTAs sharing one M=256 MMA, was built and
+// measured at half this kernel's rate: its cross-CTA stage ring has twice the latency shared memory can
+// cover.  It is not kept.)  Every mbarrier wait is bounded; a wait that runs out records
 // MSL_ERR_DEVICE_TIMEOUT, and all roles fall through to the common teardown that frees the TMEM.
-#include <cstdlib>
-
 #include "msl_common.cuh"
 #include "msl_host.h"
 
@@ -291,13 +291,8 @@ template <int BN, int STAGES, int OUT, int SUBS = 1>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& args, cudaStream_t stream) {
   using S = GemmSmem<BN, STAGES, SUBS>;
   const int smem = S::kTotal + 1024;
-  static bool configured = false;   // per template instance; attribute is per function, set once per process
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN, STAGES, OUT, SUBS>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return MSL_ERR_CUDA;
-    configured = true;
-  }
+  static SmemConfig config;         // one per template instance, tracked per device
+  if (int rc = config.ensure(gemm_bf16_kernel<BN, STAGES, OUT, SUBS>, smem)) return rc;
   const int m_tiles = (args.m + kBM * SUBS - 1) / (kBM * SUBS);
   const int n_tiles = (args.n + BN - 1) / BN;
   const int grid = std::min(m_tiles * n_tiles * args.splits, sm_count());
@@ -329,213 +324,6 @@ splitk_reduce_kernel(const float* __restrict__ part, int splits, int m, int n, f
           make_uint2(pack_bf16x2(acc.x, acc.y), pack_bf16x2(acc.z, acc.w));
     }
   }
-}
-
-// ============================================================================ CTA-pair variant
-// The same GEMM with two CTAs of a cluster sharing one M=256 x N=256 tcgen05.mma (cta_group::2):
-// CTA r of the pair owns rows [256 mt + 128 r, +128) of A and of the accumulator and loads rows
-// [256 nt + 128 r, +128) of B; the tensor cores of both SMs read both halves of B.  Per SM and per
-// FLOP this halves the B bytes staged in and fetched from shared memory, which is what limits the
-// single-CTA kernel.  The even CTA issues the MMAs; "full" barriers live in the even CTA and count
-// the bytes of both CTAs' loads, "empty"/"accumulator ready" are signalled in both CTAs by one
-// commit, "accumulator drained" is counted in the even CTA.  No load uses cluster multicast.
-template <int STAGES>
-struct PairSmem {
-  static constexpr int kABytes = kBM * kBK * 2;
-  static constexpr int kBBytes = 128 * kBK * 2;
-  static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kBarOffset = STAGES * kStageBytes;
-  static constexpr int kTotal = kBarOffset + (2 * STAGES + 4) * 8 + 16;
-};
-
-template <int STAGES, int OUT>
-__global__ void __launch_bounds__(192, 1)
-gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, GemmArgs p) {
-  using S = PairSmem<STAGES>;
-  constexpr int BN = 256;
-  extern __shared__ __align__(1024) uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + S::kBarOffset);
-  uint64_t* empty = full + STAGES;
-  uint64_t* tmem_full = empty + STAGES;
-  uint64_t* tmem_empty = tmem_full + 2;
-  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
-  volatile uint32_t* abort_flag = tmem_base_slot + 1;
-
-  const int warp = threadIdx.x >> 5;
-  const int lane = threadIdx.x & 31;
-  const uint32_t rank = cluster_ctarank();          // 0 = leader
-  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
-  const int m_tiles = (p.m + 2 * kBM - 1) / (2 * kBM);
-  const int n_tiles = (p.n + BN - 1) / BN;
-  const int total_tiles = m_tiles * n_tiles;
-  const int kb_per_seg = (p.k + kBK - 1) / kBK;
-  const int k_blocks = kb_per_seg * p.segs;
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
-      // leader: its own producer's expect_tx arrival + the odd CTA's relay; odd CTA: its producer only
-      mbar_init(&full[s], cluster_ctarank() == 0 ? 2 : 1);
-      mbar_init(&empty[s], 1);
-    }
-    for (int a = 0; a < 2; ++a) {
-      mbar_init(&tmem_full[a], 1);
-      mbar_init(&tmem_empty[a], 8);    // 4 epilogue warps of each CTA (used in the leader only)
-    }
-    *abort_flag = 0;
-    mbar_fence_init();
-  }
-  if (warp == 1) tmem_alloc_pair(tmem_base_slot, 2 * BN);
-  tc_fence_before();
-  cluster_sync_all();                  // both CTAs' barriers exist before either signals the other
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_base_slot;
-
-  if (warp == 0) {
-    // ------------------------------------------------------------ TMA producer (one lane per CTA)
-    if (lane == 0) {
-      tma_prefetch_desc(&tm_a);
-      tma_prefetch_desc(&tm_b);
-      uint32_t it = 0;
-      bool ok = true;
-      for (int t = pair; t < total_tiles && ok; t += n_pairs) {
-        int mt, nt;
-        tile_coords(t, m_tiles, n_tiles, mt, nt);
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
-          if (*abort_flag || !mbar_wait(&empty[s], ph ^ 1)) { ok = false; break; }
-
-          const int seg = kb / kb_per_seg;
-          const int kk = (kb - seg * kb_per_seg) * kBK;
-          uint8_t* sa = smem + s * S::kStageBytes;
-          // Each CTA's loads complete on its own barrier; the odd CTA relays "stage full" to the leader.
-          mbar_expect_tx(&full[s], S::kStageBytes);
-          tma_load_2d(sa, &tm_a, &full[s], seg * p.a_seg_stride + kk, mt * 2 * kBM + rank * kBM);
-          tma_load_2d(sa + S::kABytes, &tm_b, &full[s], seg * p.b_seg_stride + kk, nt * BN + rank * 128);
-        }
-      }
-      if (!ok) { *abort_flag = 1; report_error(p.status, MSL_ERR_DEVICE_TIMEOUT); }
-    }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer (leader CTA, one lane)
-    if (rank == 1 && lane == 0) {
-      // relay: when this CTA's stage has landed, tell the leader (whose MMA reads both CTAs' tiles)
-      uint32_t it = 0;
-      bool ok = true;
-      for (int t = pair; t < total_tiles && ok; t += n_pairs) {
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-          const int s = it % STAGES;
-          if (*abort_flag || !mbar_wait(&full[s], (it / STAGES) & 1)) { ok = false; break; }
-          mbar_arrive_cluster(map_to_cta(smem_u32(&full[s]), 0));
-        }
-      }
-      if (!ok) { *abort_flag = 1; report_error(p.status, MSL_ERR_DEVICE_TIMEOUT); }
-    }
-    if (rank == 0 && lane == 0) {
-      constexpr uint32_t idesc = make_idesc(1, 1, 2 * kBM, BN);
-      uint32_t it = 0, tile_i = 0;
-      bool ok = true;
-      for (int t = pair; t < total_tiles && ok; t += n_pairs, ++tile_i) {
-        const uint32_t acc = tile_i & 1;
-        const uint32_t acc_ph = (tile_i >> 1) & 1;
-        if (*abort_flag || !mbar_wait(&tmem_empty[acc], acc_ph ^ 1)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
-          if (*abort_flag || !mbar_wait(&full[s], ph)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t sa = smem_u32(smem + s * S::kStageBytes);
-          const uint32_t sb = sa + S::kABytes;
-#pragma unroll
-          for (int k16 = 0; k16 < kBK / 16; ++k16)
-            tc_mma_f16_pair(d_tmem, make_sdesc(sa + k16 * 32, 16, 1024, 2), make_sdesc(sb + k16 * 32, 16, 1024, 2), idesc,
-                            (kb | k16) != 0);
-          tc_commit_pair(&empty[s]);
-        }
-        if (ok) tc_commit_pair(&tmem_full[acc]);
-      }
-      if (!ok) { *abort_flag = 1; report_error(p.status, MSL_ERR_DEVICE_TIMEOUT); }
-    }
-  } else {
-    // ------------------------------------------------------------ epilogue warps (both CTAs)
-    const int quarter = warp & 3;
-    uint32_t tile_i = 0;
-    bool ok = true;
-    for (int t = pair; t < total_tiles && ok; t += n_pairs, ++tile_i) {
-      int mt, nt;
-      tile_coords(t, m_tiles, n_tiles, mt, nt);
-      const uint32_t acc = tile_i & 1;
-      const uint32_t acc_ph = (tile_i >> 1) & 1;
-      if (*abort_flag || !mbar_wait(&tmem_full[acc], acc_ph)) { ok = false; break; }
-      tc_fence_after();
-      const int row = mt * 2 * kBM + rank * kBM + quarter * 32 + lane;
-      const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
-      if constexpr (OUT == MSL_OUT_SWIGLU_BF16) {
-#pragma unroll 1
-        for (int c = 0; c < BN / 2; c += 32) {
-          uint32_t g[32], u[32];
-          tmem_ld32(taddr + c, g);
-          tmem_ld32(taddr + BN / 2 + c, u);
-          tmem_ld_wait();
-          store_chunk<BN, OUT>(p, row, nt * (BN / 2) + c, g, u);
-        }
-      } else {
-#pragma unroll 1
-        for (int c = 0; c < BN; c += 32) {
-          uint32_t v[32];
-          tmem_ld32(taddr + c, v);
-          tmem_ld_wait();
-          store_chunk<BN, OUT>(p, row, nt * BN + c, v, v);
-        }
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[acc]), 0));
-    }
-    if (!ok && lane == 0) { *abort_flag = 1; report_error(p.status, MSL_ERR_DEVICE_TIMEOUT); }
-  }
-
-  if (warp == 0 && lane == 0 && *abort_flag) drain_pause();
-  tc_fence_before();
-  __syncthreads();
-  cluster_sync_all();                  // neither CTA leaves while the other may still signal it
-  if (warp == 1) {
-    __syncwarp();
-    tmem_dealloc_pair(tmem_base, 2 * BN);
-  }
-}
-
-template <int STAGES, int OUT>
-static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& args, cudaStream_t stream) {
-  using S = PairSmem<STAGES>;
-  const int smem = S::kTotal + 1024;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(gemm_bf16_pair_kernel<STAGES, OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
-        cudaSuccess)
-      return MSL_ERR_CUDA;
-    configured = true;
-  }
-  const int m_tiles = (args.m + 2 * kBM - 1) / (2 * kBM);
-  const int n_tiles = (args.n + 255) / 256;
-  const int pairs = std::min(m_tiles * n_tiles, sm_count() / 2);
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(2 * pairs);
-  cfg.blockDim = dim3(192);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 2;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, gemm_bf16_pair_kernel<STAGES, OUT>, ta, tb, args) == cudaSuccess ? MSL_OK
-                                                                                                 : MSL_ERR_CUDA;
 }
 
 }  // namespace msl
@@ -589,26 +377,9 @@ static int gemm_entry(const void* a, int64_t lda, const void* b, int64_t ldb, vo
   rc = make_tmap_2d(&tb, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, b_cols, n, ldb * 2, kBK, bn,
                     CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc) return rc;
-  // The CTA-pair kernel is correct but measured at half the single-CTA rate on this pool's B200s
-  // (its M256 MMA alone, with no loads, runs at 0.93 PFLOP/s against 1.77): opt-in only.
-  const char* pair_env = getenv("MSL_GEMM_PAIR");
-  const bool use_pair = !narrow && (n % 256 == 0) && m >= 256 && pair_env && pair_env[0] == '1';
-  if (use_pair) {
-    CUtensorMap tbp;
-    rc = make_tmap_2d(&tbp, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, b_cols, n, ldb * 2, kBK, 128,
-                      CU_TENSOR_MAP_SWIZZLE_128B);
-    if (rc) return rc;
-    switch (out_mode) {
-      case MSL_OUT_BF16: return launch_gemm_pair<6, MSL_OUT_BF16>(ta, tbp, args, st);
-      case MSL_OUT_F32: return launch_gemm_pair<6, MSL_OUT_F32>(ta, tbp, args, st);
-      case MSL_OUT_SWIGLU_BF16: return launch_gemm_pair<6, MSL_OUT_SWIGLU_BF16>(ta, tbp, args, st);
-      default: return MSL_ERR_ARG;
-    }
-  }
   // 256 x 256 tiles once there are enough rows to fill them and enough tiles to fill the GPU.
-  const char* wide_env = getenv("MSL_GEMM_WIDE");
   const bool wide = !narrow && m >= 512 && static_cast<int64_t>((m + 255) / 256) * ((n + 255) / 256) >= sm_count() &&
-                    !(wide_env && wide_env[0] == '0');
+                    option(MSL_OPT_GEMM_WIDE) != 0;
   switch (out_mode) {
     case MSL_OUT_BF16:
       if (wide) return launch_gemm<256, 3, MSL_OUT_BF16, 2>(ta, tb, args, st);
@@ -636,9 +407,8 @@ extern "C" int msl_gemm_bf16(const void* a, int64_t lda, const void* b, int64_t 
 extern "C" int msl_gemm_splitk_plan(int m, int n, int k, int segs, int out_mode) {
   if (m <= 0 || n <= 0 || k <= 0 || segs < 1 || out_mode == MSL_OUT_SWIGLU_BF16 || (n & 3)) return 1;
   // Slicing K changes the order of the fp32 sums, so a product's low bits then depend on how many rows
-  // it has; MSL_GEMM_SPLITK=0 keeps every product in one pass for hosts that need batch-invariant bits.
-  const char* env = getenv("MSL_GEMM_SPLITK");
-  if (env && env[0] == '0') return 1;
+  // it has; with the option off every product runs in one pass, for hosts that need batch-invariant bits.
+  if (option(MSL_OPT_GEMM_SPLITK) == 0) return 1;
   const bool narrow_n = n <= 128 || (n % 256 != 0 && n % 128 == 0);
   const int64_t tiles = static_cast<int64_t>((m + kBM - 1) / kBM) * ((n + (narrow_n ? 127 : 255)) / (narrow_n ? 128 : 256));
   const int k_blocks = ((k + kBK - 1) / kBK) * segs;

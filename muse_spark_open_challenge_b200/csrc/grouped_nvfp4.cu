@@ -24,9 +24,11 @@
 // Dequantisation without a table for the codes: a 4-bit code s|e1 e0|m placed at bf16 bits
 // 15|8 7|6 is the bf16 number value * 2^-126 (also for the subnormal codes 0 and 0.5); the block
 // scale is looked up as bf16(scale * 2^118); one bf16x2 multiply gives value * scale * 2^-8
-// exactly (at most 6 significant bits), and the 2^8 is folded into the epilogue scale.
-#include <cstdlib>
-
+// exactly (at most 6 significant bits), and the 2^8 is folded into the epilogue scale.  The idea of
+// decoding e2m1 by bit placement plus one bf16 multiply with a biased block scale comes from the
+// reference's experimental W4A16 kernel (tools/prefill/moe_kernel/moe_fp4.py:163-183); the bit layout
+// (moved into the load-time repack so three of four pairs need one shift and one mask), the arithmetic
+// scale decode and the table for special scale codes are this file's own.
 #include "msl_common.cuh"
 #include "msl_host.h"
 
@@ -46,16 +48,16 @@ constexpr int kGroupThreads = kProducers / kGroups;
 //   kWide    256 token rows (two 128-row MMAs per K step sharing one dequantised weight tile) x 256
 //            weight rows, 3 stages, one accumulator set (both sub-tiles fill the 512 TMEM columns).
 //            Halves the weight bytes staged, dequantised and fetched per FLOP.
-//   kPair    two CTAs of a cluster run one M=256 x N=256 MMA (cta_group::2): each CTA stages its own
-//            128 token rows and dequantises only its 128 of the tile's 256 weight rows.
-constexpr int kNarrow = 0, kPair = 1, kWide = 2;
+// (A third geometry, two CTAs of a cluster sharing one M=256 MMA with cta_group::2, each dequantising
+// half of the weight tile, was built and measured slower, 820 against 1012 TFLOP/s: not kept.)
+constexpr int kNarrow = 0, kWide = 2;
 template <int MODE>
 struct GroupedCfg {
-  static constexpr bool PAIR = MODE == kPair, WIDE = MODE == kWide;
+  static constexpr bool WIDE = MODE == kWide;
   static constexpr int kSubs = WIDE ? 2 : 1;                 // 128-row MMAs per K step in one CTA
-  static constexpr int kTileM = MODE == kNarrow ? 128 : 256; // token rows per tile
-  static constexpr int kBRows = PAIR ? 128 : 256;            // weight rows dequantised per CTA per stage
-  static constexpr int kStages = PAIR ? 6 : (WIDE ? 3 : 4);
+  static constexpr int kTileM = WIDE ? 256 : 128;            // token rows per tile
+  static constexpr int kBRows = 256;                         // weight rows dequantised per stage
+  static constexpr int kStages = WIDE ? 3 : 4;
   static constexpr int kRowsPerThread = kBRows / kGroupThreads;
   static constexpr int kSubBytes = kSubM * kGK * 2;
   static constexpr int kABytes = kSubs * kSubBytes;
@@ -75,22 +77,12 @@ struct GroupedArgs {
   const int* offsets;      // [groups + 1] slab row ranges
   void* out;
   int64_t ld_out;
+  int64_t slab_rows;       // rows of x and of out: no row at or beyond it is stored
   int experts, n, k;       // experts = row groups; n = padded weight rows (multiple of 256), k multiple of 64
   int wexperts;            // weight banks: group g uses bank g % wexperts
   int n_out;               // valid output columns (after the SwiGLU halving when fused)
   int swiglu;
   int* status;
-};
-
-// Scattered output (expert parallelism, the SCATTER instantiation only): row r of group g is stored to
-// bases[g / div] + index[r] * ld_out instead of out + r * ld_out.  The bases may point into other GPUs'
-// memory: the combine exchange then rides on this kernel's epilogue.  Kept out of GroupedArgs and out of
-// the default instantiation: with these three fields and one branch in the default epilogue the kernel
-// measured 4 % (gate/up) and 9 % (down) slower.
-struct ScatterArgs {
-  void* const* bases;
-  const int* index;
-  int div;
 };
 
 struct TileInfo {
@@ -152,17 +144,13 @@ __device__ __forceinline__ uint4 dequant8(uint32_t w, uint32_t scale2) {
   return make_uint4(o[0], o[1], o[2], o[3]);
 }
 
-template <bool SWIGLU, bool SCATTER>
-__device__ __forceinline__ void store_rows(const GroupedArgs& p, const ScatterArgs& sc, const TileInfo& ti,
-                                           uint32_t taddr, int r, float alpha) {
-  // One thread owns row r of the tile: 128 accumulator columns -> 128 (or 64 fused) outputs.
-  const bool valid = r < ti.rows;
+template <bool SWIGLU>
+__device__ __forceinline__ void store_rows(const GroupedArgs& p, const TileInfo& ti, uint32_t taddr, int r,
+                                           float alpha) {
+  // One thread owns row r of the tile: 128 accumulator columns -> 128 (or 64 fused) outputs.  Offsets
+  // that run past the slab (a routing that needs more rows than the buffers hold) store nothing.
+  const bool valid = r < ti.rows && static_cast<int64_t>(ti.row0) + r < p.slab_rows;
   __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<int64_t>(ti.row0 + r) * p.ld_out;
-  if constexpr (SCATTER) {
-    if (valid)
-      orow = reinterpret_cast<__nv_bfloat16*>(sc.bases[ti.expert / sc.div]) +
-             static_cast<int64_t>(sc.index[ti.row0 + r]) * p.ld_out;
-  }
   constexpr int kOutCols = SWIGLU ? kGN / 2 : kGN;
 #pragma unroll 1
   for (int c = 0; c < kOutCols; c += 32) {
@@ -196,11 +184,11 @@ __device__ __forceinline__ void store_rows(const GroupedArgs& p, const ScatterAr
   }
 }
 
-template <int MODE, bool SCATTER = false>
+template <int MODE>
 __global__ void __launch_bounds__(448, 1)
-grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p, ScatterArgs sc) {
+grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
   using S = GroupedCfg<MODE>;
-  constexpr bool PAIR = S::PAIR, WIDE = S::WIDE;
+  constexpr bool WIDE = S::WIDE;
   constexpr int kStages = S::kStages;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -217,9 +205,8 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p, Sc
   const int lane = threadIdx.x & 31;
   const int n_tiles = p.n / kGN;
   const int k_blocks = p.k / kGK;
-  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;        // 0 = the CTA that issues the MMAs
-  const int worker = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
-  const int n_workers = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+  const int worker = static_cast<int>(blockIdx.x);
+  const int n_workers = static_cast<int>(gridDim.x);
 
   // Scale table: e4m3 byte -> bf16(scale * 2^118) in both halves.  (0x7f / 0xff are NaN codes.)
   for (int i = threadIdx.x; i < 256; i += blockDim.x) {
@@ -248,27 +235,22 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p, Sc
     if (lane == 0) mt_prefix[p.experts] = carry;
   }
   if (threadIdx.x == 0) {
-    // full: one expect_tx arrival per CTA's TMA lane + the warps of one producer group per CTA
-    // (with PAIR both CTAs arrive on the leader's barrier); tmem_empty: 4 epilogue warps per CTA.
-    constexpr int kCtas = PAIR ? 2 : 1;
+    // full: one expect_tx arrival of the TMA lane + the warps of one producer group;
+    // tmem_empty: the 4 epilogue warps.
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(&full[s], kCtas * (1 + kGroupThreads / 32));
+      mbar_init(&full[s], 1 + kGroupThreads / 32);
       mbar_init(&empty[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tmem_full[a], 1);
-      mbar_init(&tmem_empty[a], kCtas * 4);
+      mbar_init(&tmem_empty[a], 4);
     }
     *abort_flag = 0;
     mbar_fence_init();
   }
-  if (warp == 1) {
-    if constexpr (PAIR) tmem_alloc_pair(tmem_base_slot, 2 * kGN);
-    else tmem_alloc(tmem_base_slot, 2 * kGN);
-  }
+  if (warp == 1) tmem_alloc(tmem_base_slot, 2 * kGN);
   tc_fence_before();
-  if constexpr (PAIR) cluster_sync_all();
-  else __syncthreads();
+  __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_slot;
   const int total_tiles = mt_prefix[p.experts] * n_tiles;
@@ -285,25 +267,19 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p, Sc
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1;
           if (*abort_flag || !mbar_wait(&empty[s], ph ^ 1)) { ok = false; break; }
-          if constexpr (PAIR) {
-            const uint32_t bar = map_to_cta(smem_u32(&full[s]), 0);
-            mbar_expect_tx_cluster(bar, S::kABytes);
-            tma_load_2d_pair(smem + s * S::kStageBytes, &tm_x, bar, kb * kGK, ti.row0 + rank * kSubM);
-          } else {
-            const int nsub = WIDE ? (ti.rows + kSubM - 1) / kSubM : 1;
-            mbar_expect_tx(&full[s], nsub * S::kSubBytes);
-            for (int sub = 0; sub < nsub; ++sub)
-              tma_load_2d(smem + s * S::kStageBytes + sub * S::kSubBytes, &tm_x, &full[s], kb * kGK,
-                          ti.row0 + sub * kSubM);
-          }
+          const int nsub = WIDE ? (ti.rows + kSubM - 1) / kSubM : 1;
+          mbar_expect_tx(&full[s], nsub * S::kSubBytes);
+          for (int sub = 0; sub < nsub; ++sub)
+            tma_load_2d(smem + s * S::kStageBytes + sub * S::kSubBytes, &tm_x, &full[s], kb * kGK,
+                        ti.row0 + sub * kSubM);
         }
       }
       if (!ok) { *abort_flag = 1; report_error(p.status, MSL_ERR_DEVICE_TIMEOUT); }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0 && rank == 0) {
-      constexpr uint32_t idesc = make_idesc(1, 1, PAIR ? 256 : 128, kGN);
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(1, 1, 128, kGN);
       uint32_t it = 0, tile_i = 0;
       bool ok = true;
       for (int g = worker; g < total_tiles && ok; g += n_workers, ++tile_i) {
@@ -327,36 +303,24 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p, Sc
 #pragma unroll
           for (int k16 = 0; k16 < kGK / 16; ++k16) {
             const uint64_t da = make_sdesc(sa + k16 * 32, 16, 1024, 2), db = make_sdesc(sb + k16 * 32, 16, 1024, 2);
-            if constexpr (PAIR) {
-              tc_mma_f16_pair(d_tmem, da, db, idesc, (kb | k16) != 0);
-            } else {
-              tc_mma_f16(d_tmem, da, db, idesc, (kb | k16) != 0);
-              if (WIDE && nsub > 1)
-                tc_mma_f16(d_tmem + kGN, make_sdesc(sa + S::kSubBytes + k16 * 32, 16, 1024, 2), db, idesc,
-                           (kb | k16) != 0);
-            }
+            tc_mma_f16(d_tmem, da, db, idesc, (kb | k16) != 0);
+            if (WIDE && nsub > 1)
+              tc_mma_f16(d_tmem + kGN, make_sdesc(sa + S::kSubBytes + k16 * 32, 16, 1024, 2), db, idesc,
+                         (kb | k16) != 0);
           }
-          if constexpr (PAIR) tc_commit_pair(&empty[s]);
-          else tc_commit(&empty[s]);
+          tc_commit(&empty[s]);
         }
-        if (ok) {
-          if constexpr (PAIR) tc_commit_pair(&tmem_full[acc]);
-          else tc_commit(&tmem_full[acc]);
-        }
+        if (ok) tc_commit(&tmem_full[acc]);
       }
       if (!ok) { *abort_flag = 1; report_error(p.status, MSL_ERR_DEVICE_TIMEOUT); }
     }
   } else if (warp < 6) {
-    // ------------------------------------------------------------ epilogue: this CTA's 128 rows
+    // ------------------------------------------------------------ epilogue
     const int quarter = warp & 3;
     uint32_t tile_i = 0;
     bool ok = true;
     for (int g = worker; g < total_tiles && ok; g += n_workers, ++tile_i) {
-      TileInfo ti = decode_tile(g, mt_prefix, p.offsets, p.experts, n_tiles, S::kTileM);
-      if constexpr (PAIR) {                                  // this CTA's 128 rows of the pair's tile
-        ti.row0 += rank * kSubM;
-        ti.rows = max(0, min(kSubM, ti.rows - static_cast<int>(rank) * kSubM));
-      }
+      const TileInfo ti = decode_tile(g, mt_prefix, p.offsets, p.experts, n_tiles, S::kTileM);
       const uint32_t acc = WIDE ? 0u : (tile_i & 1), acc_ph = WIDE ? (tile_i & 1) : ((tile_i >> 1) & 1);
       if (*abort_flag || !mbar_wait(&tmem_full[acc], acc_ph)) { ok = false; break; }
       tc_fence_after();
@@ -365,15 +329,12 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p, Sc
       for (int sub = 0; sub < nsub; ++sub) {
         const uint32_t taddr = tmem_base + (acc + sub) * kGN + (static_cast<uint32_t>(quarter * 32) << 16);
         const int r = sub * kSubM + quarter * 32 + lane;
-        if (p.swiglu) store_rows<true, false>(p, sc, ti, taddr, r, alpha);
-        else store_rows<false, SCATTER>(p, sc, ti, taddr, r, alpha);
+        if (p.swiglu) store_rows<true>(p, ti, taddr, r, alpha);
+        else store_rows<false>(p, ti, taddr, r, alpha);
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) {
-        if constexpr (PAIR) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[acc]), 0));
-        else mbar_arrive(&tmem_empty[acc]);
-      }
+      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
     }
     if (!ok && lane == 0) { *abort_flag = 1; report_error(p.status, MSL_ERR_DEVICE_TIMEOUT); }
   } else {
@@ -395,7 +356,7 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p, Sc
       if (c.g < total_tiles) {
         const TileInfo ti = decode_tile(c.g, mt_prefix, p.offsets, p.experts, n_tiles, S::kTileM);
         const int64_t tile_id = (static_cast<int64_t>(ti.expert % p.wexperts) * n_tiles + ti.nt) * k_blocks;
-        const int first_row = static_cast<int>(rank) * S::kBRows + tg;   // this CTA's rows of the 256-row tile
+        const int first_row = tg;
         c.wq = p.wq + tile_id * (kGN * 32) + first_row * 32;
         c.sf = p.sf + tile_id * (kGN * 4) + first_row * 4;
       }
@@ -453,10 +414,7 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p, Sc
         }
         fence_async_smem();
         __syncwarp();
-        if (lane == 0) {
-          if constexpr (PAIR) mbar_arrive_cluster(map_to_cta(smem_u32(&full[s]), 0));
-          else mbar_arrive(&full[s]);
-        }
+        if (lane == 0) mbar_arrive(&full[s]);
         it += kGroups;
         advance(cons, kGroups);
       }
@@ -467,18 +425,16 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p, Sc
   if (warp == 0 && lane == 0 && *abort_flag) drain_pause();
   tc_fence_before();
   __syncthreads();
-  if constexpr (PAIR) cluster_sync_all();    // neither CTA leaves while the other may still signal it
   if (warp == 1) {
     __syncwarp();
-    if constexpr (PAIR) tmem_dealloc_pair(tmem_base, 2 * kGN);
-    else tmem_dealloc(tmem_base, 2 * kGN);
+    tmem_dealloc(tmem_base, 2 * kGN);
   }
 }
 
 // ---------------------------------------------------------------------------- load-time re-tiling
 // src: codes [banks, rows, k/2] (element 2i in the low nibble of byte i), scales [banks, rows, k/16].
-// dst tiles of 128 rows x 64 k; with `interleave` (gate/up bank, rows = 2 * inter) tile j holds gate
-// rows [64 j, 64 j + 64) then up rows inter + [64 j, 64 j + 64).  Rows beyond the source are zero
+// dst tiles of 256 rows x 64 k; with `interleave` (gate/up bank, rows = 2 * inter) tile j holds gate
+// rows [128 j, 128 j + 128) then up rows inter + [128 j, 128 j + 128).  Rows beyond the source are zero
 // codes / zero scales.  Within each 32-bit word (8 consecutive k) the codes are re-placed bit by bit
 // as dequant8 expects.  Lossless: a permutation of the input bits.
 __device__ __forceinline__ uint32_t place_code(uint32_t code, int j) {
@@ -561,12 +517,25 @@ extern "C" int msl_nvfp4_repack(const void* src_codes, const void* src_scales, v
   return cudaGetLastError() == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
 }
 
-static int grouped_entry(const void* x, int64_t slab_rows, const void* codes, const void* scales,
-                         const float* global_scales, const int* offsets, void* out, int64_t ld_out, int experts,
-                         int weight_experts, int n_padded, int k, int n_out, int swiglu, void* const* scatter_bases,
-                         const int* scatter_index, int scatter_div, int* status, void* stream) {
+template <int MODE>
+static int launch_grouped(const CUtensorMap& tx, const GroupedArgs& a, int64_t slab_rows, int experts, int n_padded,
+                          cudaStream_t st) {
+  using S = GroupedCfg<MODE>;
+  const int smem = S::kTotal + 1024;
+  static SmemConfig config;
+  if (int rc = config.ensure(grouped_nvfp4_kernel<MODE>, smem)) return rc;
+  // Upper bound on tiles without reading the device counts: every group may add one partial tile.
+  const int64_t max_tiles = ((slab_rows + S::kTileM - 1) / S::kTileM + experts) * (n_padded / kGN);
+  const int grid = static_cast<int>(std::min<int64_t>(max_tiles, sm_count()));
+  grouped_nvfp4_kernel<MODE><<<grid, 448, smem, st>>>(tx, a);
+  return cudaGetLastError() == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
+}
+
+extern "C" int msl_grouped_gemm_nvfp4(const void* x, int64_t slab_rows, const void* codes, const void* scales,
+                                      const float* global_scales, const int* offsets, void* out, int64_t ld_out,
+                                      int experts, int weight_experts, int n_padded, int k, int n_out, int swiglu,
+                                      int* status, void* stream) {
   if (!x || !codes || !scales || !global_scales || !offsets || !out) return MSL_ERR_ARG;
-  if (scatter_bases != nullptr && (!scatter_index || scatter_div <= 0)) return MSL_ERR_ARG;
   if (experts <= 0 || experts > kMaxLocal || weight_experts <= 0 || n_padded <= 0 || k <= 0 || n_out <= 0 ||
       slab_rows < 0)
     return MSL_ERR_ARG;
@@ -579,95 +548,10 @@ static int grouped_entry(const void* x, int64_t slab_rows, const void* codes, co
                         kSubM, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc) return rc;
   GroupedArgs a{static_cast<const uint8_t*>(codes), static_cast<const uint8_t*>(scales), global_scales, offsets, out,
-                ld_out, experts, n_padded, k, weight_experts, n_out, swiglu, status};
-  const ScatterArgs sc{scatter_bases, scatter_index, scatter_div};
+                ld_out, slab_rows, experts, n_padded, k, weight_experts, n_out, swiglu, status};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const char* pair_env = getenv("MSL_GROUPED_PAIR");
-  const char* wide_env = getenv("MSL_GROUPED_WIDE");
-  // The CTA-pair variant (256-row tiles, each CTA dequantises half of the weight tile) is correct but
-  // measured slower than the single-CTA kernel here (820 vs 1012 TFLOP/s): opt-in only.
-  const bool use_pair = slab_rows >= 256LL * experts && pair_env && pair_env[0] == '1';
-  if (use_pair) {
-    using S = GroupedCfg<kPair>;
-    const int smem = S::kTotal + 1024;
-    static bool configured = false;
-    if (!configured) {
-      if (cudaFuncSetAttribute(grouped_nvfp4_kernel<kPair>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
-          cudaSuccess)
-        return MSL_ERR_CUDA;
-      configured = true;
-    }
-    const int64_t max_tiles = ((slab_rows + S::kTileM - 1) / S::kTileM + experts) * (n_padded / kGN);
-    const int pairs = static_cast<int>(std::min<int64_t>(max_tiles, sm_count() / 2));
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(2 * pairs);
-    cfg.blockDim = dim3(448);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    if (scatter_bases != nullptr) return MSL_ERR_UNSUPPORTED;
-    return cudaLaunchKernelEx(&cfg, grouped_nvfp4_kernel<kPair>, tx, a, sc) == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
-  }
   // 256-row tiles when the groups are large enough on average to fill them.
-  const bool use_wide = slab_rows >= 256LL * experts && !(wide_env && wide_env[0] == '0');
-  if (use_wide) {
-    using S = GroupedCfg<kWide>;
-    const int smem = S::kTotal + 1024;
-    static bool configured = false;
-    if (!configured) {
-      if (cudaFuncSetAttribute(grouped_nvfp4_kernel<kWide>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
-              cudaSuccess ||
-          cudaFuncSetAttribute(grouped_nvfp4_kernel<kWide, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
-              cudaSuccess)
-        return MSL_ERR_CUDA;
-      configured = true;
-    }
-    const int64_t max_tiles = ((slab_rows + S::kTileM - 1) / S::kTileM + experts) * (n_padded / kGN);
-    const int grid = static_cast<int>(std::min<int64_t>(max_tiles, sm_count()));
-    if (scatter_bases != nullptr) grouped_nvfp4_kernel<kWide, true><<<grid, 448, smem, st>>>(tx, a, sc);
-    else grouped_nvfp4_kernel<kWide><<<grid, 448, smem, st>>>(tx, a, sc);
-    return cudaGetLastError() == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
-  }
-  using S = GroupedCfg<kNarrow>;
-  const int smem = S::kTotal + 1024;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(grouped_nvfp4_kernel<kNarrow>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
-            cudaSuccess ||
-        cudaFuncSetAttribute(grouped_nvfp4_kernel<kNarrow, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
-            cudaSuccess)
-      return MSL_ERR_CUDA;
-    configured = true;
-  }
-  // Upper bound on tiles without reading the device counts: every group may add one partial tile.
-  const int64_t max_tiles = ((slab_rows + S::kTileM - 1) / S::kTileM + experts) * (n_padded / kGN);
-  const int grid = static_cast<int>(std::min<int64_t>(max_tiles, sm_count()));
-  if (scatter_bases != nullptr) grouped_nvfp4_kernel<kNarrow, true><<<grid, 448, smem, st>>>(tx, a, sc);
-  else grouped_nvfp4_kernel<kNarrow><<<grid, 448, smem, st>>>(tx, a, sc);
-  return cudaGetLastError() == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
-}
-
-extern "C" int msl_grouped_gemm_nvfp4(const void* x, int64_t slab_rows, const void* codes, const void* scales,
-                                      const float* global_scales, const int* offsets, void* out, int64_t ld_out,
-                                      int experts, int weight_experts, int n_padded, int k, int n_out, int swiglu,
-                                      int* status, void* stream) {
-  return grouped_entry(x, slab_rows, codes, scales, global_scales, offsets, out, ld_out, experts, weight_experts,
-                       n_padded, k, n_out, swiglu, nullptr, nullptr, 1, status, stream);
-}
-
-extern "C" int msl_grouped_gemm_nvfp4_scatter(const void* x, int64_t slab_rows, const void* codes, const void* scales,
-                                              const float* global_scales, const int* offsets, int64_t ld_out,
-                                              int experts, int weight_experts, int n_padded, int k, int n_out,
-                                              void* const* scatter_bases, const int* scatter_index, int scatter_div,
-                                              int* status, void* stream) {
-  if (!scatter_bases) return MSL_ERR_ARG;
-  // `out` is unused when every row is scattered; x stands in so that the common checks pass
-  return grouped_entry(x, slab_rows, codes, scales, global_scales, offsets, const_cast<void*>(x), ld_out, experts,
-                       weight_experts, n_padded, k, n_out, 0, scatter_bases, scatter_index, scatter_div, status, stream);
+  const bool use_wide = slab_rows >= 256LL * experts && option(MSL_OPT_GROUPED_WIDE) != 0;
+  return use_wide ? launch_grouped<kWide>(tx, a, slab_rows, experts, n_padded, st)
+                  : launch_grouped<kNarrow>(tx, a, slab_rows, experts, n_padded, st);
 }

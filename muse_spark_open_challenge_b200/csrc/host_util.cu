@@ -1,7 +1,8 @@
 // Host utilities: driver entry point lookup for cuTensorMapEncodeTiled, device property cache,
-// status strings.
+// run-time options, status strings.
 #include <cudaTypedefs.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "msl_host.h"
@@ -31,6 +32,26 @@ int sm_count() {
     cached[dev] = n;
   }
   return cached[dev];
+}
+
+// Run-time options.  Their defaults are taken from the environment exactly once (the first look-up), so
+// what a later launch does never depends on an environment change made in between; msl_set_option is the
+// way to change one afterwards.
+static std::atomic<int> g_options[MSL_OPT_COUNT];
+static void init_options() {
+  static std::once_flag once;
+  std::call_once(once, [] {
+    static const char* const names[MSL_OPT_COUNT] = {"MSL_GEMM_SPLITK", "MSL_GEMM_WIDE", "MSL_GROUPED_WIDE"};
+    for (int i = 0; i < MSL_OPT_COUNT; ++i) {
+      const char* env = getenv(names[i]);
+      g_options[i].store(env && env[0] == '0' ? 0 : 1, std::memory_order_relaxed);
+    }
+  });
+}
+int option(int which) {
+  if (which < 0 || which >= MSL_OPT_COUNT) return 0;
+  init_options();
+  return g_options[which].load(std::memory_order_relaxed);
 }
 
 int make_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dtype, int elem_bytes, uint64_t cols,
@@ -79,3 +100,15 @@ extern "C" const char* msl_status_string(int code) {
 }
 
 extern "C" int msl_abi_version(void) { return MSL_ABI_VERSION; }
+
+extern "C" int msl_set_option(int option, int value) {
+  if (option < 0 || option >= MSL_OPT_COUNT || (value != 0 && value != 1)) return MSL_ERR_ARG;
+  msl::init_options();
+  msl::g_options[option].store(value, std::memory_order_relaxed);
+  return MSL_OK;
+}
+
+extern "C" int msl_get_option(int option) {
+  if (option < 0 || option >= MSL_OPT_COUNT) return MSL_ERR_ARG;
+  return msl::option(option);
+}

@@ -103,7 +103,6 @@ class ExpertParallel:
         self.cap = 0
         self.recv_x = self.recv_i = None
         self.peer = None                       # set by enable_peer
-        self.push = False
         self.side = torch.cuda.Stream(st["device"]) if torch.device(st["device"]).type == "cuda" else None
 
     def buffers(self, st, rows):
@@ -117,60 +116,60 @@ class ExpertParallel:
 
 class PeerSlabs:
     """Peer-mapped memory of one rank, allocated as symmetric memory and exchanged once: a bf16
-    [cap, width] row slab (what the other ranks dispatch into), the barrier's flag words, an i32 [cap]
-    return index (for every slab row, where its owner wants the output row back) and a bf16
-    [ret_rows, width] return buffer (where the other ranks' down projections store this rank's output
-    rows); plus the device arrays of every rank's pointers to each of them."""
+    [cap, width] row slab (what the other ranks dispatch into and read expert outputs from) followed by
+    `guard_rows` rows that nothing may touch (the tests check them) and the barrier's flag words; plus
+    the device arrays of every rank's pointers to the slab and to the flag words."""
 
     FLAG_BYTES = 4096
 
-    def __init__(self, ctx: "ExpertParallel", st: dict, cap: int, ret_rows: int = 0):
-        import torch.distributed._symmetric_memory as symm
-
-        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # plain peer loads/stores only
+    def __init__(self, ctx: "ExpertParallel", st: dict, cap: int, guard_rows: int = 0):
         dev = torch.device(st["device"])
         width = st["moe_width"]
         slab_bytes = cap * width * 2
-        index_at = slab_bytes + self.FLAG_BYTES
-        ret_at = index_at + (cap * 4 + 255) // 256 * 256
-        self.raw = symm.empty(ret_at + ret_rows * width * 2, dtype=torch.uint8, device=dev)
-        self.raw.zero_()
-        group = ctx.group if ctx.group is not None else dist.group.WORLD
-        self.handle = symm.rendezvous(self.raw, group)
-        bases = [int(p) for p in self.handle.buffer_ptrs]
+        guard_bytes = guard_rows * width * 2
+        flags_at = slab_bytes + guard_bytes
+        if ctx.world > 1:
+            import torch.distributed._symmetric_memory as symm
+
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # plain peer loads/stores only
+            self.raw = symm.empty(flags_at + self.FLAG_BYTES, dtype=torch.uint8, device=dev)
+            self.raw.zero_()
+            group = ctx.group if ctx.group is not None else dist.group.WORLD
+            self.handle = symm.rendezvous(self.raw, group)
+            bases = [int(p) for p in self.handle.buffer_ptrs]
+        else:                                  # a single rank is its own and only peer: ordinary memory will do
+            self.raw = torch.zeros(flags_at + self.FLAG_BYTES, dtype=torch.uint8, device=dev)
+            bases = [self.raw.data_ptr()]
         self.slab = self.raw[:slab_bytes].view(torch.bfloat16).view(cap, width)
+        self.guard = self.raw[slab_bytes:flags_at]
+        self.flags = self.raw[flags_at:flags_at + self.FLAG_BYTES].view(torch.int32)
         self.slab_ptrs = torch.tensor(bases, dtype=torch.int64, device=dev)
-        self.flag_ptrs = torch.tensor([b + slab_bytes for b in bases], dtype=torch.int64, device=dev)
-        self.ret_index = self.raw[index_at:index_at + cap * 4].view(torch.int32)
-        self.index_ptrs = torch.tensor([b + index_at for b in bases], dtype=torch.int64, device=dev)
-        self.ret_rows = ret_rows
-        if ret_rows:
-            self.ret = self.raw[ret_at:].view(torch.bfloat16).view(ret_rows, width)
-            self.ret_ptrs = torch.tensor([b + ret_at for b in bases], dtype=torch.int64, device=dev)
+        self.flag_ptrs = torch.tensor([b + flags_at for b in bases], dtype=torch.int64, device=dev)
         self.cap = cap
         torch.cuda.synchronize(dev)
-        dist.barrier(group=ctx.group)          # every rank's flag words are zero before the first barrier
+        if ctx.world > 1:
+            dist.barrier(group=ctx.group)      # every rank's flag words are zero before the first barrier
 
 
 def enable_peer(ctx: "ExpertParallel", st: dict, max_tokens: int, top_k: int, capacity_factor: float = 2.0,
-                push: bool = False):
+                cap_rows: int = None, guard_rows: int = 0):
     """Switch `ctx` to the peer-memory transport.  Every rank's slab holds up to
     capacity_factor * max_tokens * top_k rows (never more than the worst case world * max_tokens *
-    top_k); a layer whose routing needs more sets MSL_ERR_CAPACITY in the status word.  By default the
-    combine kernel loads the expert outputs from the owners' slabs.  With `push` the down projection
-    stores every output row straight into the token owner's return buffer instead (the exchange rides
-    on the GEMM's epilogue): correct, but its 64-byte stores cross NVLink at a fraction of the link rate
-    (down projection 1.9 -> 5.7 ms on two GPUs), so it is opt-in."""
+    top_k; `cap_rows` sets the size directly); a layer whose routing needs more sets MSL_ERR_CAPACITY in
+    the status word, the rows that do not fit are dropped, and no kernel addresses a row at or beyond
+    the capacity.  The combine kernel loads the expert outputs from the owners' slabs.  (Returning
+    the outputs from the down projection's epilogue instead, 64-byte stores over NVLink, was built and
+    measured three times slower: 5.7 against 1.9 ms on two GPUs.  Not kept.)"""
     dev = st["device"]
     most = torch.tensor([max_tokens], dtype=torch.int64, device=dev)
-    dist.all_reduce(most, op=dist.ReduceOp.MAX, group=ctx.group)       # slabs have one size on every rank
-    cap = int(min(ctx.world, capacity_factor) * int(most.item()) * top_k)
+    if ctx.world > 1:
+        dist.all_reduce(most, op=dist.ReduceOp.MAX, group=ctx.group)   # slabs have one size on every rank
+    cap = int(min(ctx.world, capacity_factor) * int(most.item()) * top_k) if cap_rows is None else int(cap_rows)
     cap = (cap + 255) // 256 * 256
-    most_tokens = int(most.item())
-    ctx.peer = PeerSlabs(ctx, st, cap, most_tokens * top_k if push else 0)
-    ctx.push = push
-    ctx.ident = torch.arange(most_tokens * top_k, dtype=torch.int32, device=dev).view(most_tokens, top_k)
-    ctx.recv_i = torch.empty((cap, st["inter"]), dtype=torch.bfloat16, device=dev)
+    ctx.peer = PeerSlabs(ctx, st, cap, guard_rows)
+    # the intermediate slab carries the same number of guard rows behind it
+    ctx.recv_i_raw = torch.zeros((cap + guard_rows, st["inter"]), dtype=torch.bfloat16, device=dev)
+    ctx.recv_i = ctx.recv_i_raw[:cap]
     ctx.counts_all = torch.zeros((ctx.world, ctx.n_experts), dtype=torch.int32, device=dev)
     ctx.dest_base = torch.zeros(ctx.n_experts, dtype=torch.int32, device=dev)
     ctx.group_offsets = torch.zeros(ctx.n_experts + 1, dtype=torch.int32, device=dev)
@@ -196,19 +195,21 @@ def moe_stage_peer(h, data, st, ctx: ExpertParallel):
     if fork:
         ctx.side.wait_stream(main)
     with torch.cuda.stream(ctx.side if fork else main):
-        dist.all_gather_into_tensor(ctx.counts_all.view(-1), ctx.counts, group=ctx.group)
+        if ctx.world > 1:
+            dist.all_gather_into_tensor(ctx.counts_all.view(-1), ctx.counts, group=ctx.group)
+        else:
+            ctx.counts_all.view(-1).copy_(ctx.counts)
         ops.ep_plan(ctx.counts_all, ctx.rank, peer.cap, ctx.dest_base, ctx.group_offsets, status)
         # every rank has finished reading this rank's slab (the previous layer's combine) before new rows land
         ops.peer_barrier(peer.flag_ptrs.data_ptr(), ctx.rank, ctx.world, status)
         layer._mark(st, "plan")
-        index_bases = peer.index_ptrs.data_ptr() if ctx.push else 0
         if st["pooled"]:
             p = ops.gemm(h, st["pooler"], status=status)
             rowmap = ops.dispatch_peer(p, st["w_pre_exp"], ids, slots, ctx.dest_base, peer.slab_ptrs.data_ptr(),
-                                       local, peer.cap, index_bases=index_bases)
+                                       local, peer.cap)
         else:
             rowmap = ops.dispatch_peer(h, None, ids, slots, ctx.dest_base, peer.slab_ptrs.data_ptr(), local,
-                                       peer.cap, index_bases=index_bases)
+                                       peer.cap)
         layer._mark(st, "dispatch")
     shared = None
     if st["shared"]:                           # also absorbs the skew between ranks ahead of the barrier
@@ -223,24 +224,14 @@ def moe_stage_peer(h, data, st, ctx: ExpertParallel):
     ops.grouped_gemm_nvfp4(peer.slab, st["w13_q"], st["w13_s"], st["w13_gs"], ctx.group_offsets, ctx.recv_i,
                            st["inter"], True, status)
     layer._mark(st, "experts_gate_up")
-    if ctx.push:
-        # every output row goes straight to the return buffer of the rank that owns its token
-        ops.grouped_gemm_nvfp4_scatter(ctx.recv_i, st["w2_q"], st["w2_s"], st["w2_gs"], ctx.group_offsets,
-                                       st["moe_width"], peer.ret_ptrs.data_ptr(), peer.ret_index, local, status)
-    else:
-        ops.grouped_gemm_nvfp4(ctx.recv_i, st["w2_q"], st["w2_s"], st["w2_gs"], ctx.group_offsets, peer.slab,
-                               st["moe_width"], False, status)
+    ops.grouped_gemm_nvfp4(ctx.recv_i, st["w2_q"], st["w2_s"], st["w2_gs"], ctx.group_offsets, peer.slab,
+                           st["moe_width"], False, status)
     layer._mark(st, "experts_down")
     st["offsets"][-1:] = ctx.group_offsets[-1:]             # rows computed on this rank (for the bench's FLOP count)
     ops.peer_barrier(peer.flag_ptrs.data_ptr(), ctx.rank, ctx.world, status)      # all expert outputs are written
     layer._mark(st, "barrier_outputs")
-    if ctx.push:
-        tokens = h.shape[0]
-        back = torch.where(rowmap >= 0, ctx.ident[:tokens], rowmap)              # a route without a slab row has none
-        moe = ops.combine(peer.ret[:tokens * top_k], back, tw, st["w_post_exp"], addend=shared)
-    else:
-        moe = ops.combine_peer(peer.slab_ptrs.data_ptr(), peer.cap, st["moe_width"], rowmap, tw, st["w_post_exp"],
-                               addend=shared)
+    moe = ops.combine_peer(peer.slab_ptrs.data_ptr(), peer.cap, st["moe_width"], rowmap, tw, st["w_post_exp"],
+                           addend=shared)
     layer._mark(st, "combine")
     if st["pooled"]:
         moe = layer.unpool(moe, st)
@@ -297,7 +288,7 @@ def moe_stage(h, data, st, ctx: ExpertParallel):
     exchange_rows(recv_x[:plan.recv_rows], tokens * top_k, plan.recv_splits, plan.send_splits, out=send_x,
                   group=ctx.group)
     layer._mark(st, "a2a_combine")
-    moe = ops.combine(send_x, rowmap, tw, st["w_post_exp"], addend=shared)
+    moe = ops.combine(send_x, rowmap, tw, st["w_post_exp"], addend=shared, status=status)
     layer._mark(st, "combine")
     if st["pooled"]:
         moe = layer.unpool(moe, st)
@@ -331,8 +322,31 @@ class ChunkedSequence:
             seen[o] += self.lens[p]
         self.row_bytes = hkv * head_dim
         most = max(seen)
+        self.most = most
         self.send = torch.empty((2, most, self.row_bytes), dtype=torch.uint8, device=device)
         self.recv = torch.empty((self.world, 2, most, self.row_bytes), dtype=torch.uint8, device=device)
+        self._plans = {}
+
+    def plan(self, page: int):
+        """Index tensors of the hand-off, which depend on the sizes only and are built once per page
+        size: for each of this rank's requests with a cached context, (page number and offset in the
+        page of every context position, and for K and V the row of the receive buffer - viewed as
+        [world * 2 * most, row_bytes] - that holds that position's row)."""
+        if page not in self._plans:
+            dev = self.recv.device
+            out = []
+            for p in self.mine:
+                ctx_len = self.starts[p]
+                if ctx_len == 0:
+                    out.append(None)
+                    continue
+                pos = torch.arange(ctx_len, device=dev)
+                src = [torch.cat([(self.owners[q] * 2 + which) * self.most + self.offset_in_owner[q]
+                                  + torch.arange(self.lens[q], device=dev) for q in range(p)])
+                       for which in range(2)]
+                out.append((pos // page, pos % page, src[0], src[1]))
+            self._plans[page] = out
+        return self._plans[page]
 
 
 def zigzag_owners(ranks: int):
@@ -351,19 +365,20 @@ def kv_handoff(data: dict, st: dict, seq: ChunkedSequence):
     caches = [data[k].view(torch.uint8).view(-1, seq.row_bytes) for k in ("k_cache", "v_cache")]
     for which, cache in enumerate(caches):
         ops.kv_rows_copy(cache, seq.send[which], n_mine, src_idx=data["cache_loc"], status=st["status"])
-    dist.all_gather_into_tensor(seq.recv.view(-1), seq.send.view(-1), group=seq.group)
+    if seq.world > 1:
+        dist.all_gather_into_tensor(seq.recv.view(-1), seq.send.view(-1), group=seq.group)
+    else:
+        seq.recv.view(-1).copy_(seq.send.view(-1))         # every piece runs on this rank
     page = cfg["page_size"]
-    for b, p in enumerate(seq.mine):
-        ctx_len = seq.starts[p]
-        if ctx_len == 0:
+    recv_rows = seq.recv.view(-1, seq.row_bytes)
+    for b, plan in enumerate(seq.plan(page)):
+        if plan is None:
             continue
-        pos = torch.arange(ctx_len, device=caches[0].device)
-        prefix_loc = data["page_table"][b].long()[pos // page] * page + pos % page
-        for q in range(p):
-            idx = prefix_loc[seq.starts[q]:seq.starts[q] + seq.lens[q]]
-            rows = seq.recv[seq.owners[q]][:, seq.offset_in_owner[q]:seq.offset_in_owner[q] + seq.lens[q]]
-            for which, cache in enumerate(caches):
-                ops.kv_rows_copy(rows[which], cache, seq.lens[q], dst_idx=idx, status=st["status"])
+        page_no, page_off, src_k, src_v = plan
+        # where the request's page table puts positions 0 .. ctx-1 (the only data-dependent part)
+        prefix_loc = data["page_table"][b].long()[page_no] * page + page_off
+        for src, cache in zip((src_k, src_v), caches):
+            ops.kv_rows_copy(recv_rows, cache, prefix_loc.numel(), src_idx=src, dst_idx=prefix_loc, status=st["status"])
 
 
 def kernel_fn(data: dict, st: dict, ctx: ExpertParallel, seq: ChunkedSequence = None):

@@ -67,7 +67,8 @@ def prepare(weights: dict) -> dict:
             raise MslError("a shared expert together with pooler/unpooler is not supported")
         st["shared_w13"] = ops.interleave_gate_up(weights["shared_w13"])
         st["shared_w2"] = weights["shared_w2"].contiguous()
-    st["counts"] = torch.zeros(el, dtype=torch.int32, device=dev)
+    st["counts"] = torch.zeros(el, dtype=torch.int32, device=dev)     # zero between launches (the kernel re-zeroes)
+    st["sync"] = torch.zeros(2, dtype=torch.int32, device=dev)        # grid-barrier words of the routing kernel
     st["offsets"] = torch.zeros(el + 1, dtype=torch.int32, device=dev)
     st["status"] = torch.zeros(1, dtype=torch.int32, device=dev)
     st["inv_freq"] = {}
@@ -139,17 +140,13 @@ def attention_stage(data, st, after_store=None):
     return out
 
 
-def _route(h, data, st, top_k):
-    """Router logits (BF16 hi + lo product, fp32 out), top-k, weights, per-expert slots."""
+def _router_logits(h, st):
+    """Router logits as a BF16 hi + lo product with fp32 output (TASK.md:88 allows the split)."""
     hidden = h.shape[1]
     logits = ops.gemm(h, st["router_hilo"], out_mode=OUT_F32, k=hidden, segs=2, a_seg_stride=0, b_seg_stride=hidden,
                       status=st["status"])
     _mark(st, "gemm_router")
-    st["counts"].zero_()
-    routed = ops.route_topk(logits, st["router_bias"], ROUTER_MULTIPLIER, data["local_start"], st["n_experts"], top_k,
-                            st["n_local"], st["counts"])
-    _mark(st, "route_topk")
-    return routed
+    return logits
 
 
 def _shared_expert(h, st):
@@ -159,14 +156,17 @@ def _shared_expert(h, st):
     return shared
 
 
-def moe_stage(h, data, st):
+def moe_stage(h, data, st, boundary_stream=None):
     """Router, dispatch, routed experts (+ shared expert), weighted combine, unpooler.
     h: bf16 [T, H], the FFN input.  Returns (FFN branch bf16 [T, H], expert ids i32 [T, K]).
+    With `boundary_stream` (the fp32 residual stream entering the FFN boundary; layers without an
+    unpooler only) the weighted combine and the FFN boundary run as one kernel and the first result
+    is (stream_out fp32, hidden bf16) instead.
 
-    The routing chain (router GEMM, top-k, and without a pooler the dispatch) runs on a side stream
-    next to the dense GEMM that does not depend on it (shared expert, or pooler), as the reference
-    forks its router (submission.py:1105-1117); fork and join are stream waits, so the call stays
-    capturable.  With per-stage timing marks enabled everything runs on one stream."""
+    The router product runs on a side stream next to the dense GEMM that does not depend on it
+    (shared expert, or pooler), as the reference forks its router (submission.py:1105-1117); fork and
+    join are stream waits, so the call stays capturable.  Top-k, slot assignment and dispatch are one
+    kernel.  With per-stage timing marks enabled everything runs on one stream."""
     cfg = data["config"]
     top_k, status = cfg["top_k"], st["status"]
     tokens = h.shape[0]
@@ -174,14 +174,20 @@ def moe_stage(h, data, st):
     overlap = st.get("marks") is None
     main = torch.cuda.current_stream()
     side = st["side"] if overlap else main
+
+    def route_dispatch(x, norm_w, logits):
+        out = ops.route_dispatch(logits, st["router_bias"], ROUTER_MULTIPLIER, data["local_start"], st["n_experts"],
+                                 top_k, st["n_local"], x, norm_w, slab_x, st["offsets"], st["counts"], st["sync"],
+                                 status)
+        _mark(st, "route_dispatch")
+        return out
+
     if overlap:
         side.wait_stream(main)
     with torch.cuda.stream(side):
-        ids, tw, local_ids, slots = _route(h, data, st, top_k)
-        rowmap = None
+        logits = _router_logits(h, st)
         if not st["pooled"]:
-            rowmap = ops.dispatch(h, None, local_ids, slots, st["counts"], slab_x, st["offsets"], status)
-            _mark(st, "dispatch")
+            ids, tw, rowmap = route_dispatch(h, None, logits)
     shared = None
     if st["pooled"]:
         p = ops.gemm(h, st["pooler"], status=status)
@@ -190,18 +196,24 @@ def moe_stage(h, data, st):
         shared = _shared_expert(h, st)
     if overlap:
         main.wait_stream(side)
-        for t in (ids, tw, local_ids, slots) + ((rowmap,) if rowmap is not None else ()):
-            t.record_stream(main)          # allocated on the side stream, read on the main one
+        logits.record_stream(main)             # allocated on the side stream, read (or freed) on the main one
     if st["pooled"]:
-        rowmap = ops.dispatch(p, st["w_pre_exp"], local_ids, slots, st["counts"], slab_x, st["offsets"], status)
-        _mark(st, "dispatch")
+        ids, tw, rowmap = route_dispatch(p, st["w_pre_exp"], logits)
+    elif overlap:
+        for t in (ids, tw, rowmap):
+            t.record_stream(main)
     ops.grouped_gemm_nvfp4(slab_x, st["w13_q"], st["w13_s"], st["w13_gs"], st["offsets"], slab_i, st["inter"], True,
                            status)
     _mark(st, "experts_gate_up")
     ops.grouped_gemm_nvfp4(slab_i, st["w2_q"], st["w2_s"], st["w2_gs"], st["offsets"], slab_x, st["moe_width"],
                            False, status)
     _mark(st, "experts_down")
-    moe = ops.combine(slab_x, rowmap, tw, st["w_post_exp"], addend=shared)
+    if boundary_stream is not None and not st["pooled"]:
+        out = ops.combine_boundary(slab_x, rowmap, tw, st["w_post_exp"], shared, st["w_post_ffn"], boundary_stream,
+                                   st["a2"], st["b2"], st["w_next"], POST_NORM_EPS, RMS_EPS, status)
+        _mark(st, "combine_boundary_ffn")
+        return out, ids
+    moe = ops.combine(slab_x, rowmap, tw, st["w_post_exp"], addend=shared, status=status)
     _mark(st, "combine")
     if st["pooled"]:
         moe = unpool(moe, st)
@@ -234,6 +246,9 @@ def kernel_fn(data: dict, st: dict):
     _mark(st, "gemm_o")
     s1, h = ops.boundary(a, None, data["stream"], st["a1"], st["b1"], st["w_pre_ffn"], POST_NORM_EPS, RMS_EPS)
     _mark(st, "boundary_attn")
+    if not st["pooled"]:                       # combine and FFN boundary as one kernel
+        (s2, hidden), ids = moe_stage(h, data, st, boundary_stream=s1)
+        return hidden, s2, ids
     f, ids = moe_stage(h, data, st)
     s2, hidden = ops.boundary(f, st["w_post_ffn"], s1, st["a2"], st["b2"], st["w_next"], POST_NORM_EPS, RMS_EPS)
     _mark(st, "boundary_ffn")

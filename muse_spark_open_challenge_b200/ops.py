@@ -146,7 +146,30 @@ def dispatch(x, norm_w, local_ids, slots, counts, slab, offsets, status=None):
     return rowmap
 
 
-def combine(y, rowmap, weights, post_w, addend=None, out=None):
+def route_dispatch(logits, bias, multiplier, local_start, n_experts, top_k, n_local, x, norm_w, slab, offsets, counts,
+                   sync, status=None, hilo=False):
+    """`route_topk` and `dispatch` as one launch.  Returns (ids, weights, rowmap); fills `slab` and
+    `offsets`.  `counts` i32 [n_local] and `sync` i32 [2] must be zero on entry and are zero again when
+    the kernel ends (the counts of the call are the differences of `offsets`)."""
+    _need(logits, torch.float32, "logits"), _need(bias, torch.float32, "bias"), _need(counts, torch.int32, "counts")
+    _need(local_start, torch.int32, "local_start"), _need(x, torch.bfloat16, "x"), _need(slab, torch.bfloat16, "slab")
+    _need(offsets, torch.int32, "offsets"), _need(sync, torch.int32, "sync")
+    t, dev = logits.shape[0], logits.device
+    ids = torch.empty((t, top_k), dtype=torch.int32, device=dev)
+    weights = torch.empty((t, top_k), dtype=torch.float32, device=dev)
+    scratch = torch.empty((2, t, top_k), dtype=torch.int32, device=dev)          # local ids, slots
+    rowmap = torch.empty((t, top_k), dtype=torch.int32, device=dev)
+    check(_lib.lib().msl_route_dispatch(logits.data_ptr(), _rows(logits, "logits"), int(hilo), bias.data_ptr(),
+                                        float(multiplier), local_start.data_ptr(), x.data_ptr(), _rows(x, "x"),
+                                        _ptr(norm_w), t, n_experts, top_k, n_local, slab.shape[1], ids.data_ptr(),
+                                        weights.data_ptr(), scratch[0].data_ptr(), scratch[1].data_ptr(),
+                                        counts.data_ptr(), sync.data_ptr(), slab.data_ptr(), slab.shape[0],
+                                        rowmap.data_ptr(), offsets.data_ptr(), _ptr(status), _stream()),
+          "msl_route_dispatch")
+    return ids, weights, rowmap
+
+
+def combine(y, rowmap, weights, post_w, addend=None, out=None, status=None):
     """bf16 [T, width] = sum_j w_j * rms(y[rowmap_j] * post_w, 1e-8) (+ addend)."""
     _need(y, torch.bfloat16, "y"), _need(rowmap, torch.int32, "rowmap"), _need(weights, torch.float32, "weights")
     t, top_k = rowmap.shape
@@ -155,8 +178,29 @@ def combine(y, rowmap, weights, post_w, addend=None, out=None):
         out = torch.empty((t, width), dtype=torch.bfloat16, device=y.device)
     check(_lib.lib().msl_combine(y.data_ptr(), rowmap.data_ptr(), weights.data_ptr(), post_w.data_ptr(), _ptr(addend),
                                  0 if addend is None else _rows(addend, "addend"), out.data_ptr(), _rows(out, "out"),
-                                 t, top_k, width, _stream()), "msl_combine")
+                                 t, top_k, width, _ptr(status), _stream()), "msl_combine")
     return out
+
+
+def combine_boundary(y, rowmap, weights, post_w, addend, branch_scale, stream_in, alpha, beta, norm_w,
+                     eps_branch=1e-8, eps_out=1e-5, status=None):
+    """`combine` followed by `boundary` in one kernel (the combined row never leaves the registers).
+    Returns (stream_out fp32 [T, H], hidden bf16 [T, H]); y's width must be the hidden size."""
+    _need(y, torch.bfloat16, "y"), _need(rowmap, torch.int32, "rowmap"), _need(weights, torch.float32, "weights")
+    _need(stream_in, torch.float32, "stream_in")
+    t, top_k = rowmap.shape
+    width = y.shape[1]
+    if stream_in.shape != (t, width) or not stream_in.is_contiguous():
+        raise MslError("combine_boundary: stream_in must be a contiguous [tokens, width] tensor")
+    s_out = torch.empty_like(stream_in)
+    hid = torch.empty((t, width), dtype=torch.bfloat16, device=y.device)
+    check(_lib.lib().msl_combine_boundary(y.data_ptr(), rowmap.data_ptr(), weights.data_ptr(), post_w.data_ptr(),
+                                          _ptr(addend), 0 if addend is None else _rows(addend, "addend"), t, top_k,
+                                          width, _ptr(branch_scale), stream_in.data_ptr(), alpha.data_ptr(),
+                                          beta.data_ptr(), norm_w.data_ptr(), s_out.data_ptr(), hid.data_ptr(), width,
+                                          float(eps_branch), float(eps_out), _ptr(status), _stream()),
+          "msl_combine_boundary")
+    return s_out, hid
 
 
 def ep_plan(counts_all, rank, cap, dest_base, group_offsets, status):
@@ -174,17 +218,16 @@ def peer_barrier(flag_bases, rank, world, status, timeout_ms=20000):
           "msl_peer_barrier")
 
 
-def dispatch_peer(x, norm_w, ids, slots, dest_base, peer_bases, local_experts, cap, rowmap=None, index_bases=0):
+def dispatch_peer(x, norm_w, ids, slots, dest_base, peer_bases, local_experts, cap, rowmap=None):
     """Token rows written straight into the owning ranks' slabs (peer_bases: device array of slab
-    pointers, one per rank); with index_bases (device array of the ranks' i32 [cap] arrays) the owner
-    also learns the return row t * top_k + j of every slab row."""
+    pointers, one per rank)."""
     _need(x, torch.bfloat16, "x"), _need(ids, torch.int32, "ids"), _need(slots, torch.int32, "slots")
     t, top_k = ids.shape
     if rowmap is None:
         rowmap = torch.empty((t, top_k), dtype=torch.int32, device=x.device)
     check(_lib.lib().msl_dispatch_peer(x.data_ptr(), _rows(x, "x"), _ptr(norm_w), ids.data_ptr(), slots.data_ptr(),
                                        dest_base.data_ptr(), int(peer_bases), local_experts, cap, t, top_k,
-                                       x.shape[1], rowmap.data_ptr(), int(index_bases) or None, _stream()),
+                                       x.shape[1], rowmap.data_ptr(), _stream()),
           "msl_dispatch_peer")
     return rowmap
 
@@ -243,21 +286,6 @@ def grouped_gemm_nvfp4(x, codes_t, scales_t, global_scales, offsets, out, n_out,
                                             n_out, int(swiglu),
                                             _ptr(status), _stream()), "msl_grouped_gemm_nvfp4")
     return out
-
-
-def grouped_gemm_nvfp4_scatter(x, codes_t, scales_t, global_scales, offsets, n_out, scatter_bases, scatter_index,
-                               scatter_div, status=None):
-    """The grouped GEMM with every output row stored to scatter_bases[g // scatter_div] +
-    scatter_index[r] * n_out (device array of row-buffer pointers, possibly other GPUs' memory)."""
-    _need(x, torch.bfloat16, "x"), _need(offsets, torch.int32, "offsets"), _need(scatter_index, torch.int32, "index")
-    e, n_tiles, k_blocks = codes_t.shape[:3]
-    if not x.is_contiguous():
-        raise MslError("x must be contiguous")
-    check(_lib.lib().msl_grouped_gemm_nvfp4_scatter(x.data_ptr(), x.shape[0], codes_t.data_ptr(), scales_t.data_ptr(),
-                                                    global_scales.data_ptr(), offsets.data_ptr(), n_out,
-                                                    offsets.numel() - 1, e, n_tiles * TILE_N, k_blocks * 64, n_out,
-                                                    int(scatter_bases), scatter_index.data_ptr(), scatter_div,
-                                                    _ptr(status), _stream()), "msl_grouped_gemm_nvfp4_scatter")
 
 
 def interleave_gate_up(w13: torch.Tensor) -> torch.Tensor:

@@ -31,7 +31,7 @@ def test_library_exports_every_declared_symbol(lib):
     for n in names:
         assert hasattr(lib, n), f"{n} declared in include/msl.h but not exported"
     assert sorted(_lib.SIGNATURES) == names          # the ctypes table binds exactly the header
-    assert lib.msl_abi_version() == 1
+    assert lib.msl_abi_version() == _lib.ABI_VERSION == 2
     assert lib.msl_status_string(0) == b"ok" and b"argument" in lib.msl_status_string(-1)
 
 
@@ -44,6 +44,26 @@ def test_argument_errors_are_rejected_before_any_launch(lib):
     assert lib.msl_boundary(fake, 8, null, fake, fake, fake, fake, fake, fake, 8, 0, 8, 1e-8, 1e-5, null) == 0
     assert lib.msl_boundary(fake, 8, null, fake, fake, fake, fake, fake, fake, 8, 1, 12, 1e-8, 1e-5, null) == -2
     assert lib.msl_route_topk(fake, 8, 0, fake, 1.0, fake, 1, 4, 8, 4, fake, fake, fake, fake, fake, null) == -1
+    # the allocation-free routing entry checks everything before it touches its array or enqueues work
+    rds = lambda **kw: lib.msl_route_dispatch_static(   # noqa: E731
+        kw.get("logits", fake), 8, 0, fake, 1.0, fake, kw.get("x", fake), kw.get("ldx", 8), null, kw.get("tokens", 4),
+        kw.get("n_experts", 16), kw.get("top_k", 4), kw.get("n_local", 8), kw.get("width", 8), fake, fake,
+        kw.get("slab", fake), 64, fake, fake, null, null)
+    assert rds(n_local=0) == -1 and rds(n_local=-3) == -1 and rds(n_local=17) == -1
+    assert rds(logits=null) == -1 and rds(x=null) == -1 and rds(slab=null) == -1
+    assert rds(top_k=17, n_experts=64) == -1                      # accepted by the routing, not by the dispatch
+    assert rds(n_experts=1024, n_local=8) == -7                   # more experts than the routing kernel supports
+    assert rds(width=12) == -2 and rds(ldx=4) == -2 and rds(x=ctypes.c_void_p((1 << 20) + 8)) == -2
+    assert rds(tokens=0) == 0
+    assert lib.msl_route_dispatch(fake, 8, 0, fake, 1.0, fake, fake, 8, null, 4, 16, 4, 8, 8, fake, fake, fake, fake,
+                                  fake, null, fake, 64, fake, fake, null, null) == -1      # no barrier words
+    assert lib.msl_combine_boundary(fake, fake, fake, fake, null, 0, 4, 4, 64, null, null, fake, fake, fake, fake, fake,
+                                    64, 1e-8, 1e-5, null, null) == -1                      # no residual stream
+    # options: a value outside {0, 1} or an unknown option is refused; a set value reads back
+    assert lib.msl_set_option(99, 1) == -1 and lib.msl_set_option(0, 2) == -1
+    old = lib.msl_get_option(1)
+    assert lib.msl_set_option(1, 0) == 0 and lib.msl_get_option(1) == 0
+    assert lib.msl_set_option(1, old) == 0 and lib.msl_get_option(1) == old
     assert lib.msl_nvfp4_padded_rows(3072, 1) == 3072 and lib.msl_nvfp4_padded_rows(512, 1) == 512
     assert lib.msl_nvfp4_padded_rows(128, 0) == 256 and lib.msl_nvfp4_padded_rows(200, 1) == 256
 

@@ -54,7 +54,6 @@ def _worker(rank, world, port):
         # kernel differs (it sums the same terms with another association), so ids are equal and the
         # outputs agree to fp32 rounding of a bf16 result
         ep.enable_peer(ctx, st, max_tokens=hidden.shape[0], top_k=shape.top_k)
-        assert not ctx.push
         for _ in range(3):                                               # slab reuse across layers
             hidden3, stream3, ids3 = ep.kernel_fn(dev, st, ctx)
         torch.cuda.synchronize()
@@ -62,24 +61,22 @@ def _worker(rank, world, port):
         assert torch.equal(ids3, ids), f"rank {rank}: peer transport changed the routing"
         assert L.relative_l2(stream3, stream) < 1e-5 and L.relative_l2(hidden3.float(), hidden.float()) < 2e-3, \
             f"rank {rank}: peer transport differs"
-        # the same with the down projection storing every output row into the token owner's return buffer
-        push = ep.ExpertParallel(st, world, rank, shape.n_experts)
-        ep.enable_peer(push, st, max_tokens=hidden.shape[0], top_k=shape.top_k, push=True)
-        for _ in range(2):
-            hidden4, stream4, ids4 = ep.kernel_fn(dev, st, push)
+        # a slab physically too small for the routing: reported, the rows that do not fit are dropped, and
+        # neither the guard rows behind the slab and the intermediate buffer nor the flag words are touched
+        tight = ep.ExpertParallel(st, world, rank, shape.n_experts)
+        ep.enable_peer(tight, st, max_tokens=hidden.shape[0], top_k=shape.top_k, cap_rows=256, guard_rows=4096)
+        tight.peer.guard.fill_(0x5A)
+        tight.recv_i_raw[256:].fill_(3.0)
+        dist.barrier()
+        ep.kernel_fn(dev, st, tight)
         torch.cuda.synchronize()
-        layer.check_status(st)
-        assert torch.equal(ids4, ids)
-        assert L.relative_l2(stream4, stream) < 1e-5 and L.relative_l2(hidden4.float(), hidden.float()) < 2e-3
-        # a slab too small for the routing is reported, not overrun
-        ctx.peer.cap_saved = ctx.peer.cap
-        ctx.peer.cap = 256
-        ep.kernel_fn(dev, st, ctx)
-        torch.cuda.synchronize()
+        dist.barrier()
         with pytest.raises(Exception, match="out of range"):
             layer.check_status(st)
         st["status"].zero_()
-        ctx.peer.cap = ctx.peer.cap_saved
+        assert int(tight.group_offsets.max()) == 256
+        assert bool((tight.peer.guard == 0x5A).all()) and bool((tight.recv_i_raw[256:] == 3.0).all())
+        assert tight.peer.flags[:world + 1].tolist() == [3] * (world + 1)
         dist.barrier()
         # One sequence prefilled as two chunks, one per rank: the second rank's cached context is the
         # first rank's new K/V rows, handed over inside the layer call.

@@ -1,0 +1,114 @@
+"""The expert-parallel code paths that normally need several GPUs, run on ONE: a single rank is its
+own and only peer, so the plan kernel, the stream barrier, the dispatch into "the owner's" slab and
+the combine that loads from it all execute (on ordinary memory, with no process group), and a
+sequence split into pieces that all live on this rank exercises the K/V hand-off.  Every result is
+judged by the CPU oracle's layer check, like the single-GPU layer."""
+import dataclasses
+
+import pytest
+import torch
+
+from conftest import to_device
+from oracle import layer_ref as L
+
+pytestmark = pytest.mark.gpu
+
+
+def _small():
+    from muse_spark_open_challenge_b200 import synth
+    shape = dataclasses.replace(synth.MID, hidden=1024, hq=8, hkv=2, n_experts=16, local_experts=16, moe_width=1024,
+                                inter=256, shared_inter=512)
+    return shape, synth.make_weights(shape, seed=5)
+
+
+def _check(data_cpu, dev, weights, out):
+    hidden, stream, ids = out
+    d = L.dims_of(weights, data_cpu["config"])
+    slots = L.new_slots(data_cpu).cuda()
+    after = dict(data_cpu)
+    after["k_cache"], after["v_cache"] = dev["k_cache"].cpu(), dev["v_cache"].cpu()
+    k_rows = dev["k_cache"].view(-1, d.hkv, d.head_dim)[slots].cpu()
+    v_rows = dev["v_cache"].view(-1, d.hkv, d.head_dim)[slots].cpu()
+    return L.check_layer(after, weights, hidden.cpu(), stream.cpu(), ids.cpu(), k_rows, v_rows)
+
+
+def test_peer_transport_with_one_rank_matches_the_oracle_and_the_plain_layer():
+    from muse_spark_open_challenge_b200 import ep, layer, synth
+    shape, weights = _small()
+    data = synth.make_input(shape, [150, 77], [30, 0], seed=20, page=64, kv_scale=0.5)
+    st = layer.prepare(to_device(weights, "cuda"))
+    ctx = ep.ExpertParallel(st, 1, 0, shape.n_experts)
+    ep.enable_peer(ctx, st, max_tokens=227, top_k=shape.top_k, guard_rows=64)
+    ctx.peer.guard.fill_(0x5A)
+    ctx.recv_i_raw[ctx.peer.cap:].fill_(3.0)
+    dev = to_device(data, "cuda")
+    for _ in range(3):                                   # slab and barrier words are reused across layers
+        out = ep.kernel_fn(dev, st, ctx)
+    torch.cuda.synchronize()
+    layer.check_status(st)
+    ok, msg, _ = _check(data, dev, weights, out)
+    assert ok, msg
+    # the same rows through the same GEMMs as the plain single-GPU layer: equal routing, outputs equal to
+    # fp32 rounding (the two combine kernels associate their sums differently)
+    ref = layer.kernel_fn(to_device(data, "cuda"), st)
+    torch.cuda.synchronize()
+    assert torch.equal(out[2], ref[2])
+    assert L.relative_l2(out[1], ref[1]) < 1e-5 and L.relative_l2(out[0].float(), ref[0].float()) < 2e-3
+    assert bool((ctx.peer.guard == 0x5A).all()) and bool((ctx.recv_i_raw[ctx.peer.cap:] == 3.0).all())
+    assert int(ctx.peer.flags[1]) == 9                   # three barriers per layer, three layers
+
+
+def test_peer_slab_overflow_is_reported_and_nothing_lands_behind_the_slab():
+    """A slab (and intermediate buffer) physically sized to a capacity smaller than the routing needs:
+    the plan reports it, the rows that do not fit are dropped, and the guard rows directly behind
+    both buffers and the barrier's flag words behind them are untouched."""
+    from muse_spark_open_challenge_b200 import ep, layer, synth, _lib
+    shape, weights = _small()
+    data = synth.make_input(shape, [150, 77], [30, 0], seed=20, page=64, kv_scale=0.5)
+    st = layer.prepare(to_device(weights, "cuda"))
+    ctx = ep.ExpertParallel(st, 1, 0, shape.n_experts)
+    ep.enable_peer(ctx, st, max_tokens=227, top_k=shape.top_k, cap_rows=512, guard_rows=2048)   # 1816 routes
+    assert ctx.peer.cap == 512 and ctx.peer.slab.shape[0] == 512 and ctx.recv_i.shape[0] == 512
+    ctx.peer.guard.fill_(0x5A)
+    ctx.recv_i_raw[512:].fill_(3.0)
+    dev = to_device(data, "cuda")
+    hidden, stream, ids = ep.kernel_fn(dev, st, ctx)
+    torch.cuda.synchronize()
+    assert int(st["status"].item()) == _lib.ERR_CAPACITY
+    st["status"].zero_()
+    assert int(ctx.group_offsets.max()) == 512 and int(ctx.group_offsets[-1]) == 512
+    assert bool((ctx.peer.guard == 0x5A).all()), "rows were stored behind the slab"
+    assert bool((ctx.recv_i_raw[512:] == 3.0).all()), "rows were stored behind the intermediate buffer"
+    assert ctx.peer.flags[:2].tolist() == [3, 3]         # the barrier words hold barrier numbers, nothing else
+    assert torch.isfinite(hidden.float()).all()
+
+
+@pytest.mark.parametrize("lens,page", [([190, 131], 64), ([70, 45, 83], 16)])
+def test_kv_handoff_between_pieces_of_one_sequence_on_one_rank(lens, page):
+    """One sequence prefilled as pieces that are separate requests of the same layer call: a later
+    piece's cached context does not exist until the hand-off copies the earlier pieces' new K/V rows
+    into its pages.  Afterwards the context rows are byte-identical to the rows their pieces wrote,
+    and every piece passes the oracle's layer check."""
+    from muse_spark_open_challenge_b200 import ep, layer, synth
+    shape, weights = _small()
+    starts = [sum(lens[:p]) for p in range(len(lens))]
+    data = synth.make_input(shape, lens, starts, seed=50, page=page, kv_scale=0.5, fill_cache=False)
+    st = layer.prepare(to_device(weights, "cuda"))
+    ctx = ep.ExpertParallel(st, 1, 0, shape.n_experts)
+    ep.enable_peer(ctx, st, max_tokens=sum(lens), top_k=shape.top_k)
+    seq = ep.ChunkedSequence(None, 0, lens, shape.hkv, shape.head_dim, "cuda", owners=[0] * len(lens))
+    dev = to_device(data, "cuda")
+    out = ep.kernel_fn(dev, st, ctx, seq)
+    torch.cuda.synchronize()
+    layer.check_status(st)
+    row_bytes = shape.hkv * shape.head_dim
+    slots = L.new_slots(data).cuda()
+    for name in ("k_cache", "v_cache"):
+        rows = dev[name].view(torch.uint8).view(-1, row_bytes)
+        new = rows[slots]                                # the new rows of all pieces, in token order
+        for b in range(1, len(lens)):
+            pos = torch.arange(starts[b], device="cuda")
+            loc = dev["page_table"][b].long()[pos // page] * page + pos % page
+            assert torch.equal(rows[loc], new[:starts[b]]), f"{name}: piece {b}'s context differs from its source"
+    ok, msg, _ = _check(data, dev, weights, out)
+    assert ok, msg

@@ -33,11 +33,20 @@ def full():
     return shape, weights, data, st
 
 
-def test_full_size_layer_cache_rows_repeatability_and_batch_independence(full, monkeypatch):
+def test_full_size_layer_cache_rows_repeatability_and_batch_independence(full):
     from muse_spark_open_challenge_b200 import layer, synth
     # split-K (used for the router product of the 4096-token batch, not of the 16384-token one) sums in
     # another order: switched off so that both batches run the same arithmetic
-    monkeypatch.setenv("MSL_GEMM_SPLITK", "0")
+    from muse_spark_open_challenge_b200 import _lib
+    old_splitk = _lib.set_option("gemm_splitk", False)
+    try:
+        _cache_rows_repeatability_and_batch_independence(full)
+    finally:
+        _lib.set_option("gemm_splitk", old_splitk)
+
+
+def _cache_rows_repeatability_and_batch_independence(full):
+    from muse_spark_open_challenge_b200 import layer, synth
     shape, weights, data, st = full
     t = SEQS * SEQ_LEN
     hidden, stream, ids = layer.kernel_fn(data, st)
@@ -120,6 +129,21 @@ def test_full_size_routing_and_dispatch(full):
     assert torch.equal(owner, ids.long())
     for j in range(k):
         assert torch.equal(slab[rowmap[:, j].long()], h)
+    # the one-launch form the layer uses: the same ids, weights and offsets, and again a permutation
+    slab2 = torch.empty_like(slab)
+    off2 = torch.zeros_like(offsets)
+    counts2 = torch.zeros_like(counts)
+    sync = torch.zeros(2, dtype=torch.int32, device="cuda")
+    ids2, tw2, rowmap2 = ops.route_dispatch(logits, st["router_bias"], layer.ROUTER_MULTIPLIER, zero, e, k, e, h, None,
+                                            slab2, off2, counts2, sync, status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert torch.equal(ids2, ids) and torch.equal(tw2, tw) and torch.equal(off2, offsets)
+    assert torch.equal(rowmap2.flatten().long().sort().values, torch.arange(t * k, device="cuda"))
+    assert torch.equal(torch.bucketize(rowmap2.long(), off2[1:].long(), right=True), ids.long())
+    for j in range(k):
+        assert torch.equal(slab2[rowmap2[:, j].long()], h)
+    assert int(counts2.abs().sum()) == 0 and int(sync.abs().sum()) == 0
 
 
 def test_full_size_grouped_gemm_linearity_and_sampled_experts(full):

@@ -42,23 +42,6 @@ def test_gemm_bf16_matches_fp32_matmul(ops, m, n, k):
     assert int(status.item()) == 0
 
 
-@pytest.mark.parametrize("m,n,k,mode", [(256, 512, 512, 0), (300, 1280, 512, 0), (4096, 4096, 1024, 1),
-                                        (2500, 10240, 512, 0), (700, 512, 256, 2)])
-def test_gemm_cta_pair_variant(ops, m, n, k, mode, monkeypatch):
-    """The opt-in CTA-pair kernel (cluster of 2, one M256 x N256 MMA per step) gives the same result
-    as the default kernel: bit-identical, since both accumulate the same products in the same order."""
-    g = torch.Generator(device="cuda").manual_seed(m + n)
-    a = torch.randn((m, k), generator=g, device="cuda").to(torch.bfloat16)
-    w = (torch.randn((n, k), generator=g, device="cuda") / math.sqrt(k)).to(torch.bfloat16)
-    status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    monkeypatch.setenv("MSL_GEMM_PAIR", "0")
-    want = ops.gemm(a, w, out_mode=mode, status=status)
-    monkeypatch.setenv("MSL_GEMM_PAIR", "1")
-    got = ops.gemm(a, w, out_mode=mode, status=status)
-    assert int(status.item()) == 0
-    assert torch.equal(got, want)
-
-
 @pytest.mark.parametrize("m,n,k,segs,splits", [(753, 2304, 8192, 1, 2), (8, 2304, 4096, 1, 16), (100, 256, 2048, 2, 7),
                                                (24, 64, 1024, 1, 16), (300, 1280, 1024, 1, 3)])
 def test_gemm_split_k(ops, m, n, k, segs, splits):
@@ -255,12 +238,83 @@ def test_dispatch_then_combine_round_trip(ops, t, width, e, k, normed):
     # combine over the dispatched rows themselves (y = slab)
     post_w = 1.0 + 0.1 * torch.randn((width,), generator=g, device="cuda")
     add = torch.randn((t, width), generator=g, device="cuda").to(torch.bfloat16)
-    out = ops.combine(slab, rowmap, w, post_w, addend=add)
+    out = ops.combine(slab, rowmap, w, post_w, addend=add, status=status)
     yy = L.post_expert_norm(want_rows.float(), post_w - 1.0)          # (1 + w) form of the oracle
     weight_sum = (w * (rowmap >= 0)).sum(-1, keepdim=True)
     ref = yy * weight_sum + add.float()
     assert torch.allclose(out.float(), ref, rtol=2 ** -6, atol=2e-2)
     assert rel_l2(out, ref) < 5e-3
+    assert int(status.item()) == 0
+
+
+@pytest.mark.parametrize("t,width,e,k,n_local,start,normed", [(200, 256, 16, 4, 16, 0, True),
+                                                              (4100, 4096, 128, 8, 128, 0, False),
+                                                              (777, 512, 256, 8, 32, 96, True),
+                                                              (5, 512, 16, 4, 8, 12, False)])
+def test_fused_route_dispatch_matches_the_two_kernels(ops, t, width, e, k, n_local, start, normed):
+    """msl_route_dispatch (one cooperative launch) against msl_route_topk + msl_dispatch: ids and weights
+    bit-exact, the same per-expert offsets, every route's slab row holds the same bytes and lies in its
+    expert's range; the kernel leaves its counters and barrier words at zero, so a second call on other
+    inputs (no memset in between) is right as well."""
+    g = torch.Generator(device="cuda").manual_seed(t + e)
+    ls = torch.tensor([start], dtype=torch.int32, device="cuda")
+    counts1 = torch.zeros(n_local, dtype=torch.int32, device="cuda")
+    sync = torch.zeros(2, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for rep_i in range(2):
+        logits = 2.0 * torch.randn((t, e), generator=g, device="cuda")
+        bias = 0.1 * torch.randn((e,), generator=g, device="cuda")
+        x = torch.randn((t, width), generator=g, device="cuda").to(torch.bfloat16)
+        norm_w = (1.0 + 0.1 * torch.randn((width,), generator=g, device="cuda")) if normed else None
+        counts0 = torch.zeros(n_local, dtype=torch.int32, device="cuda")
+        ids0, w0, local_ids, slots = ops.route_topk(logits, bias, 0.5, ls, e, k, n_local, counts0)
+        slab0 = torch.zeros((t * k, width), dtype=torch.bfloat16, device="cuda")
+        off0 = torch.zeros(n_local + 1, dtype=torch.int32, device="cuda")
+        rowmap0 = ops.dispatch(x, norm_w, local_ids, slots, counts0, slab0, off0, status)
+        slab1 = torch.zeros_like(slab0)
+        off1 = torch.zeros_like(off0)
+        ids1, w1, rowmap1 = ops.route_dispatch(logits, bias, 0.5, ls, e, k, n_local, x, norm_w, slab1, off1, counts1,
+                                               sync, status)
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        assert torch.equal(ids0, ids1) and torch.equal(w0, w1)
+        assert torch.equal(off0, off1)
+        assert int(counts1.abs().sum()) == 0 and int(sync.abs().sum()) == 0       # left clean for the next call
+        live = rowmap0 >= 0
+        assert torch.equal(live, rowmap1 >= 0)
+        assert torch.equal(slab0[rowmap0[live].long()].view(torch.int16), slab1[rowmap1[live].long()].view(torch.int16))
+        rows = rowmap1[live].long()
+        assert len(torch.unique(rows)) == rows.numel() == int(off1[-1])
+        assert torch.equal(torch.bucketize(rows, off1[1:].long(), right=True).int(), local_ids[live])
+
+
+@pytest.mark.parametrize("t,width,k", [(300, 4096, 8), (64, 512, 4), (33, 8192, 8)])
+def test_fused_combine_boundary_matches_combine_then_boundary(ops, t, width, k):
+    """One kernel against the two it replaces: bit-identical up to width 4096 (the same per-thread sums
+    in the same order, the combined row rounded to bf16 in between as the unfused path stores it)."""
+    g = torch.Generator(device="cuda").manual_seed(width + t)
+    rows = t * k
+    y = torch.randn((rows, width), generator=g, device="cuda").to(torch.bfloat16)
+    rowmap = torch.randperm(rows, generator=g, device="cuda").int().view(t, k)
+    rowmap[::5, 1] = -1                                               # routes without a row
+    rowmap[3] = -1                                                    # a token with no local route at all
+    w = torch.rand((t, k), generator=g, device="cuda")
+    vec = lambda: 1.0 + 0.1 * torch.randn((width,), generator=g, device="cuda")   # noqa: E731
+    post_w, branch_scale, norm_w = vec(), vec(), vec()
+    alpha, beta = torch.rand((width,), generator=g, device="cuda"), torch.rand((width,), generator=g, device="cuda")
+    add = torch.randn((t, width), generator=g, device="cuda").to(torch.bfloat16)
+    s_in = torch.randn((t, width), generator=g, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    moe = ops.combine(y, rowmap, w, post_w, addend=add, status=status)
+    s_want, h_want = ops.boundary(moe, branch_scale, s_in, alpha, beta, norm_w)
+    s_got, h_got = ops.combine_boundary(y, rowmap, w, post_w, add, branch_scale, s_in, alpha, beta, norm_w,
+                                        status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    if width <= 4096:
+        assert torch.equal(s_got, s_want) and torch.equal(h_got.view(torch.int16), h_want.view(torch.int16))
+    else:
+        assert torch.allclose(s_got, s_want, rtol=1e-5, atol=1e-5) and rel_l2(h_got, h_want) < 2e-3
 
 
 # ------------------------------------------------------------------------------ grouped NVFP4 GEMM
@@ -310,8 +364,8 @@ def test_grouped_dequant_is_exact_for_every_code_and_scale(ops):
     ([255, 256, 257, 0, 511, 513, 1, 900], 512, 256, True),
     ([255, 256, 257, 0, 511, 513, 1, 900], 1024, 512, False),
 ])
-@pytest.mark.parametrize("variant", ["narrow", "wide", "pair"])
-def test_grouped_gemm_matches_dequantised_matmul(ops, counts, n, k, swiglu, variant, monkeypatch):
+@pytest.mark.parametrize("variant", ["narrow", "wide"])
+def test_grouped_gemm_matches_dequantised_matmul(ops, counts, n, k, swiglu, variant):
     """rel-L2 per expert against x.float() @ dequantize(w).T (the check of the reference's
     tools/prefill/moe_kernel/test_moe_fp4.py:124-145; its kernels score about 1.7e-3)."""
     g = torch.Generator(device="cuda").manual_seed(n + k)
@@ -324,7 +378,11 @@ def test_grouped_gemm_matches_dequantised_matmul(ops, counts, n, k, swiglu, vari
     n_out = n // 2 if swiglu else n
     out = torch.full((total + 5, n_out), 7.0, dtype=torch.bfloat16, device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    ops.grouped_gemm_nvfp4(x, cq, cs, gs, offsets, out, n_out, swiglu, status)
+    old = ops._lib.set_option("grouped_wide", variant == "wide")     # 128-row or (when the groups fill them) 256-row tiles
+    try:
+        ops.grouped_gemm_nvfp4(x, cq, cs, gs, offsets, out, n_out, swiglu, status)
+    finally:
+        ops._lib.set_option("grouped_wide", old)
     assert int(status.item()) == 0
     at = 0
     for ex, c in enumerate(counts):
@@ -337,6 +395,33 @@ def test_grouped_gemm_matches_dequantised_matmul(ops, counts, n, k, swiglu, vari
         assert rel_l2(out[at:at + c], ref) < 4e-3, f"expert {ex}"
         at += c
     assert (out[total:] == 7.0).all()              # rows outside every expert's range are never written
+
+
+@pytest.mark.parametrize("variant", ["narrow", "wide"])
+def test_grouped_gemm_never_stores_past_the_slab(ops, variant):
+    """Offsets that run past the slab (what an expert-parallel plan could hand over when the routing
+    needs more rows than the buffers hold) must not make the kernel store beyond it: the output
+    buffer is longer than the slab it is declared with, and the rows behind the declared end stay as
+    they were."""
+    g = torch.Generator(device="cuda").manual_seed(3)
+    n, k, e = 512, 256, 4
+    codes, sf, gs = _bank(e, n, k, g)
+    cq, cs, _ = ops.nvfp4_repack(codes, sf, interleave=False)
+    slab_rows, guard = 1024, 512
+    x_all = torch.randn((slab_rows + guard, k), generator=g, device="cuda").to(torch.bfloat16)
+    out_all = torch.full((slab_rows + guard, n), 7.0, dtype=torch.bfloat16, device="cuda")
+    # the groups claim 1400 rows of a 1024-row slab
+    offsets = torch.tensor([0, 500, 900, 1300, 1400], dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    old = ops._lib.set_option("grouped_wide", variant == "wide")
+    try:
+        ops.grouped_gemm_nvfp4(x_all[:slab_rows], cq, cs, gs, offsets, out_all[:slab_rows], n, False, status)
+    finally:
+        ops._lib.set_option("grouped_wide", old)
+    torch.cuda.synchronize()
+    assert (out_all[slab_rows:] == 7.0).all()
+    w0 = L.nvfp4_dequantize(codes[0].cpu(), sf[0].cpu(), gs[0].cpu()).cuda()
+    assert rel_l2(out_all[:500], x_all[:500].float() @ w0.T) < 4e-3           # the rows inside are still right
 
 
 # ------------------------------------------------------------------------------ attention
@@ -499,10 +584,13 @@ def test_ep_plan_places_every_rank_and_reports_overflow(ops):
                 assert int(seen[src][0][owner * local + le]) == at, (owner, src, le)
                 at += int(counts[src, owner * local + le])
         assert seen[owner][1].tolist() == want + [at]
-    # a slab smaller than the rows routed to rank 0 is reported
-    ops.ep_plan(counts.cuda(), 0, 8, torch.zeros(world * local, dtype=torch.int32, device="cuda"),
-                torch.zeros(world * local + 1, dtype=torch.int32, device="cuda"), status)
+    # a slab smaller than the rows routed to rank 0 is reported, and the row ranges stop at its end
+    small = torch.zeros(world * local + 1, dtype=torch.int32, device="cuda")
+    ops.ep_plan(counts.cuda(), 0, 8, torch.zeros(world * local, dtype=torch.int32, device="cuda"), small, status)
     assert int(status.item()) == ops._lib.ERR_CAPACITY
+    small = small.cpu()
+    assert int(small.max()) == 8 and int(small[-1]) == 8 and bool((small.diff() >= 0).all())
+    assert small.tolist() == [min(v, 8) for v in seen[0][1].tolist()]
 
 
 def test_peer_barrier_gives_up_when_a_rank_never_arrives(ops):

@@ -69,4 +69,54 @@ def test_static_route_dispatch_rejects_oversize():
     assert lib.msl_route_dispatch_static(p, 8, 0, p, 1.0, p, p, 8, None, 40000, 16, 8, 16, 8, p, p, p, 8, p, p, None,
                                          None) == -6          # 320000 routes > 262144
     assert lib.msl_route_dispatch_static(p, 8, 0, p, 1.0, p, p, 8, None, 16, 4096, 8, 2048, 8, p, p, p, 8, p, p, None,
-                                         None) == -6          # 2048 local experts > 1024
+                                         None) == -7          # more experts than the routing kernel supports (512)
+    # rejected before anything is enqueued or the shared array is touched: bad sizes, missing pointers
+    assert lib.msl_route_dispatch_static(p, 8, 0, p, 1.0, p, p, 8, None, 16, 16, 4, 0, 8, p, p, p, 8, p, p, None,
+                                         None) == -1          # no local expert
+    assert lib.msl_route_dispatch_static(p, 8, 0, p, 1.0, p, None, 8, None, 16, 16, 4, 8, 8, p, p, p, 8, p, p, None,
+                                         None) == -1          # no token rows
+    assert lib.msl_route_dispatch_static(p, 8, 0, p, 1.0, p, p, 8, None, 16, 64, 17, 8, 8, p, p, p, 8, p, p, None,
+                                         None) == -1          # top_k beyond what the dispatch handles
+    assert lib.msl_route_dispatch_static(p, 8, 0, p, 1.0, p, p, 8, None, 16, 16, 4, 8, 12, p, p, p, 8, p, p, None,
+                                         None) == -2          # width not a multiple of 8
+    torch.cuda.synchronize()
+
+
+def test_static_route_dispatch_allocates_nothing_and_matches_the_oracle_topk():
+    """The call must not allocate device memory (free memory as the driver reports it is the same
+    before and after; torch's own allocator is not involved in the call), and its expert ids are
+    the CPU oracle's top-k (bit-exact given the same fp32 logits) wherever no two biased scores
+    are closer than fp32 rounding."""
+    from muse_spark_open_challenge_b200 import _lib
+    from oracle import layer_ref as L
+    lib = _lib.lib()
+    t, e, k, n_local, width = 500, 64, 8, 64, 256
+    g = torch.Generator(device="cuda").manual_seed(11)
+    logits = 2.0 * torch.randn((t, e), generator=g, device="cuda")
+    bias = 0.1 * torch.randn((e,), generator=g, device="cuda")
+    x = torch.randn((t, width), generator=g, device="cuda").to(torch.bfloat16)
+    ls = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ids = torch.empty((t, k), dtype=torch.int32, device="cuda")
+    w = torch.empty((t, k), dtype=torch.float32, device="cuda")
+    slab = torch.zeros((t * k, width), dtype=torch.bfloat16, device="cuda")
+    rowmap = torch.empty((t, k), dtype=torch.int32, device="cuda")
+    off = torch.zeros(n_local + 1, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    args = (logits.data_ptr(), logits.stride(0), 0, bias.data_ptr(), 0.5, ls.data_ptr(), x.data_ptr(), x.stride(0), None,
+            t, e, k, n_local, width, ids.data_ptr(), w.data_ptr(), slab.data_ptr(), slab.shape[0], rowmap.data_ptr(),
+            off.data_ptr(), status.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert lib.msl_route_dispatch_static(*args) == 0         # the first call on a device looks the array up
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    assert lib.msl_route_dispatch_static(*args) == 0
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
+    assert int(status.item()) == 0
+    scores = torch.sigmoid(0.5 * logits.double().cpu()).float()          # the reference forms its scores in fp64
+    biased = scores + bias.cpu()
+    want = L.topk_ids(biased, k)
+    top = biased.topk(k + 1, dim=-1).values
+    clear = (top[:, :-1] - top[:, 1:]).min(-1).values > 1e-6
+    assert float(clear.float().mean()) > 0.9
+    assert torch.equal(ids.cpu().long().sort(-1).values[clear], want.long().sort(-1).values[clear])
