@@ -250,6 +250,45 @@ int msl_grouped_gemm_nvfp4(const void* x, int64_t slab_rows, const void* codes, 
                            const float* global_scales, const int* offsets, void* out, int64_t ld_out, int experts,
                            int weight_experts, int n_padded, int k, int n_out, int swiglu, int* status, void* stream);
 
+/* ---- Opt-in expert mode: NVFP4 activations x NVFP4 weights on the block-scaled tensor-core path
+ * (tcgen05.mma kind::mxf4nvf4, UE4M3 scales of 16-element blocks, K = 64 per instruction).  The default
+ * expert path (msl_grouped_gemm_nvfp4) keeps BF16 activations, as the reference's contract states
+ * (TASK.md:89); this mode quantises them to 4 bits and therefore has its own, larger error.  It follows
+ * the format of muse_prefill_layer/nvfp4.py:66-97 and stands where the reference's experiment
+ * tools/prefill/moe_kernel/moe_fp4.py:362-448 (tested by test_moe_fp4.py:124-169) runs its W4A16 kernel.
+ * k must be a multiple of 256.
+ *
+ * msl_nvfp4_bs_tiles: weight-row tiles (192 rows; for a gate/up bank 96 gate rows + their 96 up rows) of
+ * a bank with `rows` rows.  msl_nvfp4_bs_row_tiles: upper bound of the 128-row activation tiles of a slab
+ * with `groups` row groups (sizes the activation scale buffer: row tiles * (k / 256) * 2048 bytes).
+ *
+ * msl_nvfp4_bs_sf_repack (load time, lossless): e4m3 block scales [banks, rows, k / 16] of a bank as the
+ * reference stores it (baseline.py:74-79) -> [banks][tiles][k / 256][4][2][512 bytes], the per-stage
+ * blocks the kernel copies to tensor memory.  The 4-bit codes themselves are consumed in place, in the
+ * reference's own [banks, rows, k / 2] layout.
+ *
+ * msl_nvfp4_bs_quantize: rows [0, offsets[groups]) of x (bf16 [slab_rows, ldx], k columns) -> codes u8
+ * [slab_rows, k / 2] (element 2i in the low nibble of byte i), block scales in the kernel's tile layout
+ * (indexed by the same row tiles the GEMM's scheduler forms from `offsets`), and one fp32 scale per row
+ * (max |x| / (6 * 448)), round to nearest throughout. */
+int msl_nvfp4_bs_tiles(int rows, int swiglu);
+int64_t msl_nvfp4_bs_row_tiles(int64_t slab_rows, int groups);
+int msl_nvfp4_bs_sf_repack(const void* src_scales, void* dst_scales, int banks, int rows, int k, int swiglu,
+                           void* stream);
+int msl_nvfp4_bs_quantize(const void* x, int64_t ldx, int64_t slab_rows, int k, const int* offsets, int groups,
+                          void* codes, void* scales, float* row_scales, void* stream);
+
+/* out[r, :] = global_scales[e] * x_row_scales[r] * (xq (*) sx)[r, :] * (wq_e (*) sw_e)^T for the slab rows of
+ * row group g (e = g % weight_experts), with the operands of msl_nvfp4_bs_quantize and
+ * msl_nvfp4_bs_sf_repack; w_codes is the reference's u8 [weight_experts, weight_rows, k / 2].  With
+ * swiglu != 0 the bank is gate rows then up rows and out = silu(gate) * up (n_out = weight_rows / 2).
+ * Same scheduling, bounds and status conventions as msl_grouped_gemm_nvfp4. */
+int msl_grouped_gemm_nvfp4_bs(const void* x_codes, const void* x_scales, const float* x_row_scales,
+                              int64_t slab_rows, const void* w_codes, const void* w_scales_tiled,
+                              const float* global_scales, const int* offsets, void* out, int64_t ld_out, int groups,
+                              int weight_experts, int weight_rows, int k, int n_out, int swiglu, int* status,
+                              void* stream);
+
 /* Causal attention of the new tokens over the paged FP8 cache (which already holds the new
  * tokens' K/V rows): q8 e4m3 [tokens, hq, head_dim]; caches e4m3 [cache_rows, hkv, head_dim];
  * request b owns query rows cu_seqlens_q[b] .. cu_seqlens_q[b+1] at positions seq_lens[b] + i and

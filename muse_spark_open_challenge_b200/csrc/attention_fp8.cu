@@ -8,18 +8,37 @@
 // One CTA per (request, KV head, block of 2 * 128/G query tokens), G = query heads per KV head.
 // The CTA holds two 128-row query sub-tiles (rows are (token, head-in-group) pairs), so each K/V
 // tile staged in shared memory serves 256 MMA rows.  384 threads:
-//   warps 0-3, 4-7  softmax groups of sub-tile 0 / 1: one thread per row (TMEM lane = row); row
-//                   maximum, P = exp2(s - m) as E4M3 * 2^8 into shared memory, running sum, O
-//                   rescale in TMEM only when a row maximum moved, epilogue (1/l, v_scale, optional
-//                   per-head RMS norm * sigmoid(gate)) -> bf16
-//   warp  8         TMEM allocation + tcgen05.mma issue: S_s = Q_s K^T and O_s += P_s V (FP8 operands,
-//                   fp32 accumulators in TMEM, V consumed N-major straight from its [key][d] tile),
-//                   ordered so one group's softmax overlaps the other group's MMAs
+//   warps 0-3, 4-7  softmax groups of sub-tile 0 / 1: one thread per row (TMEM lane = row).  The row of
+//                   S (128 scores) is read from TMEM once and stays in registers; row maximum;
+//                   P = 2^(8 - tau) exp2(s - m) as E4M3 written back to TMEM over the first 32 columns
+//                   of the sub-tile's own S (four keys per 32-bit column: the layout of an 8-bit A
+//                   operand in tensor memory), in two halves of 64 keys so that P V can start on the
+//                   first half while the second is still being formed; running sum; O rescaled in TMEM
+//                   only when a row maximum moved; epilogue (1/l, v_scale, optional per-head RMS norm *
+//                   sigmoid(gate)) -> bf16
+//   warp  8         TMEM allocation + tcgen05.mma issue: S_s = Q_s K^T (both operands from shared
+//                   memory) and O_s += P_s V with P as the A operand FROM TMEM and V consumed N-major
+//                   straight from its [key][d] tile (FP8 operands, fp32 accumulators in TMEM).  Per
+//                   sub-tile the order is P V(j) then Q K^T(j+1): the tensor pipe runs them in that
+//                   order, so S(j+1) may overwrite the columns P(j) was read from, and a finished
+//                   Q K^T(j+1) implies a finished P V(j) (nobody waits for P V explicitly).  The two
+//                   sub-tiles alternate, one's MMAs running under the other's softmax
 //   warp  9         TMA: the two Q sub-tiles, and whole 128-key K/V tiles as two 64-row boxes per
 //                   tensor when the page size is a multiple of 64 and every key of the tile exists
 //   warps 10-11     gather loaders for all other tiles (any page size, ragged tail): two keys per
 //                   thread, 16-byte copies into the swizzled tile, zeros for keys past the causal end
-// K/V tiles move through a 4-stage ring.  TMEM: S0 | S1 | O0 | O1 (512 columns).  Every wait is bounded.
+// K/V tiles move through a 4-stage ring.  TMEM: S0 | S1 | O0 | O1 (512 columns), P inside S.  Every
+// wait is bounded.
+//
+// What bounds it (cycle counters inside the kernel, 4 x 4096 tokens, head_dim 128): per pair of 128-key
+// tiles a softmax warp spends about 125 cycles reading S, 800 on the row maximum, 2100 on the
+// exponentials and P, and 1200 waiting for its next S, 4300 in all, of which the tensor pipe is busy
+// about 1000 (1700 with the cost of issuing its 16 small MMAs).  The two groups run in lockstep: they
+// share each scheduler's ex2 unit during the exponential pass and are idle together while S is formed.
+// Variants that were built and measured slower on the same inputs (0.64 ms): two threads per row (16
+// softmax warps, 0.68 ms), one MMA issuer per sub-tile (0.72 ms), the exponential pass handed from group
+// to group through a token so that it never overlaps (0.74 ms: a single warp per scheduler does not
+// cover the ex2 latency), part of the exponentials as a cubic on the FMA pipe (0.70 ms).
 #include "msl_common.cuh"
 #include "msl_host.h"
 
@@ -59,10 +78,9 @@ template <int D>
 struct AttnSmem {
   static constexpr int kTile = kAN * D;                    // bytes of one K or V tile, and of one Q sub-tile
   static constexpr int kQ = 0;                             // 2 sub-tiles
-  static constexpr int kP = 2 * kTile;                     // 2 x (128 x 128 bytes)
-  static constexpr int kKV = kP + 2 * kAM * kAN;           // stages of (K tile, V tile)
+  static constexpr int kKV = 2 * kTile;                    // stages of (K tile, V tile)
   static constexpr int kBar = kKV + kAStages * 2 * kTile;
-  // q_full, kv_full[stages], kv_empty[stages], s_full[2], s_free[2], p_full[2], pv_done[2]
+  // q_full, kv_full[stages], kv_empty[stages], s_full[2], p_lo[2], p_hi[2], pv_done[2]
   static constexpr int kNumBars = 1 + 2 * kAStages + 8;
   static constexpr int kTotal = kBar + kNumBars * 8 + 16;
 };
@@ -99,13 +117,13 @@ __device__ __forceinline__ uint32_t e4m3x4(float a, float b, float c, float d) {
          (static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3)) << 16);
 }
 
-// One 64-column half of a row of S: exponentials (scaled by 2^8) summed into l, written as E4M3 to
-// the row's P chunks [chunk0, chunk0 + 4).  lim_hi / lim_lo bound the visible columns (col <= lim_hi
-// and col > lim_lo) when MASKED.
+// One 64-column half of a row of S: exponentials (scaled by 2^(8 - tau)) summed into l and packed as
+// E4M3, four keys per word in key order: the layout of an 8-bit A operand in TMEM.  lim_hi / lim_lo
+// bound the visible columns (col <= lim_hi and col > lim_lo) when MASKED.
 template <bool MASKED>
 __device__ __forceinline__ void softmax_half(const uint32_t (&s0)[32], const uint32_t (&s1)[32], float scale_log2,
-                                             float neg_m, int col0, int lim_hi, int lim_lo, float& l, uint8_t* p_row_base,
-                                             uint32_t r, int chunk0) {
+                                             float neg_m, int col0, int lim_hi, int lim_lo, float& l,
+                                             uint32_t (&packed)[16]) {
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const uint32_t(&s)[32] = h ? s1 : s0;
@@ -123,13 +141,8 @@ __device__ __forceinline__ void softmax_half(const uint32_t (&s0)[32], const uin
     }
     l += (part[0] + part[1]) + (part[2] + part[3]);
 #pragma unroll
-    for (int q = 0; q < 2; ++q) {
-      const uint4 packed = make_uint4(e4m3x4(e[16 * q + 0], e[16 * q + 1], e[16 * q + 2], e[16 * q + 3]),
-                                      e4m3x4(e[16 * q + 4], e[16 * q + 5], e[16 * q + 6], e[16 * q + 7]),
-                                      e4m3x4(e[16 * q + 8], e[16 * q + 9], e[16 * q + 10], e[16 * q + 11]),
-                                      e4m3x4(e[16 * q + 12], e[16 * q + 13], e[16 * q + 14], e[16 * q + 15]));
-      *reinterpret_cast<uint4*>(p_row_base + swz<128>(r, chunk0 + 2 * h + q)) = packed;
-    }
+    for (int q = 0; q < 8; ++q)
+      packed[8 * h + q] = e4m3x4(e[4 * q], e[4 * q + 1], e[4 * q + 2], e[4 * q + 3]);
   }
 }
 
@@ -164,9 +177,9 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   uint64_t* kv_full = bars + 1;
   uint64_t* kv_empty = kv_full + kAStages;
   uint64_t* s_full = kv_empty + kAStages;
-  uint64_t* s_free = s_full + 2;
-  uint64_t* p_full = s_free + 2;
-  uint64_t* pv_done = p_full + 2;
+  uint64_t* p_lo = s_full + 2;
+  uint64_t* p_hi = p_lo + 2;
+  uint64_t* pv_done = p_hi + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + S::kNumBars);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -224,8 +237,8 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     for (int i = 0; i < kAStages; ++i) { mbar_init(&kv_full[i], 3); mbar_init(&kv_empty[i], 1); }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s_full[i], 1);
-      mbar_init(&s_free[i], 4);
-      mbar_init(&p_full[i], 4);
+      mbar_init(&p_lo[i], 4);
+      mbar_init(&p_hi[i], 4);
       mbar_init(&pv_done[i], 1);
     }
     *abort_flag = 0;
@@ -245,8 +258,8 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc_qk = make_idesc(0, 0, kAM, kAN);
-      constexpr uint32_t idesc_pv = make_idesc(0, 0, kAM, D, 0, 1);     // B = V, N-major
-      const uint32_t sq = smem_u32(smem + S::kQ), sp = smem_u32(smem + S::kP);
+      constexpr uint32_t idesc_pv = make_idesc(0, 0, kAM, D, 0, 1);     // A = P from TMEM (K-major), B = V, N-major
+      const uint32_t sq = smem_u32(smem + S::kQ);
       auto issue_qk = [&](int s, uint32_t sk) {
 #pragma unroll
         for (int k = 0; k < D / 32; ++k)
@@ -254,12 +267,12 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                     make_sdesc(sk + k * 32, 16, kSbo, kSwz), idesc_qk, k != 0);
         tc_commit(&s_full[s]);
       };
-      auto issue_pv = [&](int s, uint32_t sv, bool first) {
+      // keys [64 half, 64 half + 64) of the tile: P columns [16 half, +16) of the sub-tile's S, 8 per MMA
+      auto issue_pv_half = [&](int s, uint32_t sv, int half, bool first) {
 #pragma unroll
-        for (int k = 0; k < kAN / 32; ++k)
-          tc_mma_f8(tmem_base + 2 * kAN + s * kAN, make_sdesc(sp + s * (kAM * kAN) + k * 32, 16, 1024, 2),
-                    make_sdesc(sv + k * 32 * D, 16, kSbo, kSwz), idesc_pv, !(first && k == 0));
-        tc_commit(&pv_done[s]);
+        for (int k = 2 * half; k < 2 * half + 2; ++k)
+          tc_mma_f8_ts(tmem_base + 2 * kAN + s * kAN, tmem_base + s * kAN + k * 8,
+                       make_sdesc(sv + k * 32 * D, 16, kSbo, kSwz), idesc_pv, !(first && k == 0));
       };
       bool ok = mbar_wait(q_full, 0) && mbar_wait(&kv_full[0], 0);
       if (ok) {
@@ -268,34 +281,33 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         if (n_sub[0] > 0) issue_qk(0, sk0);
         if (n_sub[1] > 0) issue_qk(1, sk0);
       }
-      // Per tile j: as soon as a group has copied S(j) into registers its S columns are free, so
-      // Q K^T of tile j+1 is issued while that group still works on the softmax of tile j; P V of
-      // tile j follows when the group has published P(j).
+      // Per tile j and sub-tile s: P V(j) as soon as the group has published the halves of P(j), then
+      // Q K^T(j+1) right behind it on the tensor pipe (it overwrites the S columns P(j) lived in).
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int st = j % kAStages;
         const uint32_t ph = j & 1;
         const uint32_t sv = smem_u32(smem + S::kKV + st * 2 * S::kTile + S::kTile);
-        if (j + 1 < n_tiles) {
-          const int st1 = (j + 1) % kAStages;
-          const uint32_t sk1 = smem_u32(smem + S::kKV + st1 * 2 * S::kTile);
-          if (*abort_flag || !mbar_wait(&kv_full[st1], ((j + 1) / kAStages) & 1)) { ok = false; break; }
-          tc_fence_after();
-#pragma unroll
-          for (int s = 0; s < 2; ++s) {
-            if (j + 1 < n_sub[s]) {
-              if (*abort_flag || !mbar_wait(&s_free[s], ph)) { ok = false; break; }
-              tc_fence_after();
-              issue_qk(s, sk1);
-            }
-          }
-          if (!ok) break;
-        }
+        const int st1 = (j + 1) % kAStages;
+        const uint32_t sk1 = smem_u32(smem + S::kKV + st1 * 2 * S::kTile);
+        bool next_ready = false;
 #pragma unroll
         for (int s = 0; s < 2; ++s) {
           if (j < n_sub[s]) {
-            if (*abort_flag || !mbar_wait(&p_full[s], ph)) { ok = false; break; }
+            if (*abort_flag || !mbar_wait(&p_lo[s], ph)) { ok = false; break; }
             tc_fence_after();
-            issue_pv(s, sv, j == 0);
+            issue_pv_half(s, sv, 0, j == 0);
+            if (*abort_flag || !mbar_wait(&p_hi[s], ph)) { ok = false; break; }
+            tc_fence_after();
+            issue_pv_half(s, sv, 1, false);
+            if (j == n_sub[s] - 1) tc_commit(&pv_done[s]);
+            if (j + 1 < n_sub[s]) {
+              if (!next_ready) {
+                if (*abort_flag || !mbar_wait(&kv_full[st1], ((j + 1) / kAStages) & 1)) { ok = false; break; }
+                tc_fence_after();
+                next_ready = true;
+              }
+              issue_qk(s, sk1);
+            }
           }
         }
         if (!ok) break;
@@ -396,7 +408,6 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t tmem_s = tmem_base + sub * kAN + lane_sel;
     const uint32_t tmem_o = tmem_base + 2 * kAN + sub * kAN + lane_sel;
-    uint8_t* sp = smem + S::kP + sub * (kAM * kAN);
     float m_run = -INFINITY, l_run = 0.f;                  // l accumulates 2^(8 - kTau) * sum of exponentials
     bool ok = true;
     for (int j = 0; j < n_mine && ok; ++j) {
@@ -415,9 +426,6 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       tmem_ld32(tmem_s + 64, sc);
       tmem_ld32(tmem_s + 96, sd);
       tmem_ld_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s_free[sub]);            // S(j) is in registers: its TMEM columns may be overwritten
       // pass 1: row maximum of the raw scores
       float m_tile = -INFINITY;
       if (full_tile) {
@@ -438,43 +446,44 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         m_run = m_new;
       }
       const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
-      // The previous tile's P V must have finished before P is overwritten (or O rescaled).
-      if (j > 0) {
-        if (*abort_flag || !mbar_wait(&pv_done[sub], (j - 1) & 1)) { ok = false; break; }
-        tc_fence_after();
-        if (__any_sync(0xffffffffu, corr != 1.0f)) {
+      // S(j) is ready only after P V(j-1) has finished (the tensor pipe ran it first), so O may be
+      // rescaled and the P columns overwritten without another wait.
+      if (j > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
 #pragma unroll 1
-          for (int c = 0; c < D; c += 16) {
-            uint32_t o[16];
-            tmem_ld16(tmem_o + c, o);
-            tmem_ld_wait();
+        for (int c = 0; c < D; c += 16) {
+          uint32_t o[16];
+          tmem_ld16(tmem_o + c, o);
+          tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
-            tmem_st16(tmem_o + c, o);
-          }
-          tmem_st_wait();
+          for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
+          tmem_st16(tmem_o + c, o);
         }
       }
       l_run *= corr;
-      // pass 2: P = 2^(8 - kTau) * exp2(s * scale - m) as E4M3, row sum in fp32
+      // pass 2: P = 2^(8 - kTau) * exp2(s * scale - m) as E4M3 into TMEM, row sum in fp32; the first
+      // 64 keys are published before the last 64 are formed
       const float neg_m = (8.0f - kTau) - m_use;
       float l_tile = 0.f;
-      if (full_tile) {
-        softmax_half<false>(sa, sb, scale_log2, neg_m, 0, lim_hi, lim_lo, l_tile, sp, r, 0);
-        softmax_half<false>(sc, sd, scale_log2, neg_m, 64, lim_hi, lim_lo, l_tile, sp, r, 4);
-      } else {
-        softmax_half<true>(sa, sb, scale_log2, neg_m, 0, lim_hi, lim_lo, l_tile, sp, r, 0);
-        softmax_half<true>(sc, sd, scale_log2, neg_m, 64, lim_hi, lim_lo, l_tile, sp, r, 4);
-      }
-      l_run += l_tile;
+      uint32_t pk[16];
+      if (full_tile) softmax_half<false>(sa, sb, scale_log2, neg_m, 0, lim_hi, lim_lo, l_tile, pk);
+      else softmax_half<true>(sa, sb, scale_log2, neg_m, 0, lim_hi, lim_lo, l_tile, pk);
+      tmem_st16(tmem_s, pk);
+      tmem_st_wait();                                       // also covers the rescaled O
       tc_fence_before();
-      fence_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_full[sub]);
+      if (lane == 0) mbar_arrive(&p_lo[sub]);
+      if (full_tile) softmax_half<false>(sc, sd, scale_log2, neg_m, 64, lim_hi, lim_lo, l_tile, pk);
+      else softmax_half<true>(sc, sd, scale_log2, neg_m, 64, lim_hi, lim_lo, l_tile, pk);
+      tmem_st16(tmem_s + 16, pk);
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_hi[sub]);
+      l_run += l_tile;
     }
     // ---------------------------------------------------------------- epilogue
     if (ok && n_mine > 0) {
-      if (*abort_flag || !mbar_wait(&pv_done[sub], (n_mine - 1) & 1)) ok = false;
+      if (*abort_flag || !mbar_wait(&pv_done[sub], 0)) ok = false;     // committed once, behind the last P V
     }
     if (p.kv_splits > 1) {
       // partial result of this key slice: O as it stands in TMEM, with the maximum and sum it refers to

@@ -55,7 +55,10 @@ __device__ __forceinline__ void block_sum(float (&v)[N], float* scratch) {
 // HKV values (the row layout of the QKV+gate projection; the gate columns after them are not read).
 // A token's D/2 rotation angles are evaluated once per block (not once per head) while the loads are in
 // flight, and shared through shared memory.
-constexpr int kRopeTok = 2;
+#ifndef MSL_ROPE_TOK
+#define MSL_ROPE_TOK 2
+#endif
+constexpr int kRopeTok = MSL_ROPE_TOK;
 
 template <int D>
 __global__ void __launch_bounds__(256, 6)
@@ -632,17 +635,20 @@ __global__ void peer_barrier_kernel(int* const* __restrict__ flag_bases, int ran
 // ============================================================================ weighted combine
 // out[t] = sum_j w[t,j] * rms(y[rowmap[t,j]] * post_w, 1e-8) (+ addend[t]).  One block per token.  The
 // routes that have a slab row (rowmap >= 0; under the reference's sharding only the local experts'
-// routes do) are compacted in route order and taken kBulkRows at a time: one elected thread moves whole
-// rows global -> shared memory with cp.async.bulk (TMA, completion on an mbarrier) into one of two
-// buffers, so the rows of round r + 1 are in flight while the block reduces round r (sums of squares,
-// then the weighted accumulation, which stays in registers across the rounds; post_w multiplies the sum
-// once at the end: sum_j w_j rms(y_j post_w) = post_w sum_j r_j y_j with r_j = w_j / sqrt(mean((y_j
-// post_w)^2) + eps)).  Each row crosses HBM exactly once; 32 KB of shared memory per block at width 4096
-// lets five blocks per SM keep bytes outstanding.  (Measured at 16384 tokens x 8 rows of 8 KB: two rows
-// per buffer 315 us, one 349 us, four 372 us; the same rounds staged with 16-byte cp.async 335 us.)
+// routes do) are compacted in route order and ALL of them (up to kCombineRows per round; more only when
+// top_k > 8) are requested at once: one elected thread moves whole rows global -> shared memory with
+// cp.async.bulk (TMA, completion on an mbarrier) while every thread prefetches its part of the addend
+// (and of the residual stream, when the boundary is fused) into registers.  Then one pass over shared
+// memory forms the rows' sums of squares, ONE block-wide reduction turns them into the per-row factors
+// r_j = w_j / sqrt(mean((y_j post_w)^2) + eps), and a second pass accumulates sum_j r_j y_j, which
+// post_w multiplies once at the end (sum_j w_j rms(y_j post_w) = post_w sum_j r_j y_j).  Each row
+// crosses HBM exactly once; a block holds 64 KB at width 4096 and top_k 8, three blocks per SM, so two
+// blocks' loads are in flight while a third computes.  (An earlier form took the rows two at a time
+// through two 16 KB buffers, five blocks per SM: four block-wide reductions and a dozen barriers per token
+// left it at 0.64 of the copy bandwidth.)
 constexpr int kCombineThreads = 256;
 constexpr int kCombineMaxChunks = 4;    // 8-element chunks per thread: width <= 8192 (MAXC = 2: <= 4096)
-constexpr int kBulkRows = 2;
+constexpr int kCombineRows = 8;         // rows staged per round
 
 __device__ __forceinline__ void bulk_row_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -666,14 +672,14 @@ struct BoundaryTail {
 };
 
 template <int MAXC, bool FUSED>
-__global__ void __launch_bounds__(kCombineThreads, MAXC <= 2 ? (FUSED ? 4 : 5) : (FUSED ? 2 : 3))
+__global__ void __launch_bounds__(kCombineThreads, MAXC <= 2 ? 3 : 1)
 combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ rowmap, const float* __restrict__ w,
                const float* __restrict__ post_w, const __nv_bfloat16* __restrict__ addend, int64_t ld_add,
                __nv_bfloat16* __restrict__ out, int64_t ld_out, int top_k, int width, BoundaryTail bt, int* status) {
   constexpr int THREADS = kCombineThreads;
-  constexpr int R = kBulkRows;
-  extern __shared__ __align__(128) uint8_t rows_smem[];     // [2][R][width] bf16
-  __shared__ __align__(8) uint64_t bars[2];
+  constexpr int R = kCombineRows;
+  extern __shared__ __align__(128) uint8_t rows_smem[];     // [R][width] bf16
+  __shared__ __align__(8) uint64_t bar;
   __shared__ float scratch[32 * R];
   __shared__ int route_of[32], row_of[32];
   __shared__ int n_valid_s, failed_s;
@@ -689,29 +695,42 @@ combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ rowm
       route_of[at] = j;
       row_of[at] = row;
     }
+    __syncwarp();
     if (j == 0) {
-      n_valid_s = __popc(have);
+      const int n = __popc(have);
+      n_valid_s = n;
       failed_s = 0;
-      mbar_init(&bars[0], 1);
-      mbar_init(&bars[1], 1);
+      mbar_init(&bar, 1);
       mbar_fence_init();
+      if (n > 0) {                                          // round 0 goes out before anything else happens
+        const int first = min(R, n);
+        mbar_expect_tx(&bar, first * row_bytes);
+        for (int q = 0; q < first; ++q)
+          bulk_row_load(rows_smem + static_cast<size_t>(q) * row_bytes, y + static_cast<int64_t>(row_of[q]) * width,
+                        row_bytes, &bar);
+      }
+    }
+  }
+  // what the tail needs from global memory, requested while the rows are in flight
+  uint4 add_raw[MAXC];
+  float s[FUSED ? MAXC : 1][8];
+#pragma unroll
+  for (int c = 0; c < MAXC; ++c) {
+    const int ch = threadIdx.x + c * THREADS;
+    add_raw[c] = make_uint4(0, 0, 0, 0);
+    if (ch < chunks) {
+      if (addend != nullptr) add_raw[c] = *reinterpret_cast<const uint4*>(addend + t * ld_add + ch * 8);
+      if constexpr (FUSED) {
+        const float4 s0 = *reinterpret_cast<const float4*>(bt.s_in + static_cast<int64_t>(t) * width + ch * 8);
+        const float4 s1 = *reinterpret_cast<const float4*>(bt.s_in + static_cast<int64_t>(t) * width + ch * 8 + 4);
+        s[c][0] = s0.x; s[c][1] = s0.y; s[c][2] = s0.z; s[c][3] = s0.w;
+        s[c][4] = s1.x; s[c][5] = s1.y; s[c][6] = s1.z; s[c][7] = s1.w;
+      }
     }
   }
   __syncthreads();
   const int n_valid = n_valid_s;
   const int n_rounds = (n_valid + R - 1) / R;
-  auto issue = [&](int r) {                                 // thread 0 only
-    const int n = min(R, n_valid - r * R);
-    uint64_t* bar = &bars[r & 1];
-    mbar_expect_tx(bar, n * row_bytes);
-    for (int q = 0; q < n; ++q)
-      bulk_row_load(rows_smem + (static_cast<size_t>((r & 1) * R + q)) * row_bytes,
-                    y + static_cast<int64_t>(row_of[r * R + q]) * width, row_bytes, bar);
-  };
-  if (threadIdx.x == 0) {
-    if (n_rounds > 0) issue(0);
-    if (n_rounds > 1) issue(1);
-  }
   float acc[MAXC][8];
 #pragma unroll
   for (int c = 0; c < MAXC; ++c) {
@@ -720,10 +739,9 @@ combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ rowm
   }
   for (int r = 0; r < n_rounds; ++r) {
     const int n_round = min(R, n_valid - r * R);
-    const uint8_t* buf = rows_smem + static_cast<size_t>((r & 1) * R) * row_bytes;
     // A bulk copy of mapped memory always lands; should the bounded wait run out all the same, the
     // block reports it and, after the next block-wide barrier, leaves without writing its token.
-    if (!mbar_wait(&bars[r & 1], (r >> 1) & 1)) {
+    if (!mbar_wait(&bar, r & 1)) {
       report_error(status, MSL_ERR_DEVICE_TIMEOUT);
       failed_s = 1;
     }
@@ -741,7 +759,7 @@ combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ rowm
         for (int q = 0; q < R; ++q) {
           if (q < n_round) {
             float v[8];
-            unpack8(*reinterpret_cast<const uint4*>(buf + static_cast<size_t>(q) * row_bytes + ch * 16), v);
+            unpack8(*reinterpret_cast<const uint4*>(rows_smem + static_cast<size_t>(q) * row_bytes + ch * 16), v);
 #pragma unroll
             for (int i = 0; i < 8; ++i) { const float x = v[i] * pw[i]; ss[q] += x * x; }
           }
@@ -766,16 +784,24 @@ combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ rowm
         for (int q = 0; q < R; ++q) {
           if (q < n_round) {
             float v[8];
-            unpack8(*reinterpret_cast<const uint4*>(buf + static_cast<size_t>(q) * row_bytes + ch * 16), v);
+            unpack8(*reinterpret_cast<const uint4*>(rows_smem + static_cast<size_t>(q) * row_bytes + ch * 16), v);
 #pragma unroll
             for (int i = 0; i < 8; ++i) acc[c][i] += v[i] * rr[q];
           }
         }
       }
     }
-    fence_async_smem();                                     // generic reads of the buffer before its next bulk write
-    __syncthreads();
-    if (threadIdx.x == 0 && r + 2 < n_rounds) issue(r + 2);
+    if (r + 1 < n_rounds) {                                 // top_k > 8 only: the next rows reuse the buffer
+      fence_async_smem();                                   // generic reads of the buffer before its next bulk write
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        const int n = min(R, n_valid - (r + 1) * R);
+        mbar_expect_tx(&bar, n * row_bytes);
+        for (int q = 0; q < n; ++q)
+          bulk_row_load(rows_smem + static_cast<size_t>(q) * row_bytes,
+                        y + static_cast<int64_t>(row_of[(r + 1) * R + q]) * width, row_bytes, &bar);
+      }
+    }
   }
   // f = addend + post_w * sum, rounded to bf16
 #pragma unroll
@@ -785,8 +811,8 @@ combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ rowm
       const float4 w0 = *reinterpret_cast<const float4*>(post_w + ch * 8);
       const float4 w1 = *reinterpret_cast<const float4*>(post_w + ch * 8 + 4);
       const float pw[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-      float o[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      if (addend != nullptr) unpack8(*reinterpret_cast<const uint4*>(addend + t * ld_add + ch * 8), o);
+      float o[8];
+      unpack8(add_raw[c], o);
 #pragma unroll
       for (int i = 0; i < 8; ++i) o[i] += acc[c][i] * pw[i];
       const uint4 packed = pack8(o);
@@ -796,7 +822,6 @@ combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ rowm
   }
   if constexpr (FUSED) {
     const int64_t row = t;
-    float s[MAXC][8];
     float ss[1] = {0.f};
 #pragma unroll
     for (int c = 0; c < MAXC; ++c) {
@@ -808,10 +833,6 @@ combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ rowm
           acc[c][0] *= w0.x; acc[c][1] *= w0.y; acc[c][2] *= w0.z; acc[c][3] *= w0.w;
           acc[c][4] *= w1.x; acc[c][5] *= w1.y; acc[c][6] *= w1.z; acc[c][7] *= w1.w;
         }
-        const float4 s0 = *reinterpret_cast<const float4*>(bt.s_in + row * width + ch * 8);
-        const float4 s1 = *reinterpret_cast<const float4*>(bt.s_in + row * width + ch * 8 + 4);
-        s[c][0] = s0.x; s[c][1] = s0.y; s[c][2] = s0.z; s[c][3] = s0.w;
-        s[c][4] = s1.x; s[c][5] = s1.y; s[c][6] = s1.z; s[c][7] = s1.w;
 #pragma unroll
         for (int i = 0; i < 8; ++i) ss[0] += acc[c][i] * acc[c][i];
       }
@@ -1122,7 +1143,7 @@ static int combine_launch(const void* y, const int* rowmap, const float* weights
   if (width > 8 * kCombineThreads * kCombineMaxChunks) return MSL_ERR_UNSUPPORTED;
   if (tokens == 0) return MSL_OK;
   constexpr int kPeerSmemMax = 200 * 1024;
-  const int most = 2 * kBulkRows * 8 * kCombineThreads * kCombineMaxChunks * 2;
+  const int most = 200 * 1024;
   static SmemConfig c2, c4, c2f, c4f, p4, p8;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   auto* yy = static_cast<const __nv_bfloat16*>(y);
@@ -1146,7 +1167,8 @@ static int combine_launch(const void* y, const int* rowmap, const float* weights
     return cudaGetLastError() == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
   }
   if (reinterpret_cast<uintptr_t>(y) & 15) return MSL_ERR_ALIGN;
-  const int smem = 2 * kBulkRows * width * 2;               // two buffers: 32 KB at width 4096
+  const int smem = std::min(top_k, kCombineRows) * width * 2;     // all of a token's rows: 64 KB at width 4096, top_k 8
+  if (smem > most) return MSL_ERR_UNSUPPORTED;
   const bool small = width <= 8 * kCombineThreads * 2;
   if (tail != nullptr) {
     if (small) {

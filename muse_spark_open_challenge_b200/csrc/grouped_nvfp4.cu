@@ -29,7 +29,7 @@
 // reference's experimental W4A16 kernel (tools/prefill/moe_kernel/moe_fp4.py:163-183); the bit layout
 // (moved into the load-time repack so three of four pairs need one shift and one mask), the arithmetic
 // scale decode and the table for special scale codes are this file's own.
-#include "msl_common.cuh"
+#include "grouped_sched.cuh"
 #include "msl_host.h"
 
 namespace msl {
@@ -84,32 +84,6 @@ struct GroupedArgs {
   int swiglu;
   int* status;
 };
-
-struct TileInfo {
-  int expert, row0, rows, nt;   // row group, first slab row, valid rows in the tile, n tile
-};
-
-__device__ __forceinline__ TileInfo decode_tile(int g, const int* mt_prefix, const int* offsets, int experts,
-                                                int n_tiles, int tile_m) {
-  // mt_prefix[e] = number of row tiles of the groups before e.  Tiles of one (group, n tile) are
-  // adjacent so the weight tile they share stays in L2.
-  int lo = 0, hi = experts - 1;
-  while (lo < hi) {
-    const int mid = (lo + hi + 1) >> 1;
-    if (mt_prefix[mid] * n_tiles <= g) lo = mid; else hi = mid - 1;
-  }
-  const int e = lo;
-  const int mte = mt_prefix[e + 1] - mt_prefix[e];
-  const int r = g - mt_prefix[e] * n_tiles;
-  const int nt = r / mte, mt = r - nt * mte;
-  const int start = offsets[e], cnt = offsets[e + 1] - start;
-  TileInfo ti;
-  ti.expert = e;
-  ti.row0 = start + mt * tile_m;
-  ti.rows = min(tile_m, cnt - mt * tile_m);
-  ti.nt = nt;
-  return ti;
-}
 
 // Eight codes of one 32-bit word -> four bf16x2 words (elements 2j, 2j+1 in word j), times the
 // block scale.  The repack put the even elements in the low half-word and the odd ones in the
@@ -217,23 +191,7 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
     const uint32_t b = __float_as_uint(s * 3.32306998946228968e35f) >> 16;   // * 2^118: exact, top 16 bits
     lut[i] = b | (b << 16);
   }
-  if (warp == 0) {
-    // prefix of row-tile counts per row group, one warp
-    int carry = 0;
-    for (int b0 = 0; b0 < p.experts; b0 += 32) {
-      const int i = b0 + lane;
-      const int c = i < p.experts ? (p.offsets[i + 1] - p.offsets[i] + S::kTileM - 1) / S::kTileM : 0;
-      int inc = c;
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const int nb = __shfl_up_sync(0xffffffffu, inc, o);
-        if (lane >= o) inc += nb;
-      }
-      if (i < p.experts) mt_prefix[i] = carry + inc - c;
-      carry += __shfl_sync(0xffffffffu, inc, 31);
-    }
-    if (lane == 0) mt_prefix[p.experts] = carry;
-  }
+  if (warp == 0) row_tile_prefix(p.offsets, p.experts, S::kTileM, mt_prefix, lane);
   if (threadIdx.x == 0) {
     // full: one expect_tx arrival of the TMA lane + the warps of one producer group;
     // tmem_empty: the 4 epilogue warps.

@@ -96,6 +96,8 @@ class ExpertParallel:
             raise ValueError("the expert count must divide evenly over the ranks")
         if st["n_local"] != n_experts // world:
             raise ValueError("state holds a different number of local experts than n_experts / world")
+        if st.get("experts_nvfp4"):
+            raise ValueError("the NVFP4-activation expert mode is a single-GPU option")
         self.world, self.rank, self.n_experts, self.group = world, rank, n_experts, group
         self.zero = torch.zeros(1, dtype=torch.int32, device=st["device"])
         self.counts = torch.zeros(n_experts, dtype=torch.int32, device=st["device"])

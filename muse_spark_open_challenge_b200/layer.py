@@ -15,6 +15,8 @@ directly; "shared_w13"/"shared_w2" add a dense BF16 shared expert.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import ops
@@ -32,11 +34,18 @@ def _coeffs(gate):
     return alpha.contiguous(), beta.contiguous()
 
 
-def prepare(weights: dict) -> dict:
+def prepare(weights: dict, experts_nvfp4: bool = None) -> dict:
+    """One-time preparation of a layer's weights.  `experts_nvfp4` opts in to running the routed experts
+    with NVFP4 activations on the block-scaled tensor-core path (default: the environment variable
+    MSL_EXPERTS_NVFP4=1, read here once, else off): about twice the expert rate, at the cost of 4-bit
+    activations, which the reference's contract does not allow (TASK.md:89: BF16 activations), so the
+    default stays W4A16."""
     dev = weights["qkv_gate"].device
     if dev.type != "cuda":
         raise MslError("prepare() needs CUDA tensors: this implementation has no CPU path")
-    st = {"device": dev}
+    if experts_nvfp4 is None:
+        experts_nvfp4 = os.environ.get("MSL_EXPERTS_NVFP4", "0") == "1"
+    st = {"device": dev, "experts_nvfp4": bool(experts_nvfp4)}
     st["qkv_gate"] = weights["qkv_gate"].contiguous()
     st["o"] = weights["o"].contiguous()
     router = weights["router"].float()
@@ -57,8 +66,17 @@ def prepare(weights: dict) -> dict:
         st["w_pre_exp"] = (1.0 + weights["pre_expert_norm"].float()).contiguous()
     el, two_i, half_w = weights["w13"].shape
     st["n_local"], st["inter"], st["moe_width"] = el, two_i // 2, 2 * half_w
-    st["w13_q"], st["w13_s"], st["w13_rows"] = ops.nvfp4_repack(weights["w13"], weights["w13_sf"], interleave=True)
-    st["w2_q"], st["w2_s"], st["w2_rows"] = ops.nvfp4_repack(weights["w2"], weights["w2_sf"], interleave=False)
+    if st["experts_nvfp4"]:
+        if st["moe_width"] % 256 or st["inter"] % 256:
+            raise MslError("experts_nvfp4 needs an expert width and intermediate size that are multiples of 256")
+        # the 4-bit codes are consumed as the reference stores them; only the block scales are re-tiled
+        st["w13_codes"] = weights["w13"].view(torch.uint8).contiguous()
+        st["w2_codes"] = weights["w2"].view(torch.uint8).contiguous()
+        st["w13_sf_t"] = ops.nvfp4_bs_sf_repack(weights["w13_sf"], True)
+        st["w2_sf_t"] = ops.nvfp4_bs_sf_repack(weights["w2_sf"], False)
+    else:
+        st["w13_q"], st["w13_s"], st["w13_rows"] = ops.nvfp4_repack(weights["w13"], weights["w13_sf"], interleave=True)
+        st["w2_q"], st["w2_s"], st["w2_rows"] = ops.nvfp4_repack(weights["w2"], weights["w2_sf"], interleave=False)
     st["w13_gs"] = weights["w13_gs"].float().contiguous()
     st["w2_gs"] = weights["w2_gs"].float().contiguous()
     st["shared"] = "shared_w13" in weights
@@ -202,12 +220,7 @@ def moe_stage(h, data, st, boundary_stream=None):
     elif overlap:
         for t in (ids, tw, rowmap):
             t.record_stream(main)
-    ops.grouped_gemm_nvfp4(slab_x, st["w13_q"], st["w13_s"], st["w13_gs"], st["offsets"], slab_i, st["inter"], True,
-                           status)
-    _mark(st, "experts_gate_up")
-    ops.grouped_gemm_nvfp4(slab_i, st["w2_q"], st["w2_s"], st["w2_gs"], st["offsets"], slab_x, st["moe_width"],
-                           False, status)
-    _mark(st, "experts_down")
+    expert_gemms(slab_x, slab_i, st["offsets"], st)
     if boundary_stream is not None and not st["pooled"]:
         out = ops.combine_boundary(slab_x, rowmap, tw, st["w_post_exp"], shared, st["w_post_ffn"], boundary_stream,
                                    st["a2"], st["b2"], st["w_next"], POST_NORM_EPS, RMS_EPS, status)
@@ -219,6 +232,50 @@ def moe_stage(h, data, st, boundary_stream=None):
         moe = unpool(moe, st)
         _mark(st, "gemm_unpooler")
     return moe, ids
+
+
+def _lib_row_tiles(rows, groups):
+    from . import _lib
+    return _lib.lib().msl_nvfp4_bs_row_tiles(rows, groups)
+
+
+def expert_gemms(slab_x, slab_i, offsets, st):
+    """Gate/up projection with fused SiLU * up (slab_x -> slab_i), then the down projection (slab_i ->
+    slab_x, in place of the inputs).  Default: NVFP4 weights x BF16 activations.  Opt-in
+    (st["experts_nvfp4"]): each slab is first quantised to NVFP4 (4-bit codes, a UE4M3 scale per 16
+    elements, an fp32 scale per row) and both products run on the block-scaled MMA."""
+    status = st["status"]
+    if st["experts_nvfp4"]:
+        def quantised(key, slab):
+            # buffers sized for the scratch capacity, grow-only like the slabs they mirror
+            rows, k = slab.shape
+            bufs = st.get(key)
+            if bufs is None or bufs[0].shape[0] < st["cap"]:
+                st.setdefault("retired", []).append(bufs)
+                cap, dev = st["cap"], st["device"]
+                tiles = int(_lib_row_tiles(cap, offsets.numel() - 1))
+                bufs = (torch.empty((cap, k // 2), dtype=torch.uint8, device=dev),
+                        torch.zeros((tiles, k // 256, 4, 512), dtype=torch.uint8, device=dev),
+                        torch.ones(cap, dtype=torch.float32, device=dev))
+                st[key] = bufs
+            return ops.nvfp4_bs_quantize(slab, offsets, out=(bufs[0][:rows], bufs[1], bufs[2][:rows]))
+
+        xq = quantised("quant_x", slab_x)
+        _mark(st, "quantize_x")
+        ops.grouped_gemm_nvfp4_bs(xq, st["w13_codes"], st["w13_sf_t"], st["w13_gs"], offsets, slab_i, st["inter"], True,
+                                  status)
+        _mark(st, "experts_gate_up")
+        iq = quantised("quant_i", slab_i)
+        _mark(st, "quantize_inter")
+        ops.grouped_gemm_nvfp4_bs(iq, st["w2_codes"], st["w2_sf_t"], st["w2_gs"], offsets, slab_x, st["moe_width"],
+                                  False, status)
+        _mark(st, "experts_down")
+        return
+    ops.grouped_gemm_nvfp4(slab_x, st["w13_q"], st["w13_s"], st["w13_gs"], offsets, slab_i, st["inter"], True, status)
+    _mark(st, "experts_gate_up")
+    ops.grouped_gemm_nvfp4(slab_i, st["w2_q"], st["w2_s"], st["w2_gs"], offsets, slab_x, st["moe_width"], False,
+                           status)
+    _mark(st, "experts_down")
 
 
 SLICED_MAX_TOKENS = 8          # reference.py:58

@@ -288,6 +288,52 @@ def grouped_gemm_nvfp4(x, codes_t, scales_t, global_scales, offsets, out, n_out,
     return out
 
 
+# ---- opt-in expert mode: NVFP4 activations on the block-scaled tensor-core path
+def nvfp4_bs_sf_repack(scales, swiglu):
+    """Re-tile a bank's e4m3 block scales [E, rows, k/16] for `grouped_gemm_nvfp4_bs` (load time)."""
+    e, rows, k16 = scales.shape
+    k = 16 * k16
+    tiles = int(_lib.lib().msl_nvfp4_bs_tiles(rows, int(swiglu)))
+    out = torch.empty((e, tiles, k // 256, 4, 2, 512), dtype=torch.uint8, device=scales.device)
+    check(_lib.lib().msl_nvfp4_bs_sf_repack(scales.contiguous().view(torch.uint8).data_ptr(), out.data_ptr(), e, rows,
+                                            k, int(swiglu), _stream()), "msl_nvfp4_bs_sf_repack")
+    return out
+
+
+def nvfp4_bs_quantize(x, offsets, out=None):
+    """Rows [0, offsets[-1]) of x (bf16 [rows, k]) -> (codes u8 [rows, k/2], block scales in the GEMM's
+    tile layout, row scales fp32 [rows]).  `out` reuses a previous result's buffers."""
+    _need(x, torch.bfloat16, "x"), _need(offsets, torch.int32, "offsets")
+    rows, k = x.shape
+    groups = offsets.numel() - 1
+    if out is None:
+        row_tiles = int(_lib.lib().msl_nvfp4_bs_row_tiles(rows, groups))
+        out = (torch.empty((rows, k // 2), dtype=torch.uint8, device=x.device),
+               torch.zeros((row_tiles, k // 256, 4, 512), dtype=torch.uint8, device=x.device),
+               torch.ones(rows, dtype=torch.float32, device=x.device))
+    codes, scales, row_scales = out
+    check(_lib.lib().msl_nvfp4_bs_quantize(x.data_ptr(), _rows(x, "x"), rows, k, offsets.data_ptr(), groups,
+                                           codes.data_ptr(), scales.data_ptr(), row_scales.data_ptr(), _stream()),
+          "msl_nvfp4_bs_quantize")
+    return out
+
+
+def grouped_gemm_nvfp4_bs(xq, w_codes, w_scales_tiled, global_scales, offsets, out, n_out, swiglu, status=None):
+    """`grouped_gemm_nvfp4` with 4-bit activations: xq = (codes, block scales, row scales) from
+    `nvfp4_bs_quantize`; w_codes u8 [E, rows, k/2] as the reference stores them."""
+    codes, scales, row_scales = xq
+    _need(out, torch.bfloat16, "out"), _need(offsets, torch.int32, "offsets")
+    e, rows, half_k = w_codes.shape
+    if not w_codes.is_contiguous():
+        raise MslError("w_codes must be contiguous")
+    check(_lib.lib().msl_grouped_gemm_nvfp4_bs(codes.data_ptr(), scales.data_ptr(), row_scales.data_ptr(),
+                                               codes.shape[0], w_codes.data_ptr(), w_scales_tiled.data_ptr(),
+                                               global_scales.data_ptr(), offsets.data_ptr(), out.data_ptr(),
+                                               _rows(out, "out"), offsets.numel() - 1, e, rows, 2 * half_k, n_out,
+                                               int(swiglu), _ptr(status), _stream()), "msl_grouped_gemm_nvfp4_bs")
+    return out
+
+
 def interleave_gate_up(w13: torch.Tensor) -> torch.Tensor:
     """Reorder a [2*I, K] gate-then-up matrix into blocks of 128 gate rows followed by their 128
     up rows, the row order OUT_SWIGLU_BF16 expects.  I must be a multiple of 128."""

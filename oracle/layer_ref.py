@@ -103,6 +103,30 @@ def residual_coefficients(gate):
     return alpha, beta
 
 
+_E2M1_MIDS = (0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0)       # nvfp4.py:27
+
+
+def nvfp4_quantize_rows(x):
+    """The reference's NVFP4 quantiser (muse_prefill_layer/nvfp4.py:59-88) applied to every row with
+    that row's own tensor scale: scale_r = amax_r / (6 * 448), block scale = e4m3(amax_block / 6 /
+    scale_r), element codes = nearest grid value of x / (block scale * scale_r).  Returns (values on
+    the e2m1 grid fp32 [rows, k], block scales fp32 [rows, k/16], row scales fp32 [rows]).  Exact
+    mid-points between two grid values go to the lower magnitude here (torch.bucketize,
+    nvfp4.py:52-53) and to the even code in the hardware conversion; real inputs do not hit them."""
+    xf = x.float()
+    rows, k = xf.shape
+    amax = xf.abs().amax(dim=-1)
+    rs = torch.where(amax > 0, amax / (6.0 * 448.0), torch.ones_like(amax))
+    blocks = xf.view(rows, k // NVFP4_BLOCK, NVFP4_BLOCK)
+    sf = (blocks.abs().amax(dim=-1) / 6.0 / rs[:, None]).clamp(max=448.0).to(torch.float8_e4m3fn).float()
+    scale = (sf * rs[:, None]).unsqueeze(-1)
+    q = torch.where(scale > 0, blocks / scale, torch.zeros_like(blocks))
+    mids = torch.tensor(_E2M1_MIDS, dtype=torch.float32)
+    grid = torch.tensor(_E2M1, dtype=torch.float32)
+    mag = grid[torch.bucketize(q.abs().clamp(max=6.0), mids)]
+    return (torch.sign(q) * mag).view(rows, k), sf, rs
+
+
 def nvfp4_dequantize(packed, sf, gs):
     """muse_prefill_layer/nvfp4.py:40-47,90-97 in torch (see oracle/nvfp4_ref.py for numpy)."""
     p = packed.view(torch.uint8)
