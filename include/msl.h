@@ -323,6 +323,83 @@ int msl_attention_fp8_split(const void* q8, const void* k_cache, const void* v_c
                             int64_t ld_out, const void* gate, int64_t ld_gate, int kv_splits, void* workspace,
                             int* status, void* stream);
 
+/* ---- The whole layer for hosts that do not run Python.  These three calls stand where the reference's
+ * harness calls `state = prepare(weights)` once and `kernel_fn(data, state)` per step
+ * (muse_prefill_layer/submission.py:1013-1070, 1073-1140; tools/prefill/judge.py:94,113,124): the same
+ * launch order, side-stream fork of the routing chain (submission.py:1105-1117) and output contract
+ * (hidden bf16 [T, H], stream fp32 [T, H], expert ids i32 [T, K], in-place K/V cache writes), with all
+ * memory owned by the caller.  All pointers are device memory unless stated. */
+typedef struct MslLayerConfig {
+  int tokens, batch, max_q_len;   /* T; requests; longest request of the call */
+  int hidden, hq, hkv, head_dim;
+  int n_experts, n_local, top_k;
+  int moe_width, inter;           /* experts' input/output width and intermediate size */
+  int pooled;                     /* pooler / unpooler / pre-expert norm present (the reference's shard) */
+  int shared_inter;               /* BF16 shared expert's intermediate size, 0 = none (not with `pooled`) */
+  int page_size, max_pages, window;
+  int64_t cache_rows;             /* rows of each K/V cache: pages * page_size */
+  float softmax_scale;            /* sm_scale * qk_scale_factor (reference.py:36, baseline.py:304) */
+  float rope_theta;               /* 0 = no RoPE */
+} MslLayerConfig;
+
+/* The reference's Weights dict (baseline.py:66-86) as stored: bf16 matrices and vectors, fp32 router and
+ * router bias, NVFP4 banks (u8 codes, e4m3 block scales, fp32 per-expert scales). */
+typedef struct MslLayerRawWeights {
+  const void *qkv_gate, *o, *attn_residual_gate, *ffn_residual_gate, *pre_ffn_norm, *post_expert_norm, *post_ffn_norm,
+      *next_pre_attn_norm, *pre_expert_norm, *pooler, *unpooler, *shared_w13, *shared_w2;
+  const float *router, *router_bias;
+  const void *w13, *w13_sf, *w2, *w2_sf;
+  const float *w13_gs, *w2_gs;
+} MslLayerRawWeights;
+
+/* What msl_layer_prefill consumes (filled by msl_layer_prepare; points into `prepared` and into the raw
+ * weights, which must stay alive). */
+typedef struct MslLayerWeights {
+  const void *qkv_gate, *o, *router_hilo, *pooler, *unpooler, *shared_w13, *shared_w2;
+  const float *router_bias, *a1, *b1, *a2, *b2, *w_pre_ffn, *w_post_exp, *w_post_ffn, *w_next, *w_pre_exp, *inv_freq;
+  const void *w13_q, *w13_s, *w2_q, *w2_s;
+  const float *w13_gs, *w2_gs;
+  int w13_rows, w2_rows;          /* padded rows of the re-tiled banks */
+} MslLayerWeights;
+
+typedef struct MslLayerInputs {   /* the reference's Inputs dict, baseline.py:88-105 */
+  const float* stream;            /* fp32 [T, H] */
+  const void* attn_input;         /* bf16 [T, H] */
+  void *k_cache, *v_cache;        /* e4m3 [cache_rows, hkv, head_dim]; the new rows are written in place */
+  const int64_t *positions, *cache_loc;
+  const int *seq_lens, *cu_seqlens_q, *page_table;   /* page_table i32 [batch, max_pages] */
+  const float *k_scale, *v_scale; /* device scalars */
+  const int* local_start;         /* device scalar */
+} MslLayerInputs;
+
+typedef struct MslLayerOutputs {
+  void* hidden;                   /* bf16 [T, H] */
+  float* stream;                  /* fp32 [T, H] */
+  int* ids;                       /* i32 [T, top_k] */
+} MslLayerOutputs;
+
+/* cudaStream_t / cudaEvent_t as void*.  With side == NULL everything runs on `main`; otherwise the router
+ * product (and, without a pooler, routing + dispatch) is forked onto `side` and joined again through the
+ * two events, which the caller creates once (cudaEventDisableTiming) and owns. */
+typedef struct MslLayerStreams {
+  void *main, *side, *fork_event, *join_event;
+} MslLayerStreams;
+
+/* Bytes of `prepared` / of the per-call workspace for this configuration (-1: configuration rejected). */
+int64_t msl_layer_prepared_bytes(const MslLayerConfig* cfg);
+int64_t msl_layer_workspace_bytes(const MslLayerConfig* cfg);
+/* One-time preparation into caller-owned memory (256-byte aligned): router hi + lo split, residual
+ * coefficients, (1 + w) norm vectors, RoPE frequencies, lossless re-tiling of the expert banks, gate/up
+ * interleave of the shared expert.  Asynchronous on `stream`. */
+int msl_layer_prepare(const MslLayerConfig* cfg, const MslLayerRawWeights* raw, void* prepared, int64_t prepared_bytes,
+                      MslLayerWeights* out, void* stream);
+/* One layer call.  `workspace` (256-byte aligned, msl_layer_workspace_bytes) needs no initialisation and
+ * may be reused by the next call on the same stream; calls that overlap on the GPU need separate
+ * workspaces.  Device-side failures (timed-out waits, out-of-range cache rows) are reported in *status. */
+int msl_layer_prefill(const MslLayerConfig* cfg, const MslLayerWeights* weights, const MslLayerInputs* in,
+                      const MslLayerOutputs* out, void* workspace, int64_t workspace_bytes,
+                      const MslLayerStreams* streams, int* status);
+
 #ifdef __cplusplus
 }
 #endif
