@@ -323,6 +323,13 @@ int msl_attention_fp8_split(const void* q8, const void* k_cache, const void* v_c
                             int64_t ld_out, const void* gate, int64_t ld_gate, int kv_splits, void* workspace,
                             int* status, void* stream);
 
+/* Measured ceiling of one tensor-core instruction shape: every SM issues `iters` tcgen05.mma of
+ * M = 128 x N = n back to back on operands resident in shared memory (kind 0: bf16, K = 16; 1: e4m3,
+ * K = 32; 2: NVFP4 block scaled, K = 64), no loads and no epilogue.  The caller times the launch
+ * (2 * 128 * n * K * iters flops per SM).  It supplies the FP8 and NVFP4 denominators of the roofline
+ * fractions; the reference's own model takes the vendor's dense figures (reference.py:681-697). */
+int msl_mma_peak(int kind, int n, int iters, int* status, void* stream);
+
 /* ---- The whole layer for hosts that do not run Python.  These three calls stand where the reference's
  * harness calls `state = prepare(weights)` once and `kernel_fn(data, state)` per step
  * (muse_prefill_layer/submission.py:1013-1070, 1073-1140; tools/prefill/judge.py:94,113,124): the same

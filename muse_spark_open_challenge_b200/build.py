@@ -17,7 +17,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libmsl.so")
 SOURCES = ["host_util.cu", "gemm_bf16.cu", "grouped_nvfp4.cu", "grouped_nvfp4_bs.cu", "attention_fp8.cu",
-           "elementwise.cu", "layer_host.cu"]
+           "elementwise.cu", "layer_host.cu", "mma_peak.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
               "--use_fast_math=false"]
 

@@ -194,13 +194,13 @@ def zipf_targets(n_experts: int, routes: int, s: float = 1.1, cap: int = 3000, n
 
 
 def skew_router(weights: dict, h: torch.Tensor, targets: torch.Tensor, top_k: int, iters: int = 40,
-                sample: int = 4096, seed: int = 0) -> torch.Tensor:
+                sample: int = 4096, seed: int = 0, identity: bool = False) -> torch.Tensor:
     """Shift `router_bias` per expert, in place, until the top-k routing of `h` [T, H] (a sample
     of it) has per-expert counts close to `targets` (a permutation of them over experts, seeded).
     Experts with target 0 get a bias so low they are never chosen.  Returns the permutation."""
     e = weights["router"].shape[0]
     g = torch.Generator().manual_seed(seed)
-    perm = torch.randperm(e, generator=g)
+    perm = torch.arange(e) if identity else torch.randperm(e, generator=g)     # identity: target i is expert i's
     tgt = torch.empty(e, dtype=torch.float64)
     tgt[perm] = targets
     idx = torch.randperm(h.shape[0], generator=g)[:sample].to(h.device)
