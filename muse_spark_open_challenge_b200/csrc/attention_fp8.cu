@@ -38,7 +38,8 @@
 // Variants that were built and measured slower on the same inputs (0.64 ms): two threads per row (16
 // softmax warps, 0.68 ms), one MMA issuer per sub-tile (0.72 ms), the exponential pass handed from group
 // to group through a token so that it never overlaps (0.74 ms: a single warp per scheduler does not
-// cover the ex2 latency), part of the exponentials as a cubic on the FMA pipe (0.70 ms).
+// cover the ex2 latency), part of the exponentials as a cubic on the FMA pipe (0.70 ms), S read from TMEM
+// a second time for the exponential pass instead of being held in 128 registers (0.67 ms).
 #include "msl_common.cuh"
 #include "msl_host.h"
 

@@ -131,3 +131,7 @@ def test_layer_on_synthetic_shapes(case):
     ok, msg, rep = L.check_layer(data, weights, hidden, stream, ids, k_rows, v_rows)
     print(name, msg, rep)
     assert ok, msg
+    # Stated tolerance at these widths for the BF16 layer output against the reference run with FP8
+    # queries and the same expert ids: relative L2 <= 3e-2 (measured 1.5e-2 ... 2.7e-2; the reference-made
+    # tiny cases above hold 2e-2), mean absolute error <= 2.5e-2 on outputs of unit scale.
+    assert rep["hidden_vs_fp8q"]["rel_l2"] <= 3e-2 and rep["hidden_vs_fp8q"]["mean_abs"] <= 2.5e-2
