@@ -9,20 +9,28 @@
 // The CTA holds two 128-row query sub-tiles (rows are (token, head-in-group) pairs), so each K/V
 // tile staged in shared memory serves 256 MMA rows.  384 threads:
 //   warps 0-3, 4-7  softmax groups of sub-tile 0 / 1: one thread per row (TMEM lane = row).  The row of
-//                   S (128 scores) is read from TMEM once and stays in registers; row maximum;
+//                   S (128 scores) is read from TMEM once and stays in registers; hidden keys of a tile
+//                   on the causal diagonal or the window's edge are set to -inf by a separate mask pass,
+//                   so the two hot passes exist once; row maximum (three-input max);
 //                   P = 2^(8 - tau) exp2(s - m) as E4M3 written back to TMEM over the first 32 columns
 //                   of the sub-tile's own S (four keys per 32-bit column: the layout of an 8-bit A
 //                   operand in tensor memory), in two halves of 64 keys so that P V can start on the
-//                   first half while the second is still being formed; running sum; O rescaled in TMEM
-//                   only when a row maximum moved; epilogue (1/l, v_scale, optional per-head RMS norm *
-//                   sigmoid(gate)) -> bf16
-//   warp  8         TMEM allocation + tcgen05.mma issue: S_s = Q_s K^T (both operands from shared
-//                   memory) and O_s += P_s V with P as the A operand FROM TMEM and V consumed N-major
-//                   straight from its [key][d] tile (FP8 operands, fp32 accumulators in TMEM).  Per
-//                   sub-tile the order is P V(j) then Q K^T(j+1): the tensor pipe runs them in that
-//                   order, so S(j+1) may overwrite the columns P(j) was read from, and a finished
-//                   Q K^T(j+1) implies a finished P V(j) (nobody waits for P V explicitly).  The two
-//                   sub-tiles alternate, one's MMAs running under the other's softmax
+//                   first half while the second is still being formed; running sum.  The running
+//                   maximum moves only when some row of the warp exceeds it by more than tau; then all
+//                   32 rows move to their newest maximum and O is rescaled in TMEM after the
+//                   exponential pass, when the scores' registers are free to carry it in wide pieces.
+//                   The two warps that share a scheduler (one of each group) TAKE TURNS at the
+//                   exponential pass (a pair of mbarriers per scheduler): while one forms its
+//                   exponentials the other waits for its next S, reads it and finds its maximum.
+//                   Epilogue (1/l, v_scale, optional per-head RMS norm * sigmoid(gate)) -> bf16
+//   warp  8         TMEM allocation + tcgen05.mma issue.  All 32 lanes run the control flow (addresses
+//                   and descriptors stay warp-uniform), one elected lane executes the MMAs and commits:
+//                   S_s = Q_s K^T (both operands from shared memory) and O_s += P_s V with P as the A
+//                   operand FROM TMEM and V consumed N-major straight from its [key][d] tile (FP8
+//                   operands, fp32 accumulators in TMEM).  Per sub-tile the order is P V(j) then
+//                   Q K^T(j+1): the tensor pipe runs them in that order, so S(j+1) may overwrite the
+//                   columns P(j) was read from, and a finished Q K^T(j+1) implies a finished P V(j)
+//                   (nobody waits for P V explicitly)
 //   warp  9         TMA: the two Q sub-tiles, and whole 128-key K/V tiles as two 64-row boxes per
 //                   tensor when the page size is a multiple of 64 and every key of the tile exists
 //   warps 10-11     gather loaders for all other tiles (any page size, ragged tail): two keys per
@@ -30,16 +38,25 @@
 // K/V tiles move through a 4-stage ring.  TMEM: S0 | S1 | O0 | O1 (512 columns), P inside S.  Every
 // wait is bounded.
 //
-// What bounds it (cycle counters inside the kernel, 4 x 4096 tokens, head_dim 128): per pair of 128-key
-// tiles a softmax warp spends about 125 cycles reading S, 800 on the row maximum, 2100 on the
-// exponentials and P, and 1200 waiting for its next S, 4300 in all, of which the tensor pipe is busy
-// about 1000 (1700 with the cost of issuing its 16 small MMAs).  The two groups run in lockstep: they
-// share each scheduler's ex2 unit during the exponential pass and are idle together while S is formed.
-// Variants that were built and measured slower on the same inputs (0.64 ms): two threads per row (16
-// softmax warps, 0.68 ms), one MMA issuer per sub-tile (0.72 ms), the exponential pass handed from group
-// to group through a token so that it never overlaps (0.74 ms: a single warp per scheduler does not
-// cover the ex2 latency), part of the exponentials as a cubic on the FMA pipe (0.70 ms), S read from TMEM
-// a second time for the exponential pass instead of being held in 128 registers (0.67 ms).
+// What bounds it (cycle counters of the development build below, 4 x 4096 tokens, head_dim 128, per
+// 128-key tile and softmax warp): waiting for S 1200, reading it 115, maximum 450, waiting for the turn
+// 400-600, exponentials + P 1450, rescale 220 (one tile in two has one), stores + arrivals 110: about
+// 3900 cycles, of which the tensor pipe works about 1000.  No pipe is saturated; the chain
+// P ready -> P V -> Q K^T -> S ready -> read -> maximum -> exponentials is, twice, interleaved.  Facts
+// measured on the way (microbenchmarks on this GPU): ex2.approx takes 8 cycles per warp instruction and
+// scheduler, whatever the number of warps (ex2 on f16x2 pairs 16: no gain); max with two or three
+// inputs 2; the FP8 pair conversion 4; a tcgen05.mma never takes less than about 57 cycles (M128 with
+// N <= 64 runs as long as with N = 128), so smaller S tiles cost tensor time without saving any; a warp
+// whose unrolled code outgrows the instruction cache loses half its speed, which is why two warps in
+// lockstep on the same code did better than their instruction counts say.
+// Variants that were built and measured slower on the same inputs (0.64 ms before the turns, 0.575 ms
+// with them): two threads per row (16 softmax warps, 0.68 ms), one MMA issuer per sub-tile (0.72 ms),
+// 64-key S halves as separate buffers so that the next S is formed under the softmax of the other half
+// (0.64 ms in lockstep, 0.72 ms with turns: twice the Q K^T instructions and twice the per-pass ramps),
+// part of the exponentials as a cubic on the FMA pipe (0.60 ms with turns, 0.60 ms without), S read
+// from TMEM a second time for the exponential pass instead of being held in 128 registers (0.67 ms),
+// mbarrier waits with a suspend-time hint (no change), tau = 6 (0.568 ms, not kept: less range below
+// the reference maximum).
 #include "msl_common.cuh"
 #include "msl_host.h"
 
@@ -49,6 +66,19 @@ constexpr int kAM = 128;    // rows per query sub-tile
 constexpr int kAN = 128;    // keys per tile
 constexpr int kAStages = 4;
 constexpr float kTau = 4.0f;   // log2 slack of the running softmax maximum before O is rescaled
+
+// Phase timing for development builds (-DMSL_ATTN_PROF): cycles summed over all CTAs, per phase of two
+// softmax warps and of the MMA issuer; read back with msl_debug_attn_prof.
+#ifdef MSL_ATTN_PROF
+__device__ unsigned long long g_attn_prof[32];
+#define PROF_DECL long long prof_t = clock64(); long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}
+#define PROF_MARK(i) do { const long long now_ = clock64(); prof_acc[i] += now_ - prof_t; prof_t = now_; } while (0)
+#define PROF_FLUSH(base, n) do { for (int i_ = 0; i_ < (n); ++i_) atomicAdd(&g_attn_prof[(base) + i_], (unsigned long long)prof_acc[i_]); } while (0)
+#else
+#define PROF_DECL do {} while (0)
+#define PROF_MARK(i) do {} while (0)
+#define PROF_FLUSH(base, n) do {} while (0)
+#endif
 
 struct AttnArgs {
   const uint8_t* k_cache;       // [cache rows][hkv][D] e4m3
@@ -81,8 +111,8 @@ struct AttnSmem {
   static constexpr int kQ = 0;                             // 2 sub-tiles
   static constexpr int kKV = 2 * kTile;                    // stages of (K tile, V tile)
   static constexpr int kBar = kKV + kAStages * 2 * kTile;
-  // q_full, kv_full[stages], kv_empty[stages], s_full[2], p_lo[2], p_hi[2], pv_done[2]
-  static constexpr int kNumBars = 1 + 2 * kAStages + 8;
+  // q_full, kv_full[stages], kv_empty[stages], s_full[2], p_lo[2], p_hi[2], pv_done[2], turn[2][4]
+  static constexpr int kNumBars = 1 + 2 * kAStages + 16;
   static constexpr int kTotal = kBar + kNumBars * 8 + 16;
 };
 
@@ -118,13 +148,16 @@ __device__ __forceinline__ uint32_t e4m3x4(float a, float b, float c, float d) {
          (static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3)) << 16);
 }
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 // One 64-column half of a row of S: exponentials (scaled by 2^(8 - tau)) summed into l and packed as
-// E4M3, four keys per word in key order: the layout of an 8-bit A operand in TMEM.  lim_hi / lim_lo
-// bound the visible columns (col <= lim_hi and col > lim_lo) when MASKED.
-template <bool MASKED>
+// E4M3, four keys per word in key order: the layout of an 8-bit A operand in TMEM.
 __device__ __forceinline__ void softmax_half(const uint32_t (&s0)[32], const uint32_t (&s1)[32], float scale_log2,
-                                             float neg_m, int col0, int lim_hi, int lim_lo, float& l,
-                                             uint32_t (&packed)[16]) {
+                                             float neg_m, float& l, uint32_t (&packed)[16]) {
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const uint32_t(&s)[32] = h ? s1 : s0;
@@ -132,12 +165,7 @@ __device__ __forceinline__ void softmax_half(const uint32_t (&s0)[32], const uin
     float part[4] = {0.f, 0.f, 0.f, 0.f};                  // independent chains
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
-      float x = fmaf(__uint_as_float(s[i]), scale_log2, neg_m);
-      if constexpr (MASKED) {
-        const int col = col0 + 32 * h + i;
-        if (!(col <= lim_hi && col > lim_lo)) x = -INFINITY;
-      }
-      e[i] = ex2_approx(x);
+      e[i] = ex2_approx(fmaf(__uint_as_float(s[i]), scale_log2, neg_m));
       part[i & 3] += e[i];
     }
     l += (part[0] + part[1]) + (part[2] + part[3]);
@@ -147,21 +175,22 @@ __device__ __forceinline__ void softmax_half(const uint32_t (&s0)[32], const uin
   }
 }
 
-template <bool MASKED>
-__device__ __forceinline__ float row_max_half(const uint32_t (&s0)[32], const uint32_t (&s1)[32], int col0, int lim_hi,
-                                              int lim_lo, float m) {
+__device__ __forceinline__ float row_max_half(const uint32_t (&s0)[32], const uint32_t (&s1)[32], float m) {
   float acc[4] = {m, -INFINITY, -INFINITY, -INFINITY};     // independent chains
 #pragma unroll
-  for (int i = 0; i < 32; ++i) {
-    float a = __uint_as_float(s0[i]), b = __uint_as_float(s1[i]);
-    if constexpr (MASKED) {
-      const int ca = col0 + i, cb = col0 + 32 + i;
-      if (!(ca <= lim_hi && ca > lim_lo)) a = -INFINITY;
-      if (!(cb <= lim_hi && cb > lim_lo)) b = -INFINITY;
-    }
-    acc[i & 3] = fmaxf(acc[i & 3], fmaxf(a, b));
-  }
+  for (int i = 0; i < 32; ++i) acc[i & 3] = max3(acc[i & 3], __uint_as_float(s0[i]), __uint_as_float(s1[i]));
   return fmaxf(fmaxf(acc[0], acc[1]), fmaxf(acc[2], acc[3]));
+}
+
+// Scores of hidden keys (column > lim_hi or <= lim_lo) become -inf: they then lose every maximum and
+// their exponentials are exactly 0.  Only tiles that touch the causal diagonal or the window's edge
+// come here, so the two passes above exist once, without the masks.
+__device__ __forceinline__ void mask_quarter(uint32_t (&s)[32], int col0, int lim_hi, int lim_lo) {
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const int col = col0 + i;
+    if (!(col <= lim_hi && col > lim_lo)) s[i] = 0xff800000u;
+  }
 }
 
 template <int D>
@@ -181,6 +210,7 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   uint64_t* p_lo = s_full + 2;
   uint64_t* p_hi = p_lo + 2;
   uint64_t* pv_done = p_hi + 2;
+  uint64_t* turn = pv_done + 2;                            // [group][warp in group]: the exponential unit's turn
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + S::kNumBars);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -242,6 +272,7 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       mbar_init(&p_hi[i], 4);
       mbar_init(&pv_done[i], 1);
     }
+    for (int i = 0; i < 8; ++i) mbar_init(&turn[i], 1);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -257,25 +288,30 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 
   if (warp == 8) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // All 32 lanes run the control flow, so that addresses and descriptors are warp-uniform values;
+    // one elected lane executes the MMAs and commits.
+    {
+      const uint32_t on = elect_one();
       constexpr uint32_t idesc_qk = make_idesc(0, 0, kAM, kAN);
       constexpr uint32_t idesc_pv = make_idesc(0, 0, kAM, D, 0, 1);     // A = P from TMEM (K-major), B = V, N-major
       const uint32_t sq = smem_u32(smem + S::kQ);
       auto issue_qk = [&](int s, uint32_t sk) {
 #pragma unroll
         for (int k = 0; k < D / 32; ++k)
-          tc_mma_f8(tmem_base + s * kAN, make_sdesc(sq + s * S::kTile + k * 32, 16, kSbo, kSwz),
-                    make_sdesc(sk + k * 32, 16, kSbo, kSwz), idesc_qk, k != 0);
-        tc_commit(&s_full[s]);
+          tc_mma_f8_if(on, tmem_base + s * kAN, make_sdesc(sq + s * S::kTile + k * 32, 16, kSbo, kSwz),
+                       make_sdesc(sk + k * 32, 16, kSbo, kSwz), idesc_qk, k != 0);
+        tc_commit_if(on, &s_full[s]);
       };
       // keys [64 half, 64 half + 64) of the tile: P columns [16 half, +16) of the sub-tile's S, 8 per MMA
       auto issue_pv_half = [&](int s, uint32_t sv, int half, bool first) {
 #pragma unroll
         for (int k = 2 * half; k < 2 * half + 2; ++k)
-          tc_mma_f8_ts(tmem_base + 2 * kAN + s * kAN, tmem_base + s * kAN + k * 8,
-                       make_sdesc(sv + k * 32 * D, 16, kSbo, kSwz), idesc_pv, !(first && k == 0));
+          tc_mma_f8_ts_if(on, tmem_base + 2 * kAN + s * kAN, tmem_base + s * kAN + k * 8,
+                          make_sdesc(sv + k * 32 * D, 16, kSbo, kSwz), idesc_pv, !(first && k == 0));
       };
+      PROF_DECL;
       bool ok = mbar_wait(q_full, 0) && mbar_wait(&kv_full[0], 0);
+      PROF_MARK(0);
       if (ok) {
         tc_fence_after();
         const uint32_t sk0 = smem_u32(smem + S::kKV);
@@ -294,16 +330,22 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 #pragma unroll
         for (int s = 0; s < 2; ++s) {
           if (j < n_sub[s]) {
+            PROF_MARK(1);
             if (*abort_flag || !mbar_wait(&p_lo[s], ph)) { ok = false; break; }
+            PROF_MARK(2);
             tc_fence_after();
             issue_pv_half(s, sv, 0, j == 0);
+            PROF_MARK(1);
             if (*abort_flag || !mbar_wait(&p_hi[s], ph)) { ok = false; break; }
+            PROF_MARK(3);
             tc_fence_after();
             issue_pv_half(s, sv, 1, false);
-            if (j == n_sub[s] - 1) tc_commit(&pv_done[s]);
+            if (j == n_sub[s] - 1) tc_commit_if(on, &pv_done[s]);
             if (j + 1 < n_sub[s]) {
               if (!next_ready) {
+                PROF_MARK(1);
                 if (*abort_flag || !mbar_wait(&kv_full[st1], ((j + 1) / kAStages) & 1)) { ok = false; break; }
+                PROF_MARK(4);
                 tc_fence_after();
                 next_ready = true;
               }
@@ -312,9 +354,11 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           }
         }
         if (!ok) break;
-        tc_commit(&kv_empty[st]);
+        tc_commit_if(on, &kv_empty[st]);
       }
-      if (!ok) { *abort_flag = 1; report_error(p.status, MSL_ERR_DEVICE_TIMEOUT); }
+      PROF_MARK(1);
+      if (lane == 0) PROF_FLUSH(8, 5);
+      if (!ok && lane == 0) { *abort_flag = 1; report_error(p.status, MSL_ERR_DEVICE_TIMEOUT); }
     }
   } else if (warp == 9) {
     // ------------------------------------------------------------------ TMA loader
@@ -399,7 +443,7 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     // ------------------------------------------------------------------ softmax / correction / epilogue
     const int sub = warp >> 2;                             // query sub-tile of this group
     const int r = (warp & 3) * 32 + lane;                  // row = TMEM lane
-    const int n_mine = n_sub[sub];
+    const int n_mine = n_sub[sub], n_other = n_sub[sub ^ 1];
     const int tq = r / G, g = r - tq * G;
     const bool row_valid = r < rows_valid[sub];
     const int first_tok = q0 + sub * TQ;
@@ -411,10 +455,12 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     const uint32_t tmem_o = tmem_base + 2 * kAN + sub * kAN + lane_sel;
     float m_run = -INFINITY, l_run = 0.f;                  // l accumulates 2^(8 - kTau) * sum of exponentials
     bool ok = true;
+    PROF_DECL;
     for (int j = 0; j < n_mine && ok; ++j) {
       const uint32_t ph = j & 1;
       const int key0 = (kt_begin + j) * kAN;
       if (*abort_flag || !mbar_wait(&s_full[sub], ph)) { ok = false; break; }
+      PROF_MARK(0);
       tc_fence_after();
       const bool full_tile =
           (key0 + kAN - 1 <= sub_min_qpos) && (!p.window || key0 > max_qpos[sub] - p.window);
@@ -427,61 +473,93 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       tmem_ld32(tmem_s + 64, sc);
       tmem_ld32(tmem_s + 96, sd);
       tmem_ld_wait();
-      // pass 1: row maximum of the raw scores
-      float m_tile = -INFINITY;
-      if (full_tile) {
-        m_tile = row_max_half<false>(sa, sb, 0, lim_hi, lim_lo, m_tile);
-        m_tile = row_max_half<false>(sc, sd, 64, lim_hi, lim_lo, m_tile);
-      } else {
-        m_tile = row_max_half<true>(sa, sb, 0, lim_hi, lim_lo, m_tile);
-        m_tile = row_max_half<true>(sc, sd, 64, lim_hi, lim_lo, m_tile);
+      PROF_MARK(1);
+      if (!full_tile) {
+        mask_quarter(sa, 0, lim_hi, lim_lo);
+        mask_quarter(sb, 32, lim_hi, lim_lo);
+        mask_quarter(sc, 64, lim_hi, lim_lo);
+        mask_quarter(sd, 96, lim_hi, lim_lo);
       }
+      // pass 1: row maximum of the raw scores
+      const float m_tile = row_max_half(sc, sd, row_max_half(sa, sb, -INFINITY));
       // The reference maximum m_run moves only when the tile's maximum exceeds it by more than kTau
       // (log2 units): the exponentials then stay below 2^kTau, P = 2^(8 - kTau) * exp2(.) stays within
       // E4M3's range (<= 256), and the rescale of O in TMEM below becomes rare instead of per tile.
       const float m_cand = m_tile * scale_log2;
+      // When one row of the warp has to move, all 32 move to their newest maximum: the rescale below
+      // costs the same for one row as for all, and rows brought up to date do not ask again soon.
+      const bool event = __any_sync(0xffffffffu, m_cand > m_run + kTau || m_run == -INFINITY);
       float corr = 1.0f;
-      if (m_cand > m_run + kTau || m_run == -INFINITY) {
+      if (event) {
         const float m_new = fmaxf(m_run, m_cand);
         corr = ex2_approx(m_run - ((m_new == -INFINITY) ? 0.f : m_new));   // 0 when m_run = -inf
         m_run = m_new;
       }
       const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
-      // S(j) is ready only after P V(j-1) has finished (the tensor pipe ran it first), so O may be
-      // rescaled and the P columns overwritten without another wait.
-      if (j > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
-#pragma unroll 1
-        for (int c = 0; c < D; c += 16) {
-          uint32_t o[16];
-          tmem_ld16(tmem_o + c, o);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
-          tmem_st16(tmem_o + c, o);
-        }
+      const bool resc = j > 0 && event;                     // warp-uniform
+      PROF_MARK(2);
+      // The two warps that share a scheduler (one of each group) take turns at the exponential pass:
+      // alone, a warp keeps the ex2 unit busy; together they would run the pass in lockstep at half
+      // speed each and then sit idle together while their next S tiles are formed.  Order: group 0
+      // tile 0, group 1 tile 0, group 0 tile 1, ...; a turn is skipped where the partner has no such tile.
+      if (sub == 0 ? (j >= 1 && j - 1 < n_other) : (j < n_other)) {
+        if (*abort_flag || !mbar_wait(&turn[sub * 4 + (warp & 3)], (sub == 0 ? j - 1 : j) & 1)) { ok = false; break; }
       }
-      l_run *= corr;
-      // pass 2: P = 2^(8 - kTau) * exp2(s * scale - m) as E4M3 into TMEM, row sum in fp32; the first
-      // 64 keys are published before the last 64 are formed
+      PROF_MARK(3);
+      // pass 2: P = 2^(8 - kTau) * exp2(s * scale - m) as E4M3 into TMEM, row sum in fp32.  On a tile
+      // without a rescale the first 64 keys are published before the last 64 are formed.
       const float neg_m = (8.0f - kTau) - m_use;
       float l_tile = 0.f;
-      uint32_t pk[16];
-      if (full_tile) softmax_half<false>(sa, sb, scale_log2, neg_m, 0, lim_hi, lim_lo, l_tile, pk);
-      else softmax_half<true>(sa, sb, scale_log2, neg_m, 0, lim_hi, lim_lo, l_tile, pk);
-      tmem_st16(tmem_s, pk);
-      tmem_st_wait();                                       // also covers the rescaled O
+      uint32_t pk[16], pk2[16];
+      softmax_half(sa, sb, scale_log2, neg_m, l_tile, pk);
+      if (!resc) {
+        tmem_st16(tmem_s, pk);
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_lo[sub]);
+      }
+      softmax_half(sc, sd, scale_log2, neg_m, l_tile, pk2);
+      // hand the turn to the partner warp: its tile j (from group 0) or tile j + 1 (from group 1)
+      __syncwarp();
+      if (lane == 0 && (sub == 0 ? (j < n_other) : (j + 1 < n_other))) mbar_arrive(&turn[(sub ^ 1) * 4 + (warp & 3)]);
+      PROF_MARK(4);
+      if (resc) {
+        // O moves to the new maximum before any of this tile's P is used.  S(j) was ready only after
+        // P V(j-1) had finished (the tensor pipe ran it first), so O is quiet; and the scores are no
+        // longer needed, so their registers carry O through in wide pieces.
+#pragma unroll
+        for (int c = 0; c < D; c += 64) {
+          uint32_t oa[32], ob[32];
+          tmem_ld32(tmem_o + c, oa);
+          tmem_ld32(tmem_o + c + 32, ob);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            oa[i] = __float_as_uint(__uint_as_float(oa[i]) * corr);
+            ob[i] = __float_as_uint(__uint_as_float(ob[i]) * corr);
+          }
+          tmem_st32(tmem_o + c, oa);
+          tmem_st32(tmem_o + c + 32, ob);
+        }
+        tmem_st16(tmem_s, pk);
+      }
+      PROF_MARK(5);
+      tmem_st16(tmem_s + 16, pk2);
+      tmem_st_wait();                                       // P and a rescaled O
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_lo[sub]);
-      if (full_tile) softmax_half<false>(sc, sd, scale_log2, neg_m, 64, lim_hi, lim_lo, l_tile, pk);
-      else softmax_half<true>(sc, sd, scale_log2, neg_m, 64, lim_hi, lim_lo, l_tile, pk);
-      tmem_st16(tmem_s + 16, pk);
-      tmem_st_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&p_hi[sub]);
-      l_run += l_tile;
+      if (lane == 0) {
+        if (resc) mbar_arrive(&p_lo[sub]);
+        mbar_arrive(&p_hi[sub]);
+      }
+      PROF_MARK(6);
+      l_run = l_run * corr + l_tile;
     }
+#ifdef MSL_ATTN_PROF
+    if (threadIdx.x == 0) { prof_acc[7] = n_mine; PROF_FLUSH(0, 8); }
+    if (threadIdx.x == 128) { prof_acc[7] = n_mine; PROF_FLUSH(16, 8); }
+#endif
     // ---------------------------------------------------------------- epilogue
     if (ok && n_mine > 0) {
       if (*abort_flag || !mbar_wait(&pv_done[sub], 0)) ok = false;     // committed once, behind the last P V
@@ -736,3 +814,14 @@ extern "C" int msl_attention_fp8_split(const void* q8, const void* k_cache, cons
                          softmax_scale, batch, max_q_len, tokens, hq, hkv, head_dim, page_size, window, cache_rows,
                          out, ld_out, gate, ld_gate, kv_splits, workspace, status, stream);
 }
+
+#ifdef MSL_ATTN_PROF
+extern "C" int msl_debug_attn_prof(unsigned long long* out, int reset) {
+  if (cudaMemcpyFromSymbol(out, msl::g_attn_prof, sizeof(msl::g_attn_prof)) != cudaSuccess) return MSL_ERR_CUDA;
+  if (reset) {
+    unsigned long long zero[32] = {};
+    if (cudaMemcpyToSymbol(msl::g_attn_prof, zero, sizeof(zero)) != cudaSuccess) return MSL_ERR_CUDA;
+  }
+  return MSL_OK;
+}
+#endif

@@ -187,8 +187,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer (one elected lane)
-    if (lane == 0) {
+    // ------------------------------------------------------------ MMA issuer
+    // All 32 lanes run the control flow, so that addresses and descriptors are warp-uniform values; one
+    // elected lane executes the MMAs and commits.
+    {
+      const uint32_t on = elect_one();
       constexpr uint32_t idesc = make_idesc(1, 1, kBM, BN);
       uint32_t it = 0, tile_i = 0;
       bool ok = true;
@@ -214,14 +217,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             const uint64_t db = make_sdesc(sb + k16 * 32, 16, 1024, 2);
 #pragma unroll
             for (int sub = 0; sub < SUBS; ++sub)
-              tc_mma_f16(d_tmem + sub * BN, make_sdesc(sa + sub * S::kSubBytes + k16 * 32, 16, 1024, 2), db, idesc,
-                         kb != kb_lo || k16 != 0);
+              tc_mma_f16_if(on, d_tmem + sub * BN, make_sdesc(sa + sub * S::kSubBytes + k16 * 32, 16, 1024, 2), db,
+                            idesc, kb != kb_lo || k16 != 0);
           }
-          tc_commit(&empty[s]);          // frees the stage once these MMAs have read it
+          tc_commit_if(on, &empty[s]);   // frees the stage once these MMAs have read it
         }
-        if (ok) tc_commit(&tmem_full[acc]);
+        if (ok) tc_commit_if(on, &tmem_full[acc]);
       }
-      if (!ok) {
+      if (!ok && lane == 0) {
         *abort_flag = 1;
         report_error(p.status, MSL_ERR_DEVICE_TIMEOUT);
       }

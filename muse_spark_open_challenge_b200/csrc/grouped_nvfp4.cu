@@ -236,7 +236,10 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // All 32 lanes run the control flow, so that addresses and descriptors are warp-uniform values; one
+    // elected lane executes the MMAs and commits.
+    {
+      const uint32_t on = elect_one();
       constexpr uint32_t idesc = make_idesc(1, 1, 128, kGN);
       uint32_t it = 0, tile_i = 0;
       bool ok = true;
@@ -261,16 +264,16 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
 #pragma unroll
           for (int k16 = 0; k16 < kGK / 16; ++k16) {
             const uint64_t da = make_sdesc(sa + k16 * 32, 16, 1024, 2), db = make_sdesc(sb + k16 * 32, 16, 1024, 2);
-            tc_mma_f16(d_tmem, da, db, idesc, (kb | k16) != 0);
+            tc_mma_f16_if(on, d_tmem, da, db, idesc, (kb | k16) != 0);
             if (WIDE && nsub > 1)
-              tc_mma_f16(d_tmem + kGN, make_sdesc(sa + S::kSubBytes + k16 * 32, 16, 1024, 2), db, idesc,
-                         (kb | k16) != 0);
+              tc_mma_f16_if(on, d_tmem + kGN, make_sdesc(sa + S::kSubBytes + k16 * 32, 16, 1024, 2), db, idesc,
+                            (kb | k16) != 0);
           }
-          tc_commit(&empty[s]);
+          tc_commit_if(on, &empty[s]);
         }
-        if (ok) tc_commit(&tmem_full[acc]);
+        if (ok) tc_commit_if(on, &tmem_full[acc]);
       }
-      if (!ok) { *abort_flag = 1; report_error(p.status, MSL_ERR_DEVICE_TIMEOUT); }
+      if (!ok && lane == 0) { *abort_flag = 1; report_error(p.status, MSL_ERR_DEVICE_TIMEOUT); }
     }
   } else if (warp < 6) {
     // ------------------------------------------------------------ epilogue

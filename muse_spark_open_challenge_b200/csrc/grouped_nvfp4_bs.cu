@@ -71,19 +71,21 @@ __device__ __forceinline__ void bs_bulk_load(void* dst, const void* src, uint32_
                ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
 // One scale atom shared memory -> 4 TMEM columns (all four lane quarters).
-__device__ __forceinline__ void tc_cp_scales(uint32_t taddr, uint32_t saddr) {
+// `on`: predicate of the elected lane; the other lanes run the same control flow and skip the instruction.
+__device__ __forceinline__ void tc_cp_scales(uint32_t on, uint32_t taddr, uint32_t saddr) {
   // no swizzle; rows of 16 bytes, 8-row groups 128 bytes apart
   const uint64_t desc = make_sdesc(saddr, 16, 128, 0);
-  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+  asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %2, 0;\n\t"
+               "@q tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;\n\t}" ::"r"(taddr), "l"(desc), "r"(on) : "memory");
 }
 // D[tmem] (+)= (A (*) SFA) * (B (*) SFB)^T, e2m1 operands packed two per byte, UE4M3 scales of 16-element
 // blocks in TMEM, K = 64 per instruction.
-__device__ __forceinline__ void tc_mma_nvf4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                            uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+__device__ __forceinline__ void tc_mma_nvf4(uint32_t on, uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                            uint32_t idesc, uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
   asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %4, 0;\n\tsetp.ne.b32 q, %7, 0;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem), "r"(on)
       : "memory");
 }
 // Instruction descriptor of the block-scaled kinds: [7,10) A format, [10,13) B format (1 = e2m1),
@@ -163,7 +165,10 @@ grouped_nvfp4_bs_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_c
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // All 32 lanes run the control flow, so that addresses and descriptors are warp-uniform values; one
+    // elected lane executes the copies, MMAs and commits.
+    {
+      const uint32_t on = elect_one();
       constexpr uint32_t idesc = make_idesc_nvf4(kBsM, kBsN);
       const uint32_t sfa_t = tmem_base + kBsN, sfb_t = tmem_base + kBsN + 16;
       uint32_t it = 0, tile_i = 0;
@@ -184,19 +189,19 @@ grouped_nvfp4_bs_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_c
           // stage overwrite the TMEM scale columns only after the previous stage's MMAs have read them.
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks) {
-            tc_cp_scales(sfa_t + 4 * ks, ssfa + ks * kAtom);
-            tc_cp_scales(sfb_t + 8 * ks, ssfb + (2 * ks) * kAtom);
-            tc_cp_scales(sfb_t + 8 * ks + 4, ssfb + (2 * ks + 1) * kAtom);
+            tc_cp_scales(on, sfa_t + 4 * ks, ssfa + ks * kAtom);
+            tc_cp_scales(on, sfb_t + 8 * ks, ssfb + (2 * ks) * kAtom);
+            tc_cp_scales(on, sfb_t + 8 * ks + 4, ssfb + (2 * ks + 1) * kAtom);
           }
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks)
-            tc_mma_nvf4(d_tmem, make_sdesc(sa + ks * 32, 16, 1024, 2), make_sdesc(sb + ks * 32, 16, 1024, 2), idesc,
+            tc_mma_nvf4(on, d_tmem, make_sdesc(sa + ks * 32, 16, 1024, 2), make_sdesc(sb + ks * 32, 16, 1024, 2), idesc,
                         sfa_t + 4 * ks, sfb_t + 8 * ks, (kb | ks) != 0);
-          tc_commit(&empty[s]);
+          tc_commit_if(on, &empty[s]);
         }
-        if (ok) tc_commit(&tmem_full[acc]);
+        if (ok) tc_commit_if(on, &tmem_full[acc]);
       }
-      if (!ok) { *abort_flag = 1; report_error(p.status, MSL_ERR_DEVICE_TIMEOUT); }
+      if (!ok && lane == 0) { *abort_flag = 1; report_error(p.status, MSL_ERR_DEVICE_TIMEOUT); }
     }
   } else {
     // ------------------------------------------------------------ epilogue
