@@ -56,7 +56,10 @@
 // part of the exponentials as a cubic on the FMA pipe (0.60 ms with turns, 0.60 ms without), S read
 // from TMEM a second time for the exponential pass instead of being held in 128 registers (0.67 ms),
 // mbarrier waits with a suspend-time hint (no change), tau = 6 (0.568 ms, not kept: less range below
-// the reference maximum).
+// the reference maximum); at head_dim 64, where TMEM has room, P in columns of its own with Q K^T(j+1)
+// issued as soon as S(j) is in registers (the wait for S shrinks from 800 to 470 cycles, the exponential
+// pass grows by as much: 0.54 against 0.50 ms); no turns but a quarter of the exponentials as a cubic
+// (0.582 ms, and 0.503 ms at head_dim 64: the same as the turns).
 #include "msl_common.cuh"
 #include "msl_host.h"
 

@@ -96,8 +96,6 @@ class ExpertParallel:
             raise ValueError("the expert count must divide evenly over the ranks")
         if st["n_local"] != n_experts // world:
             raise ValueError("state holds a different number of local experts than n_experts / world")
-        if st.get("experts_nvfp4"):
-            raise ValueError("the NVFP4-activation expert mode is a single-GPU option")
         self.world, self.rank, self.n_experts, self.group = world, rank, n_experts, group
         self.zero = torch.zeros(1, dtype=torch.int32, device=st["device"])
         self.counts = torch.zeros(n_experts, dtype=torch.int32, device=st["device"])
@@ -223,12 +221,7 @@ def moe_stage_peer(h, data, st, ctx: ExpertParallel):
         rowmap.record_stream(main)             # allocated on the side stream, read on the main one
     ops.peer_barrier(peer.flag_ptrs.data_ptr(), ctx.rank, ctx.world, status)      # all rows have landed
     layer._mark(st, "barrier_rows")
-    ops.grouped_gemm_nvfp4(peer.slab, st["w13_q"], st["w13_s"], st["w13_gs"], ctx.group_offsets, ctx.recv_i,
-                           st["inter"], True, status)
-    layer._mark(st, "experts_gate_up")
-    ops.grouped_gemm_nvfp4(ctx.recv_i, st["w2_q"], st["w2_s"], st["w2_gs"], ctx.group_offsets, peer.slab,
-                           st["moe_width"], False, status)
-    layer._mark(st, "experts_down")
+    layer.expert_gemms(peer.slab, ctx.recv_i, ctx.group_offsets, st)      # x -> inter -> y, in place in the slab
     st["offsets"][-1:] = ctx.group_offsets[-1:]             # rows computed on this rank (for the bench's FLOP count)
     ops.peer_barrier(peer.flag_ptrs.data_ptr(), ctx.rank, ctx.world, status)      # all expert outputs are written
     layer._mark(st, "barrier_outputs")
@@ -280,12 +273,7 @@ def moe_stage(h, data, st, ctx: ExpertParallel):
     main.wait_stream(ctx.side)
     layer._mark(st, "a2a_dispatch")
     rows = max(plan.recv_rows, 1)
-    ops.grouped_gemm_nvfp4(recv_x[:rows], st["w13_q"], st["w13_s"], st["w13_gs"], plan.group_offsets, recv_i[:rows],
-                           st["inter"], True, status)
-    layer._mark(st, "experts_gate_up")
-    ops.grouped_gemm_nvfp4(recv_i[:rows], st["w2_q"], st["w2_s"], st["w2_gs"], plan.group_offsets, recv_x[:rows],
-                           st["moe_width"], False, status)
-    layer._mark(st, "experts_down")
+    layer.expert_gemms(recv_x[:rows], recv_i[:rows], plan.group_offsets, st)
     st["offsets"][-1:] = plan.group_offsets[-1:]            # rows computed on this rank (for the bench's FLOP count)
     exchange_rows(recv_x[:plan.recv_rows], tokens * top_k, plan.recv_splits, plan.send_splits, out=send_x,
                   group=ctx.group)

@@ -250,13 +250,14 @@ def expert_gemms(slab_x, slab_i, offsets, st):
             # buffers sized for the scratch capacity, grow-only like the slabs they mirror
             rows, k = slab.shape
             bufs = st.get(key)
-            if bufs is None or bufs[0].shape[0] < st["cap"]:
+            cap = max(st.get("cap", 0), rows)          # expert parallel: the slab is the caller's, not st's
+            if bufs is None or bufs[0].shape[0] < cap or bufs[3] != offsets.numel():
                 st.setdefault("retired", []).append(bufs)
-                cap, dev = st["cap"], st["device"]
+                dev = st["device"]
                 tiles = int(_lib_row_tiles(cap, offsets.numel() - 1))
                 bufs = (torch.empty((cap, k // 2), dtype=torch.uint8, device=dev),
                         torch.zeros((tiles, k // 256, 4, 512), dtype=torch.uint8, device=dev),
-                        torch.ones(cap, dtype=torch.float32, device=dev))
+                        torch.ones(cap, dtype=torch.float32, device=dev), offsets.numel())
                 st[key] = bufs
             return ops.nvfp4_bs_quantize(slab, offsets, out=(bufs[0][:rows], bufs[1], bufs[2][:rows]))
 

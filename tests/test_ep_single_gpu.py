@@ -58,6 +58,31 @@ def test_peer_transport_with_one_rank_matches_the_oracle_and_the_plain_layer():
     assert int(ctx.peer.flags[1]) == 9                   # three barriers per layer, three layers
 
 
+def test_nvfp4_activation_mode_under_expert_parallelism_equals_the_plain_layer():
+    """The opt-in NVFP4 x NVFP4 expert mode through both transports' expert stage (one rank, peer
+    transport): the rows reach the same quantiser and block-scaled GEMMs in the same order as in the plain
+    layer, so routing is identical and outputs agree to fp32 rounding of the two combine kernels."""
+    from muse_spark_open_challenge_b200 import ep, layer, synth
+    shape, weights = _small()
+    data = synth.make_input(shape, [150, 77], [30, 0], seed=21, page=64, kv_scale=0.5)
+    st = layer.prepare(to_device(weights, "cuda"), experts_nvfp4=True)
+    ctx = ep.ExpertParallel(st, 1, 0, shape.n_experts)
+    ep.enable_peer(ctx, st, max_tokens=227, top_k=shape.top_k, guard_rows=64)
+    ctx.peer.guard.fill_(0x5A)
+    out = None
+    for _ in range(2):
+        out = ep.kernel_fn(to_device(data, "cuda"), st, ctx)
+    torch.cuda.synchronize()
+    layer.check_status(st)
+    ref = layer.kernel_fn(to_device(data, "cuda"), layer.prepare(to_device(weights, "cuda"), experts_nvfp4=True))
+    torch.cuda.synchronize()
+    assert torch.equal(out[2], ref[2])
+    # the plain layer sums the expert rows and applies the FFN boundary in one kernel, in fp32; here the sum
+    # passes through a bf16 row on its way to the boundary
+    assert L.relative_l2(out[1], ref[1]) < 5e-5 and L.relative_l2(out[0].float(), ref[0].float()) < 2e-3
+    assert bool((ctx.peer.guard == 0x5A).all())
+
+
 def test_peer_slab_overflow_is_reported_and_nothing_lands_behind_the_slab():
     """A slab (and intermediate buffer) physically sized to a capacity smaller than the routing needs:
     the plan reports it, the rows that do not fit are dropped, and the guard rows directly behind
