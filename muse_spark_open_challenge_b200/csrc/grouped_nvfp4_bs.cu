@@ -22,6 +22,16 @@
 // TMEM: accumulator 0 at columns [0, 192), scales at [192, 240), accumulator 1 at [256, 448): the epilogue
 // of one tile overlaps the main loop of the next.  Every mbarrier wait is bounded.
 //
+// What bounds it (131072 rows x 3072 x 4096: 1.04 ms = 3160 TFLOP/s, 0.36 of the instruction's measured
+// ceiling): a stage of K = 256 takes 1120 cycles against 400 of MMA time.  Two things meet there.  The tensor
+// pipe runs the 12 scale copies and the 4 MMAs of a stage in order and no instruction on it takes less than
+// about 57 cycles (12 x 57 + 4 x 100 = 1084).  And the loads are bound by latency, not by L2 bandwidth: with
+// 4 x 46 KB in flight per SM and 1.8 us from issue to arrival the SMs together receive 11.5 TB/s (a probe that
+// streams an L2-resident buffer by bulk copies with 128 KB in flight per SM reaches 9.6 TB/s; by plain 16-byte
+// loads from 2048 threads per SM, 17 TB/s).  Leaving out 11 of the 12 copies (wrong results, timing only)
+// changed nothing, tiles of 256 rows with three 64 KB stages and one accumulator set ran at 2135 TFLOP/s.
+// Before the issuer ran warp-uniform (one elected lane instead of a one-lane branch) it was 2294 TFLOP/s.
+//
 // Scale layout ("atom", 512 bytes = 128 rows x 4 scales of one K = 64 step): byte (r % 32) * 16 +
 // (r / 32) * 4 + j holds scale j of row r; tcgen05.cp 32x128b.warpx4 copies an atom into 4 TMEM columns
 // of all four lane quarters.  Weight scales are re-tiled once at load time (msl_nvfp4_bs_sf_repack);
