@@ -64,48 +64,69 @@ __device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int
   nt = r / gm;
 }
 
-template <int BN, int OUT>
-__device__ __forceinline__ void store_chunk(const GemmArgs& p, int row, int col0, const uint32_t (&acc)[32],
-                                            const uint32_t (&acc2)[32]) {
-  // One thread owns 32 consecutive output columns of one row.
+__device__ __forceinline__ void st_global_v8(void* dst, const uint32_t (&w)[8]) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst), "r"(w[0]), "r"(w[1]), "r"(w[2]),
+               "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
+}
+
+// SiLU(g) * u = g * u / (1 + exp(-g)) with the fast reciprocal: 2 ulp, far below the bf16 it is rounded to.
+// For g < -88 the denominator is +inf and the quotient 0, the limit.
+__device__ __forceinline__ float silu_mul(float g, float u) {
+  return __fdividef(g * u, 1.0f + __expf(-g));
+}
+
+template <int BN, int OUT, int CH>
+__device__ __forceinline__ void store_chunk(const GemmArgs& p, int row, int col0, const uint32_t (&acc)[CH],
+                                            const uint32_t (&acc2)[CH], bool wide_ok) {
+  // One thread owns CH consecutive output columns of one row; 32-byte stores where the output's base and
+  // pitch allow them (every lane then writes whole sectors of its own row).
   if (row >= p.m) return;
   if constexpr (OUT == MSL_OUT_F32) {
     float* dst = reinterpret_cast<float*>(p.c) + static_cast<int64_t>(row) * p.ldc + col0;
-    if (col0 + 32 <= p.n && (p.ldc & 3) == 0) {
+    if (col0 + CH <= p.n && (p.ldc & 3) == 0) {
 #pragma unroll
-      for (int j = 0; j < 32; j += 4) {
-        float4 v = make_float4(__uint_as_float(acc[j]) * p.alpha, __uint_as_float(acc[j + 1]) * p.alpha,
-                               __uint_as_float(acc[j + 2]) * p.alpha, __uint_as_float(acc[j + 3]) * p.alpha);
-        *reinterpret_cast<float4*>(dst + j) = v;
+      for (int j = 0; j < CH; j += 8) {
+        uint32_t w[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) w[i] = __float_as_uint(__uint_as_float(acc[j + i]) * p.alpha);
+        if (wide_ok) {
+          st_global_v8(dst + j, w);
+        } else {
+          *reinterpret_cast<uint4*>(dst + j) = make_uint4(w[0], w[1], w[2], w[3]);
+          *reinterpret_cast<uint4*>(dst + j + 4) = make_uint4(w[4], w[5], w[6], w[7]);
+        }
       }
     } else {
-      for (int j = 0; j < 32; ++j)
+      for (int j = 0; j < CH; ++j)
         if (col0 + j < p.n) dst[j] = __uint_as_float(acc[j]) * p.alpha;
     }
   } else {
-    float v[32];
+    float v[CH];
     if constexpr (OUT == MSL_OUT_SWIGLU_BF16) {
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const float g = __uint_as_float(acc[j]) * p.alpha;
-        const float u = __uint_as_float(acc2[j]) * p.alpha;
-        v[j] = g / (1.0f + __expf(-g)) * u;
-      }
+      for (int j = 0; j < CH; ++j)
+        v[j] = silu_mul(__uint_as_float(acc[j]) * p.alpha, __uint_as_float(acc2[j]) * p.alpha);
     } else {
 #pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(acc[j]) * p.alpha;
+      for (int j = 0; j < CH; ++j) v[j] = __uint_as_float(acc[j]) * p.alpha;
     }
     const int n_out = (OUT == MSL_OUT_SWIGLU_BF16) ? p.n / 2 : p.n;
     __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.c) + static_cast<int64_t>(row) * p.ldc + col0;
-    if (col0 + 32 <= n_out && (p.ldc & 7) == 0) {
+    if (col0 + CH <= n_out && (p.ldc & 7) == 0) {
 #pragma unroll
-      for (int j = 0; j < 32; j += 8) {
-        uint4 q = make_uint4(pack_bf16x2(v[j], v[j + 1]), pack_bf16x2(v[j + 2], v[j + 3]),
-                             pack_bf16x2(v[j + 4], v[j + 5]), pack_bf16x2(v[j + 6], v[j + 7]));
-        *reinterpret_cast<uint4*>(dst + j) = q;
+      for (int j = 0; j < CH; j += 16) {
+        uint32_t w[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) w[i] = pack_bf16x2(v[j + 2 * i], v[j + 2 * i + 1]);
+        if (wide_ok) {
+          st_global_v8(dst + j, w);
+        } else {
+          *reinterpret_cast<uint4*>(dst + j) = make_uint4(w[0], w[1], w[2], w[3]);
+          *reinterpret_cast<uint4*>(dst + j + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+        }
       }
     } else {
-      for (int j = 0; j < 32; ++j)
+      for (int j = 0; j < CH; ++j)
         if (col0 + j < n_out) dst[j] = __float2bfloat16(v[j]);
     }
   }
@@ -234,6 +255,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     const int quarter = warp & 3;            // TMEM lanes [32*quarter, 32*quarter + 32)
     uint32_t tile_i = 0;
     bool ok = true;
+    const bool wide_ok = ((reinterpret_cast<uintptr_t>(p.c) | static_cast<uintptr_t>(p.ldc * (OUT == MSL_OUT_F32 ? 4 : 2)) |
+                           (OUT == MSL_OUT_F32 ? static_cast<uintptr_t>(p.split_stride * 4) : 0)) & 31) == 0;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_i) {
       int mt, nt;
       tile_coords(t % mn_tiles, m_tiles, n_tiles, mt, nt);
@@ -249,23 +272,36 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       const int row = mt * kTileM + sub * kBM + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + (acc + sub) * BN + (static_cast<uint32_t>(quarter * 32) << 16);
       if (mt * kTileM + sub * kBM >= p.m) break;             // a whole sub-tile past the last row
+      // The TMEM loads of a chunk are issued one chunk ahead of the arithmetic and the stores.
       if constexpr (OUT == MSL_OUT_SWIGLU_BF16) {
         // Columns [0, BN/2) of the tile are gate rows, [BN/2, BN) the matching up rows.
+        uint32_t g[2][16], u[2][16];
+        tmem_ld16(taddr, g[0]);
+        tmem_ld16(taddr + BN / 2, u[0]);
 #pragma unroll 1
         for (int c = 0; c < BN / 2; c += 32) {
-          uint32_t g[32], u[32];
-          tmem_ld32(taddr + c, g);
-          tmem_ld32(taddr + BN / 2 + c, u);
           tmem_ld_wait();
-          store_chunk<BN, OUT>(p, row, nt * (BN / 2) + c, g, u);
+          tmem_ld16(taddr + c + 16, g[1]);
+          tmem_ld16(taddr + BN / 2 + c + 16, u[1]);
+          store_chunk<BN, OUT, 16>(p, row, nt * (BN / 2) + c, g[0], u[0], wide_ok);
+          tmem_ld_wait();
+          if (c + 32 < BN / 2) {
+            tmem_ld16(taddr + c + 32, g[0]);
+            tmem_ld16(taddr + BN / 2 + c + 32, u[0]);
+          }
+          store_chunk<BN, OUT, 16>(p, row, nt * (BN / 2) + c + 16, g[1], u[1], wide_ok);
         }
       } else {
+        uint32_t v[2][32];
+        tmem_ld32(taddr, v[0]);
 #pragma unroll 1
-        for (int c = 0; c < BN; c += 32) {
-          uint32_t v[32];
-          tmem_ld32(taddr + c, v);
+        for (int c = 0; c < BN; c += 64) {
           tmem_ld_wait();
-          store_chunk<BN, OUT>(q, row, nt * BN + c, v, v);
+          tmem_ld32(taddr + c + 32, v[1]);
+          store_chunk<BN, OUT, 32>(q, row, nt * BN + c, v[0], v[0], wide_ok);
+          tmem_ld_wait();
+          if (c + 64 < BN) tmem_ld32(taddr + c + 64, v[0]);
+          store_chunk<BN, OUT, 32>(q, row, nt * BN + c + 32, v[1], v[1], wide_ok);
         }
       }
       }

@@ -10,7 +10,10 @@
 // One persistent CTA per SM, 448 threads:
 //   warp 0      TMA producer: activation tile 128 rows x 64 k (bf16, 128-byte swizzle)
 //   warp 1      TMEM allocation + tcgen05.mma issue (M=128 tokens, N=256 weight rows, K=16)
-//   warps 2-5   epilogue (TMEM -> registers -> global)
+//   warps 2-5   epilogue (TMEM -> registers -> global): TMEM loads issued one chunk ahead of the arithmetic,
+//               SiLU with the fast reciprocal, 32-byte stores.  With 256-row tiles it does not overlap the
+//               next tile's main loop (one accumulator set), so its length counts: it took 29.6 k cycles
+//               per gate/up tile (main loop 74 k) before these three changes and takes 8.7 k now
 //   warps 6-13  weight producers in two groups of 4 warps that take alternate stages: each thread
 //               dequantises two weight rows of its stage (2 x (64 codes + 4 block scales) -> 128 bf16)
 //               straight into the swizzled B tile in shared memory, while the codes of its next stage
@@ -43,10 +46,10 @@ constexpr int kGroups = 2;                    // producer groups, each taking ev
 constexpr int kGroupThreads = kProducers / kGroups;
 
 // Tile geometries (MODE):
-//   kNarrow  128 token rows x 256 weight rows per tile, 4 stages, two accumulator sets (the epilogue of
-//            one tile overlaps the main loop of the next).  For calls whose groups are small.
+//   kNarrow  128 token rows x 256 weight rows per tile, two accumulator sets (the epilogue of one tile
+//            overlaps the main loop of the next).  For calls whose groups are small.
 //   kWide    256 token rows (two 128-row MMAs per K step sharing one dequantised weight tile) x 256
-//            weight rows, 3 stages, one accumulator set (both sub-tiles fill the 512 TMEM columns).
+//            weight rows, one accumulator set (both sub-tiles fill the 512 TMEM columns).
 //            Halves the weight bytes staged, dequantised and fetched per FLOP.
 // (A third geometry, two CTAs of a cluster sharing one M=256 MMA with cta_group::2, each dequantising
 // half of the weight tile, was built and measured slower, 820 against 1012 TFLOP/s: not kept.)
@@ -57,18 +60,37 @@ struct GroupedCfg {
   static constexpr int kSubs = WIDE ? 2 : 1;                 // 128-row MMAs per K step in one CTA
   static constexpr int kTileM = WIDE ? 256 : 128;            // token rows per tile
   static constexpr int kBRows = 256;                         // weight rows dequantised per stage
-  static constexpr int kStages = WIDE ? 3 : 4;
+  // The activation tiles (loaded by TMA) and the weight tiles (dequantised from registers that were
+  // loaded two stages earlier) live in rings of their own, so that their depths can differ.  Measured
+  // on 128 groups x 1024 rows (gate/up): 4 + 3 slots 1440 TFLOP/s, 3 + 4 the same, 5 + 2 about 10 % less
+  // (each producer group needs a slot to fill while the one before it is being multiplied).
+  static constexpr int kAStages = WIDE ? 4 : 6;
+  static constexpr int kBStages = 3;
   static constexpr int kRowsPerThread = kBRows / kGroupThreads;
   static constexpr int kSubBytes = kSubM * kGK * 2;
   static constexpr int kABytes = kSubs * kSubBytes;
   static constexpr int kBBytes = kBRows * kGK * 2;
-  static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kLutOffset = kStages * kStageBytes;           // 256 x u32
+  static constexpr int kBRing = kAStages * kABytes;                  // weight ring behind the activation ring
+  static constexpr int kLutOffset = kBRing + kBStages * kBBytes;     // 256 x u32
   static constexpr int kPrefixOffset = kLutOffset + 1024;            // (kMaxLocal + 1) x int
   static constexpr int kBarOffset = kPrefixOffset + (kMaxLocal + 1) * 4 + 4;
-  static constexpr int kTotal = kBarOffset + (2 * kStages + 4) * 8 + 16;
+  static constexpr int kTotal = kBarOffset + (2 * kAStages + 2 * kBStages + 4) * 8 + 16;
   static_assert(kBarOffset % 8 == 0, "barriers must be 8-byte aligned");
+  static_assert(kTotal <= 232448, "shared memory of one CTA");
 };
+
+// Phase timing for development builds (-DMSL_GROUPED_PROF): cycles summed over all CTAs; read back with
+// msl_debug_grouped_prof.
+#ifdef MSL_GROUPED_PROF
+__device__ unsigned long long g_grouped_prof[32];
+#define GPROF_DECL long long prof_t = clock64(); long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}
+#define GPROF_MARK(i) do { const long long now_ = clock64(); prof_acc[i] += now_ - prof_t; prof_t = now_; } while (0)
+#define GPROF_FLUSH(base, n) do { for (int i_ = 0; i_ < (n); ++i_) atomicAdd(&g_grouped_prof[(base) + i_], (unsigned long long)prof_acc[i_]); } while (0)
+#else
+#define GPROF_DECL do {} while (0)
+#define GPROF_MARK(i) do {} while (0)
+#define GPROF_FLUSH(base, n) do {} while (0)
+#endif
 
 struct GroupedArgs {
   const uint8_t* wq;       // [banks][n_tiles][k_blocks][256 rows][32 bytes]
@@ -118,43 +140,75 @@ __device__ __forceinline__ uint4 dequant8(uint32_t w, uint32_t scale2) {
   return make_uint4(o[0], o[1], o[2], o[3]);
 }
 
+// SiLU(g) * u = g * u / (1 + exp(-g)) with the fast reciprocal: 2 ulp, far below the bf16 it is rounded to.
+// For g < -88 the denominator is +inf and the quotient 0, the limit.
+__device__ __forceinline__ float silu_mul(float g, float u) {
+  return __fdividef(g * u, 1.0f + __expf(-g));
+}
+
 template <bool SWIGLU>
 __device__ __forceinline__ void store_rows(const GroupedArgs& p, const TileInfo& ti, uint32_t taddr, int r,
                                            float alpha) {
-  // One thread owns row r of the tile: 128 accumulator columns -> 128 (or 64 fused) outputs.  Offsets
-  // that run past the slab (a routing that needs more rows than the buffers hold) store nothing.
+  // One thread owns row r of the tile: 256 accumulator columns -> 256 (or 128 fused) outputs, in chunks
+  // whose TMEM loads are issued one chunk ahead of the arithmetic and the stores.  Offsets that run past
+  // the slab (a routing that needs more rows than the buffers hold) store nothing.
   const bool valid = r < ti.rows && static_cast<int64_t>(ti.row0) + r < p.slab_rows;
   __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<int64_t>(ti.row0 + r) * p.ld_out;
+  const bool wide_ok = ((reinterpret_cast<uintptr_t>(p.out) | static_cast<uintptr_t>(p.ld_out * 2)) & 31) == 0;
   constexpr int kOutCols = SWIGLU ? kGN / 2 : kGN;
-#pragma unroll 1
-  for (int c = 0; c < kOutCols; c += 32) {
-    uint32_t a[32], b[32];
-    tmem_ld32(taddr + c, a);
-    if constexpr (SWIGLU) tmem_ld32(taddr + kGN / 2 + c, b);
-    tmem_ld_wait();
-    const int col0 = ti.nt * kOutCols + c;
-    if (valid && col0 < p.n_out) {
-      uint32_t packed[16];
-#pragma unroll
-      for (int j = 0; j < 32; j += 2) {
-        float v0 = __uint_as_float(a[j]) * alpha, v1 = __uint_as_float(a[j + 1]) * alpha;
-        if constexpr (SWIGLU) {
-          const float u0 = __uint_as_float(b[j]) * alpha, u1 = __uint_as_float(b[j + 1]) * alpha;
-          v0 = v0 / (1.0f + __expf(-v0)) * u0;
-          v1 = v1 / (1.0f + __expf(-v1)) * u1;
-        }
-        packed[j / 2] = pack_bf16x2(v0, v1);
-      }
-      if (col0 + 32 <= p.n_out) {
-#pragma unroll
-        for (int j = 0; j < 16; j += 4)
-          *reinterpret_cast<uint4*>(orow + col0 + 2 * j) = make_uint4(packed[j], packed[j + 1], packed[j + 2], packed[j + 3]);
-      } else {
-        for (int j = 0; j < 32 && col0 + j < p.n_out; ++j)
-          orow[col0 + j] = __ushort_as_bfloat16(
-              static_cast<unsigned short>((j & 1) ? (packed[j / 2] >> 16) : (packed[j / 2] & 0xffffu)));
-      }
+  constexpr int CH = SWIGLU ? 16 : 32;                       // output columns per chunk
+  constexpr int NB = SWIGLU ? 2 : 1;                         // accumulator pieces per chunk (gate, up)
+  uint32_t buf[2][NB][CH];
+  auto load = [&](int c, uint32_t (&d)[NB][CH]) {
+    if constexpr (SWIGLU) {
+      tmem_ld16(taddr + c, d[0]);
+      tmem_ld16(taddr + kGN / 2 + c, d[1]);
+    } else {
+      tmem_ld32(taddr + c, d[0]);
     }
+  };
+  auto emit = [&](int c, const uint32_t (&d)[NB][CH]) {
+    const int col0 = ti.nt * kOutCols + c;
+    if (!(valid && col0 < p.n_out)) return;
+    uint32_t packed[CH / 2];
+#pragma unroll
+    for (int j = 0; j < CH; j += 2) {
+      float v0 = __uint_as_float(d[0][j]) * alpha, v1 = __uint_as_float(d[0][j + 1]) * alpha;
+      if constexpr (SWIGLU) {
+        v0 = silu_mul(v0, __uint_as_float(d[NB - 1][j]) * alpha);
+        v1 = silu_mul(v1, __uint_as_float(d[NB - 1][j + 1]) * alpha);
+      }
+      packed[j / 2] = pack_bf16x2(v0, v1);
+    }
+    if (col0 + CH <= p.n_out) {
+      if (wide_ok) {
+        // 32-byte stores: every lane writes whole sectors of its own row, half as many store instructions
+#pragma unroll
+        for (int j = 0; j < CH / 2; j += 8)
+          asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(orow + col0 + 2 * j),
+                       "r"(packed[j]), "r"(packed[j + 1]), "r"(packed[j + 2]), "r"(packed[j + 3]), "r"(packed[j + 4]),
+                       "r"(packed[j + 5]), "r"(packed[j + 6]), "r"(packed[j + 7]) : "memory");
+      } else {
+#pragma unroll
+        for (int j = 0; j < CH / 2; j += 4)
+          *reinterpret_cast<uint4*>(orow + col0 + 2 * j) =
+              make_uint4(packed[j], packed[j + 1], packed[j + 2], packed[j + 3]);
+      }
+    } else {
+      for (int j = 0; j < CH && col0 + j < p.n_out; ++j)
+        orow[col0 + j] = __ushort_as_bfloat16(
+            static_cast<unsigned short>((j & 1) ? (packed[j / 2] >> 16) : (packed[j / 2] & 0xffffu)));
+    }
+  };
+  load(0, buf[0]);
+#pragma unroll 1
+  for (int c = 0; c < kOutCols; c += 2 * CH) {
+    tmem_ld_wait();
+    load(c + CH, buf[1]);                                    // kOutCols is a multiple of 2 CH
+    emit(c, buf[0]);
+    tmem_ld_wait();
+    if (c + 2 * CH < kOutCols) load(c + 2 * CH, buf[0]);
+    emit(c + CH, buf[1]);
   }
 }
 
@@ -163,14 +217,25 @@ __global__ void __launch_bounds__(448, 1)
 grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
   using S = GroupedCfg<MODE>;
   constexpr bool WIDE = S::WIDE;
-  constexpr int kStages = S::kStages;
+  constexpr int kAStages = S::kAStages, kBStages = S::kBStages;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  {
+    // the launch asks for as much slack as fits below the limit of one CTA; the base is normally aligned already
+    uint32_t dyn;
+    asm("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn));
+    if (static_cast<uint32_t>(smem - smem_raw) + S::kTotal > dyn) {
+      if (threadIdx.x == 0) report_error(p.status, MSL_ERR_CUDA);
+      return;                                                // uniform for the CTA, before any barrier
+    }
+  }
   uint32_t* lut = reinterpret_cast<uint32_t*>(smem + S::kLutOffset);
   int* mt_prefix = reinterpret_cast<int*>(smem + S::kPrefixOffset);
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + S::kBarOffset);
-  uint64_t* empty = full + kStages;
-  uint64_t* tmem_full = empty + kStages;
+  uint64_t* a_full = reinterpret_cast<uint64_t*>(smem + S::kBarOffset);
+  uint64_t* a_empty = a_full + kAStages;
+  uint64_t* b_full = a_empty + kAStages;
+  uint64_t* b_empty = b_full + kBStages;
+  uint64_t* tmem_full = b_empty + kBStages;
   uint64_t* tmem_empty = tmem_full + 2;
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
   volatile uint32_t* abort_flag = tmem_base_slot + 1;
@@ -193,11 +258,15 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
   }
   if (warp == 0) row_tile_prefix(p.offsets, p.experts, S::kTileM, mt_prefix, lane);
   if (threadIdx.x == 0) {
-    // full: one expect_tx arrival of the TMA lane + the warps of one producer group;
-    // tmem_empty: the 4 epilogue warps.
-    for (int s = 0; s < kStages; ++s) {
-      mbar_init(&full[s], 1 + kGroupThreads / 32);
-      mbar_init(&empty[s], 1);
+    // a_full: one expect_tx arrival of the TMA lane; b_full: the warps of one producer group; the empty
+    // barriers: one tcgen05.commit; tmem_empty: the 4 epilogue warps.
+    for (int s = 0; s < kAStages; ++s) {
+      mbar_init(&a_full[s], 1);
+      mbar_init(&a_empty[s], 1);
+    }
+    for (int s = 0; s < kBStages; ++s) {
+      mbar_init(&b_full[s], kGroupThreads / 32);
+      mbar_init(&b_empty[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tmem_full[a], 1);
@@ -222,13 +291,13 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
       for (int g = worker; g < total_tiles && ok; g += n_workers) {
         const TileInfo ti = decode_tile(g, mt_prefix, p.offsets, p.experts, n_tiles, S::kTileM);
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-          const int s = it % kStages;
-          const uint32_t ph = (it / kStages) & 1;
-          if (*abort_flag || !mbar_wait(&empty[s], ph ^ 1)) { ok = false; break; }
+          const int s = it % kAStages;
+          const uint32_t ph = (it / kAStages) & 1;
+          if (*abort_flag || !mbar_wait(&a_empty[s], ph ^ 1)) { ok = false; break; }
           const int nsub = WIDE ? (ti.rows + kSubM - 1) / kSubM : 1;
-          mbar_expect_tx(&full[s], nsub * S::kSubBytes);
+          mbar_expect_tx(&a_full[s], nsub * S::kSubBytes);
           for (int sub = 0; sub < nsub; ++sub)
-            tma_load_2d(smem + s * S::kStageBytes + sub * S::kSubBytes, &tm_x, &full[s], kb * kGK,
+            tma_load_2d(smem + s * S::kABytes + sub * S::kSubBytes, &tm_x, &a_full[s], kb * kGK,
                         ti.row0 + sub * kSubM);
         }
       }
@@ -243,6 +312,7 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
       constexpr uint32_t idesc = make_idesc(1, 1, 128, kGN);
       uint32_t it = 0, tile_i = 0;
       bool ok = true;
+      GPROF_DECL;
       for (int g = worker; g < total_tiles && ok; g += n_workers, ++tile_i) {
         // kWide has one accumulator set (index 0, phase flips every tile); the others alternate two.
         const uint32_t acc = WIDE ? 0u : (tile_i & 1), acc_ph = WIDE ? (tile_i & 1) : ((tile_i >> 1) & 1);
@@ -251,16 +321,21 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
           const TileInfo ti = decode_tile(g, mt_prefix, p.offsets, p.experts, n_tiles, S::kTileM);
           nsub = (ti.rows + kSubM - 1) / kSubM;
         }
+        GPROF_MARK(0);
         if (*abort_flag || !mbar_wait(&tmem_empty[acc], acc_ph ^ 1)) { ok = false; break; }
+        GPROF_MARK(1);
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * kGN;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-          const int s = it % kStages;
-          const uint32_t ph = (it / kStages) & 1;
-          if (*abort_flag || !mbar_wait(&full[s], ph)) { ok = false; break; }
+          const int as = it % kAStages, bs = it % kBStages;
+          GPROF_MARK(0);
+          if (*abort_flag || !mbar_wait(&b_full[bs], (it / kBStages) & 1)) { ok = false; break; }
+          GPROF_MARK(2);
+          if (!mbar_wait(&a_full[as], (it / kAStages) & 1)) { ok = false; break; }
+          GPROF_MARK(3);
           tc_fence_after();
-          const uint32_t sa = smem_u32(smem + s * S::kStageBytes);
-          const uint32_t sb = sa + S::kABytes;
+          const uint32_t sa = smem_u32(smem + as * S::kABytes);
+          const uint32_t sb = smem_u32(smem + S::kBRing + bs * S::kBBytes);
 #pragma unroll
           for (int k16 = 0; k16 < kGK / 16; ++k16) {
             const uint64_t da = make_sdesc(sa + k16 * 32, 16, 1024, 2), db = make_sdesc(sb + k16 * 32, 16, 1024, 2);
@@ -269,10 +344,16 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
               tc_mma_f16_if(on, d_tmem + kGN, make_sdesc(sa + S::kSubBytes + k16 * 32, 16, 1024, 2), db, idesc,
                             (kb | k16) != 0);
           }
-          tc_commit_if(on, &empty[s]);
+          tc_commit_if(on, &a_empty[as]);
+          tc_commit_if(on, &b_empty[bs]);
         }
         if (ok) tc_commit_if(on, &tmem_full[acc]);
       }
+      GPROF_MARK(0);
+#ifdef MSL_GROUPED_PROF
+      prof_acc[7] = it;
+      if (lane == 0) GPROF_FLUSH(0, 8);
+#endif
       if (!ok && lane == 0) { *abort_flag = 1; report_error(p.status, MSL_ERR_DEVICE_TIMEOUT); }
     }
   } else if (warp < 6) {
@@ -352,6 +433,7 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
       if (pf.g < total_tiles) { fetch(pf, wbuf[u], sbuf[u]); advance(pf, kGroups); }
     uint32_t it = gid;
     bool ok = true;
+    GPROF_DECL;
     while (cons.g < total_tiles && ok) {
 #pragma unroll
       for (int u = 0; u < kBufs; ++u) {
@@ -360,10 +442,12 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
           fetch(pf, wbuf[(u + kBufs - 1) % kBufs], sbuf[(u + kBufs - 1) % kBufs]);
           advance(pf, kGroups);
         }
-        const int s = it % kStages;
-        const uint32_t ph = (it / kStages) & 1;
-        if (*abort_flag || !mbar_wait(&empty[s], ph ^ 1)) { ok = false; break; }
-        uint8_t* sb = smem + s * S::kStageBytes + S::kABytes;
+        GPROF_MARK(0);
+        const int s = it % kBStages;
+        const uint32_t ph = (it / kBStages) & 1;
+        if (*abort_flag || !mbar_wait(&b_empty[s], ph ^ 1)) { ok = false; break; }
+        GPROF_MARK(1);
+        uint8_t* sb = smem + S::kBRing + s * S::kBBytes;
 #pragma unroll
         for (int r = 0; r < kRows; ++r) {
           const int row = tg + r * kGroupThreads;
@@ -375,11 +459,18 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
         }
         fence_async_smem();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&full[s]);
+        if (lane == 0) mbar_arrive(&b_full[s]);
+        GPROF_MARK(2);
         it += kGroups;
         advance(cons, kGroups);
+        GPROF_MARK(3);
       }
     }
+#ifdef MSL_GROUPED_PROF
+    prof_acc[7] = it / kGroups;
+    if (t == 0) GPROF_FLUSH(8, 8);
+    if (t == kGroupThreads) GPROF_FLUSH(16, 8);
+#endif
     if (!ok && lane == 0) { *abort_flag = 1; report_error(p.status, MSL_ERR_DEVICE_TIMEOUT); }
   }
 
@@ -482,7 +573,7 @@ template <int MODE>
 static int launch_grouped(const CUtensorMap& tx, const GroupedArgs& a, int64_t slab_rows, int experts, int n_padded,
                           cudaStream_t st) {
   using S = GroupedCfg<MODE>;
-  const int smem = S::kTotal + 1024;
+  const int smem = std::min(S::kTotal + 1024, 232448);      // alignment slack as far as one CTA's limit allows
   static SmemConfig config;
   if (int rc = config.ensure(grouped_nvfp4_kernel<MODE>, smem)) return rc;
   // Upper bound on tiles without reading the device counts: every group may add one partial tile.
@@ -516,3 +607,14 @@ extern "C" int msl_grouped_gemm_nvfp4(const void* x, int64_t slab_rows, const vo
   return use_wide ? launch_grouped<kWide>(tx, a, slab_rows, experts, n_padded, st)
                   : launch_grouped<kNarrow>(tx, a, slab_rows, experts, n_padded, st);
 }
+
+#ifdef MSL_GROUPED_PROF
+extern "C" int msl_debug_grouped_prof(unsigned long long* out, int reset) {
+  if (cudaMemcpyFromSymbol(out, msl::g_grouped_prof, sizeof(msl::g_grouped_prof)) != cudaSuccess) return MSL_ERR_CUDA;
+  if (reset) {
+    unsigned long long zero[32] = {};
+    if (cudaMemcpyToSymbol(msl::g_grouped_prof, zero, sizeof(zero)) != cudaSuccess) return MSL_ERR_CUDA;
+  }
+  return MSL_OK;
+}
+#endif
