@@ -729,7 +729,7 @@ def main():
         for k, v in weights.items():
             if not k.startswith(("w13", "w2")):
                 dist.broadcast(v, 0)
-        st = layer.prepare(weights)
+        st = layer.prepare(weights, experts_nvfp4=args.experts_nvfp4)
         ctx = ep.ExpertParallel(st, world, rank, shape.n_experts)
         if args.transport.startswith("peer"):
             args.transport = enable_peer_or_collective(ep, dist, ctx, st, data["config"]["tokens"], shape.top_k)
