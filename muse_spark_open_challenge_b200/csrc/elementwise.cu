@@ -645,7 +645,11 @@ __global__ void peer_barrier_kernel(int* const* __restrict__ flag_bases, int ran
 // crosses HBM exactly once; a block holds 64 KB at width 4096 and top_k 8, three blocks per SM, so two
 // blocks' loads are in flight while a third computes.  (An earlier form took the rows two at a time
 // through two 16 KB buffers, five blocks per SM: four block-wide reductions and a dozen barriers per token
-// left it at 0.64 of the copy bandwidth.)
+// left it at 0.64 of the copy bandwidth.  A persistent form, one block per SM walking over tokens with
+// the next two tokens' rows already in flight and the per-column vectors held in registers, gave the same
+// bits and ran slower, 0.75-0.89 against 0.53-0.59 ms fused with the boundary at 16384 tokens: a token
+// costs a block about 1100 instructions per thread and three block-wide reductions, which three blocks
+// per SM overlap and one block cannot.)
 constexpr int kCombineThreads = 256;
 constexpr int kCombineMaxChunks = 4;    // 8-element chunks per thread: width <= 8192 (MAXC = 2: <= 4096)
 constexpr int kCombineRows = 8;         // rows staged per round
