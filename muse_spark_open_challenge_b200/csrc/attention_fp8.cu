@@ -33,8 +33,9 @@
 //                   (nobody waits for P V explicitly)
 //   warp  9         TMA: the two Q sub-tiles, and whole 128-key K/V tiles as two 64-row boxes per
 //                   tensor when the page size is a multiple of 64 and every key of the tile exists
-//   warps 10-11     gather loaders for all other tiles (any page size, ragged tail): two keys per
-//                   thread, 16-byte copies into the swizzled tile, zeros for keys past the causal end
+//   warps 10-11     gather loaders for all other tiles (any page size, ragged tail), taking alternate
+//                   tiles: four keys per lane, 16-byte copies into the swizzled tile, zeros for keys past
+//                   the causal end
 // K/V tiles move through a 4-stage ring.  TMEM: S0 | S1 | O0 | O1 (512 columns), P inside S.  Every
 // wait is bounded.
 //
@@ -395,49 +396,60 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     }
   } else if (warp >= 10) {
     // ------------------------------------------------------------------ gather loaders
-    const int r0 = threadIdx.x - 10 * 32;                  // key rows r0 and r0 + 64 of the tile
+    // The two warps take alternate tiles, so that two tiles' chains (page table entry -> K/V rows -> shared
+    // memory) are in flight at once: with one-token pages a chain takes longer than the softmax of a tile at
+    // head_dim 64.  The warp that does not own a tile only passes the barrier on.  A lane carries kPass keys
+    // at a time (rows lane, lane + 32, ... of the tile): all four at head_dim 64, two and two at 128.
+    const int gw = warp - 10;
+    constexpr int kPass = (D <= 64) ? 4 : 2;
     const int* pt = p.page_table + static_cast<int64_t>(b) * p.max_pages;
     bool ok = true;
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int st = j % kAStages;
       const uint32_t e_ph = ((j / kAStages) & 1) ^ 1;
-      if (tile_by_tma(j)) {
+      if (tile_by_tma(j) || (j & 1) != gw) {
         if (*abort_flag || !mbar_wait(&kv_empty[st], e_ph, true)) { ok = false; break; }
         __syncwarp();
         if (lane == 0) mbar_arrive(&kv_full[st]);
         continue;
       }
-      uint4 kq[2][D / 16], vq[2][D / 16];
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int key = (kt_begin + j) * kAN + r0 + 64 * h;
-        int64_t row = -1;
-        if (key <= last_qpos) {
-          const int pg = pt[key / p.page_size];
-          if (pg >= 0) row = static_cast<int64_t>(pg) * p.page_size + key % p.page_size;
-          if (row >= p.cache_rows) row = -1;
-        }
-        if (row >= 0) {
-          const uint4* ks = reinterpret_cast<const uint4*>(p.k_cache + (row * p.hkv + kvh) * D);
-          const uint4* vs = reinterpret_cast<const uint4*>(p.v_cache + (row * p.hkv + kvh) * D);
-#pragma unroll
-          for (int c = 0; c < D / 16; ++c) { kq[h][c] = ks[c]; vq[h][c] = vs[c]; }
-        } else {
-#pragma unroll
-          for (int c = 0; c < D / 16; ++c) { kq[h][c] = make_uint4(0, 0, 0, 0); vq[h][c] = make_uint4(0, 0, 0, 0); }
-        }
-      }
-      if (*abort_flag || !mbar_wait(&kv_empty[st], e_ph, true)) { ok = false; break; }
       uint8_t* sk = smem + S::kKV + st * 2 * S::kTile;
       uint8_t* sv = sk + S::kTile;
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
+      for (int h0 = 0; h0 < 4 && ok; h0 += kPass) {
+        uint4 kq[kPass][D / 16], vq[kPass][D / 16];
 #pragma unroll
-        for (int c = 0; c < D / 16; ++c) {
-          *reinterpret_cast<uint4*>(sk + swz<D>(r0 + 64 * h, c)) = kq[h][c];
-          *reinterpret_cast<uint4*>(sv + swz<D>(r0 + 64 * h, c)) = vq[h][c];
+        for (int h = 0; h < kPass; ++h) {
+          const int key = (kt_begin + j) * kAN + lane + 32 * (h0 + h);
+          int64_t row = -1;
+          if (key <= last_qpos) {
+            const int pg = pt[key / p.page_size];
+            if (pg >= 0) row = static_cast<int64_t>(pg) * p.page_size + key % p.page_size;
+            if (row >= p.cache_rows) row = -1;
+          }
+          if (row >= 0) {
+            const uint4* ks = reinterpret_cast<const uint4*>(p.k_cache + (row * p.hkv + kvh) * D);
+            const uint4* vs = reinterpret_cast<const uint4*>(p.v_cache + (row * p.hkv + kvh) * D);
+#pragma unroll
+            for (int c = 0; c < D / 16; ++c) { kq[h][c] = ks[c]; vq[h][c] = vs[c]; }
+          } else {
+#pragma unroll
+            for (int c = 0; c < D / 16; ++c) { kq[h][c] = make_uint4(0, 0, 0, 0); vq[h][c] = make_uint4(0, 0, 0, 0); }
+          }
+        }
+        if (h0 == 0) {                                       // the loads above are in flight while the slot frees
+          if (*abort_flag || !mbar_wait(&kv_empty[st], e_ph, true)) { ok = false; break; }
+        }
+#pragma unroll
+        for (int h = 0; h < kPass; ++h) {
+#pragma unroll
+          for (int c = 0; c < D / 16; ++c) {
+            *reinterpret_cast<uint4*>(sk + swz<D>(lane + 32 * (h0 + h), c)) = kq[h][c];
+            *reinterpret_cast<uint4*>(sv + swz<D>(lane + 32 * (h0 + h), c)) = vq[h][c];
+          }
         }
       }
+      if (!ok) break;
       fence_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(&kv_full[st]);
@@ -797,9 +809,22 @@ extern "C" int msl_attention_split_plan(int batch, int max_q_len, int hq, int hk
   if (window > 0) keys = std::min<int64_t>(keys, window + tq2);
   const int64_t tiles = (keys + kAN - 1) / kAN;
   const int sms = sm_count();
-  if (ctas >= 2 * sms || tiles < 16) return 1;             // enough CTAs, or too little work to slice
-  // aim at two waves of CTAs, at least eight key tiles per slice
-  return static_cast<int>(std::max<int64_t>(1, std::min<int64_t>({(2 * sms + ctas - 1) / ctas, tiles / 8, 16})));
+  if (ctas >= 4 * sms || tiles < 16) return 1;             // enough CTAs, or too little work to slice
+  // One CTA runs per SM at a time, so the slices run in waves: take the number of slices (at most 16, at
+  // least eight key tiles each) whose waves x tiles per slice is smallest; two tiles stand for a CTA's fixed
+  // cost, and a slice more has to save 2 % to be taken (its partial results are merged afterwards).
+  const int64_t most = std::max<int64_t>(1, std::min<int64_t>(tiles / 8, 16));
+  int best = 1;
+  double best_cost = 0.0;
+  for (int64_t k = 1; k <= most; ++k) {
+    const int64_t waves = (ctas * k + sms - 1) / sms;
+    const double cost = static_cast<double>(waves) * static_cast<double>((tiles + k - 1) / k + 2);
+    if (k == 1 || cost < 0.98 * best_cost) {
+      best = static_cast<int>(k);
+      best_cost = cost;
+    }
+  }
+  return best;
 }
 
 extern "C" int64_t msl_attention_split_workspace(int kv_splits, int tokens, int hq, int head_dim) {
