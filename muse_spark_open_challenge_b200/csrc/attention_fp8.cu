@@ -809,7 +809,7 @@ extern "C" int msl_attention_split_plan(int batch, int max_q_len, int hq, int hk
   if (window > 0) keys = std::min<int64_t>(keys, window + tq2);
   const int64_t tiles = (keys + kAN - 1) / kAN;
   const int sms = sm_count();
-  if (ctas >= 4 * sms || tiles < 16) return 1;             // enough CTAs, or too little work to slice
+  if (ctas >= 2 * sms || tiles < 16) return 1;             // enough CTAs, or too little work to slice
   // One CTA runs per SM at a time, so the slices run in waves: take the number of slices (at most 16, at
   // least eight key tiles each) whose waves x tiles per slice is smallest; two tiles stand for a CTA's fixed
   // cost, and a slice more has to save 2 % to be taken (its partial results are merged afterwards).
