@@ -230,35 +230,58 @@ grouped_nvfp4_bs_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_c
       const uint32_t taddr = tmem_base + acc * 256 + (static_cast<uint32_t>(quarter * 32) << 16);
       __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + row * p.ld_out;
       const int out_cols = p.swiglu ? kBsN / 2 : kBsN;
-#pragma unroll 1
-      for (int c = 0; c < out_cols; c += 32) {
-        uint32_t a[32], b[32];
-        tmem_ld32(taddr + c, a);
-        if (p.swiglu) tmem_ld32(taddr + kBsN / 2 + c, b);
-        tmem_ld_wait();
+      const bool wide_ok = ((reinterpret_cast<uintptr_t>(p.out) | static_cast<uintptr_t>(p.ld_out * 2)) & 31) == 0;
+      // chunks of 32 output columns; the TMEM loads of a chunk are issued one chunk ahead of its arithmetic
+      // and stores (with K = 1536 a tile's main loop is no longer than this epilogue)
+      uint32_t a[2][32], b[2][32];
+      auto load = [&](int c, uint32_t (&x)[32], uint32_t (&y)[32]) {
+        tmem_ld32(taddr + c, x);
+        if (p.swiglu) tmem_ld32(taddr + kBsN / 2 + c, y);
+      };
+      auto emit = [&](int c, const uint32_t (&x)[32], const uint32_t (&y)[32]) {
         const int col0 = ti.nt * out_cols + c;
-        if (valid && col0 < p.n_out) {
-          uint32_t packed[16];
+        if (!(valid && col0 < p.n_out)) return;
+        uint32_t packed[16];
 #pragma unroll
-          for (int j = 0; j < 32; j += 2) {
-            float v0 = __uint_as_float(a[j]) * alpha, v1 = __uint_as_float(a[j + 1]) * alpha;
-            if (p.swiglu) {
-              const float u0 = __uint_as_float(b[j]) * alpha, u1 = __uint_as_float(b[j + 1]) * alpha;
-              v0 = v0 / (1.0f + __expf(-v0)) * u0;
-              v1 = v1 / (1.0f + __expf(-v1)) * u1;
-            }
-            packed[j / 2] = pack_bf16x2(v0, v1);
+        for (int j = 0; j < 32; j += 2) {
+          float v0 = __uint_as_float(x[j]) * alpha, v1 = __uint_as_float(x[j + 1]) * alpha;
+          if (p.swiglu) {
+            // SiLU(g) * u = g * u / (1 + exp(-g)) with the fast reciprocal (2 ulp; +inf denominator -> 0)
+            v0 = __fdividef(v0 * (__uint_as_float(y[j]) * alpha), 1.0f + __expf(-v0));
+            v1 = __fdividef(v1 * (__uint_as_float(y[j + 1]) * alpha), 1.0f + __expf(-v1));
           }
-          if (col0 + 32 <= p.n_out) {
+          packed[j / 2] = pack_bf16x2(v0, v1);
+        }
+        if (col0 + 32 <= p.n_out) {
+          if (wide_ok) {
+#pragma unroll
+            for (int j = 0; j < 16; j += 8)
+              asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(orow + col0 + 2 * j),
+                           "r"(packed[j]), "r"(packed[j + 1]), "r"(packed[j + 2]), "r"(packed[j + 3]),
+                           "r"(packed[j + 4]), "r"(packed[j + 5]), "r"(packed[j + 6]), "r"(packed[j + 7]) : "memory");
+          } else {
 #pragma unroll
             for (int j = 0; j < 16; j += 4)
               *reinterpret_cast<uint4*>(orow + col0 + 2 * j) =
                   make_uint4(packed[j], packed[j + 1], packed[j + 2], packed[j + 3]);
-          } else {
-            for (int j = 0; j < 32 && col0 + j < p.n_out; ++j)
-              orow[col0 + j] = __ushort_as_bfloat16(
-                  static_cast<unsigned short>((j & 1) ? (packed[j / 2] >> 16) : (packed[j / 2] & 0xffffu)));
           }
+        } else {
+          for (int j = 0; j < 32 && col0 + j < p.n_out; ++j)
+            orow[col0 + j] = __ushort_as_bfloat16(
+                static_cast<unsigned short>((j & 1) ? (packed[j / 2] >> 16) : (packed[j / 2] & 0xffffu)));
+        }
+      };
+      load(0, a[0], b[0]);
+#pragma unroll 1
+      for (int c = 0; c < out_cols; c += 64) {               // out_cols is 96 or 192
+        tmem_ld_wait();
+        const bool second = c + 32 < out_cols;
+        if (second) load(c + 32, a[1], b[1]);
+        emit(c, a[0], b[0]);
+        if (second) {
+          tmem_ld_wait();
+          if (c + 64 < out_cols) load(c + 64, a[0], b[0]);
+          emit(c + 32, a[1], b[1]);
         }
       }
       tc_fence_before();
