@@ -18,11 +18,12 @@
 //              swizzled, and the two scale blocks (2 KB + 4 KB, already in the layout tcgen05.cp expects)
 //              by bulk copies
 //   warp 1     TMEM allocation; per stage 12 tcgen05.cp (scales) and 4 tcgen05.mma (M=128, N=192, K=64)
-//   warps 2-5  epilogue: accumulator row -> scales -> (SiLU * up) -> bf16
+//   warps 2-5  epilogue: accumulator row -> scales -> (SiLU * up) -> bf16; TMEM loads one chunk ahead, fast
+//              reciprocal, 32-byte stores (at K = 1536 a tile's main loop is no longer than its epilogue)
 // TMEM: accumulator 0 at columns [0, 192), scales at [192, 240), accumulator 1 at [256, 448): the epilogue
 // of one tile overlaps the main loop of the next.  Every mbarrier wait is bounded.
 //
-// What bounds it (131072 rows x 3072 x 4096: 1.04 ms = 3160 TFLOP/s, 0.36 of the instruction's measured
+// What bounds it (131072 rows x 3072 x 4096: 0.97 ms = 3390 TFLOP/s, 0.38 of the instruction's measured
 // ceiling): a stage of K = 256 takes 1120 cycles against 400 of MMA time.  Two things meet there.  The tensor
 // pipe runs the 12 scale copies and the 4 MMAs of a stage in order and no instruction on it takes less than
 // about 57 cycles (12 x 57 + 4 x 100 = 1084).  And the loads are bound by latency, not by L2 bandwidth: with
