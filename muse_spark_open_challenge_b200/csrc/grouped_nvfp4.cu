@@ -148,10 +148,12 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
 
 template <bool SWIGLU>
 __device__ __forceinline__ void store_rows(const GroupedArgs& p, const TileInfo& ti, uint32_t taddr, int r,
-                                           float alpha) {
+                                           float alpha, uint64_t* release) {
   // One thread owns row r of the tile: 256 accumulator columns -> 256 (or 128 fused) outputs, in chunks
   // whose TMEM loads are issued one chunk ahead of the arithmetic and the stores.  Offsets that run past
-  // the slab (a routing that needs more rows than the buffers hold) store nothing.
+  // the slab (a routing that needs more rows than the buffers hold) store nothing.  `release` (the last
+  // sub-tile of a tile): the accumulators are handed back as soon as the last chunk is in registers, before
+  // its arithmetic and stores.
   const bool valid = r < ti.rows && static_cast<int64_t>(ti.row0) + r < p.slab_rows;
   __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<int64_t>(ti.row0 + r) * p.ld_out;
   const bool wide_ok = ((reinterpret_cast<uintptr_t>(p.out) | static_cast<uintptr_t>(p.ld_out * 2)) & 31) == 0;
@@ -207,7 +209,13 @@ __device__ __forceinline__ void store_rows(const GroupedArgs& p, const TileInfo&
     load(c + CH, buf[1]);                                    // kOutCols is a multiple of 2 CH
     emit(c, buf[0]);
     tmem_ld_wait();
-    if (c + 2 * CH < kOutCols) load(c + 2 * CH, buf[0]);
+    if (c + 2 * CH < kOutCols) {
+      load(c + 2 * CH, buf[0]);
+    } else if (release != nullptr) {
+      tc_fence_before();
+      __syncwarp();
+      if ((threadIdx.x & 31) == 0) mbar_arrive(release);
+    }
     emit(c + CH, buf[1]);
   }
 }
@@ -371,12 +379,15 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
       for (int sub = 0; sub < nsub; ++sub) {
         const uint32_t taddr = tmem_base + (acc + sub) * kGN + (static_cast<uint32_t>(quarter * 32) << 16);
         const int r = sub * kSubM + quarter * 32 + lane;
-        if (p.swiglu) store_rows<true>(p, ti, taddr, r, alpha);
-        else store_rows<false>(p, ti, taddr, r, alpha);
+        uint64_t* release = sub == nsub - 1 ? &tmem_empty[acc] : nullptr;
+        if (p.swiglu) store_rows<true>(p, ti, taddr, r, alpha, release);
+        else store_rows<false>(p, ti, taddr, r, alpha, release);
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+      if (nsub == 0) {                                       // an empty tile: nothing was read, hand the set back
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+      }
     }
     if (!ok && lane == 0) { *abort_flag = 1; report_error(p.status, MSL_ERR_DEVICE_TIMEOUT); }
   } else {
