@@ -429,7 +429,9 @@ static int gemm_entry(const void* a, int64_t lda, const void* b, int64_t ldb, vo
       return narrow ? launch_gemm<128, 6, MSL_OUT_F32>(ta, tb, args, st)
                     : launch_gemm<256, 4, MSL_OUT_F32>(ta, tb, args, st);
     case MSL_OUT_SWIGLU_BF16:
-      // the SiLU epilogue is long enough that overlapping it (two accumulator sets) wins: 1413 vs 1316 TFLOP/s
+      // (with the earlier, longer SiLU epilogue the 128-row tiles, whose two accumulator sets overlap it, won:
+      // 1413 against 1316 TFLOP/s; with the short one the 256-row tiles do: 1522 against 1437)
+      if (wide) return launch_gemm<256, 3, MSL_OUT_SWIGLU_BF16, 2>(ta, tb, args, st);
       return launch_gemm<256, 4, MSL_OUT_SWIGLU_BF16>(ta, tb, args, st);
     default:
       return MSL_ERR_ARG;
