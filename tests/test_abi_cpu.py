@@ -68,6 +68,22 @@ def test_argument_errors_are_rejected_before_any_launch(lib):
     assert lib.msl_nvfp4_padded_rows(128, 0) == 256 and lib.msl_nvfp4_padded_rows(200, 1) == 256
 
 
+def test_split_kv_plan_counts_waves(lib):
+    """The slice count of split-KV attention comes from sizes alone (148 SMs assumed without a GPU): one CTA
+    runs per SM at a time, so the plan takes the count whose waves x key tiles per slice is smallest, and
+    leaves calls that already fill two waves unsliced (their bits must not depend on the batch)."""
+    plan = lib.msl_attention_split_plan
+    # 753 new tokens after 80000 cached, 16 q / 2 kv heads, one-token pages: 48 query blocks
+    assert plan(1, 753, 16, 2, 80753, 1, 0) == 3           # 144 CTAs: one wave of 211 tiles (7 slices: 3 waves of 91)
+    assert plan(4, 753, 16, 2, 80753, 1, 0) == 3           # 576 CTAs: 3.9 waves of 211 (2 slices: 2.6 waves of 316)
+    # whole prefills are never sliced, alone or in a batch
+    assert plan(1, 4096, 32, 8, 64, 64, 0) == 1 and plan(4, 4096, 32, 8, 64, 64, 0) == 1
+    # a decode step over 4096 cached tokens: as many slices as leave eight key tiles each
+    assert plan(1, 1, 32, 8, 64, 64, 0) == 4
+    # short contexts and bad arguments: no slicing
+    assert plan(1, 1, 32, 8, 8, 64, 0) == 1 and plan(0, 1, 32, 8, 64, 64, 0) == 1 and plan(1, 1, 32, 5, 64, 64, 0) == 1
+
+
 def test_missing_library_fails_loudly(tmp_path):
     from muse_spark_open_challenge_b200 import _lib
     with pytest.raises(_lib.MslError):
