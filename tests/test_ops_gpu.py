@@ -563,8 +563,8 @@ def test_kv_rows_copy_gathers_scatters_and_reports_bad_rows(ops):
     assert torch.equal(other, before)
 
 
-def test_ep_plan_places_every_rank_and_reports_overflow(ops):
-    world, local = 4, 3
+@pytest.mark.parametrize("world,local", [(4, 3), (8, 16), (2, 64)])
+def test_ep_plan_places_every_rank_and_reports_overflow(ops, world, local):
     g = torch.Generator().manual_seed(1)
     counts = torch.randint(0, 50, (world, world * local), generator=g, dtype=torch.int32)
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
