@@ -32,6 +32,11 @@
 // reference's experimental W4A16 kernel (tools/prefill/moe_kernel/moe_fp4.py:163-183); the bit layout
 // (moved into the load-time repack so three of four pairs need one shift and one mask), the arithmetic
 // scale decode and the table for special scale codes are this file's own.
+#ifdef MSL_GROUPED_SPIN
+#define GWAIT mbar_wait_spin
+#else
+#define GWAIT mbar_wait
+#endif
 #include "grouped_sched.cuh"
 #include "msl_host.h"
 
@@ -337,9 +342,9 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int as = it % kAStages, bs = it % kBStages;
           GPROF_MARK(0);
-          if (*abort_flag || !mbar_wait(&b_full[bs], (it / kBStages) & 1)) { ok = false; break; }
+          if (*abort_flag || !GWAIT(&b_full[bs], (it / kBStages) & 1)) { ok = false; break; }
           GPROF_MARK(2);
-          if (!mbar_wait(&a_full[as], (it / kAStages) & 1)) { ok = false; break; }
+          if (!GWAIT(&a_full[as], (it / kAStages) & 1)) { ok = false; break; }
           GPROF_MARK(3);
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + as * S::kABytes);
@@ -456,7 +461,7 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
         GPROF_MARK(0);
         const int s = it % kBStages;
         const uint32_t ph = (it / kBStages) & 1;
-        if (*abort_flag || !mbar_wait(&b_empty[s], ph ^ 1)) { ok = false; break; }
+        if (*abort_flag || !GWAIT(&b_empty[s], ph ^ 1)) { ok = false; break; }
         GPROF_MARK(1);
         uint8_t* sb = smem + S::kBRing + s * S::kBBytes;
 #pragma unroll
