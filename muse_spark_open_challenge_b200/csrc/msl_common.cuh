@@ -65,31 +65,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, bool r
     }
   }
 }
-// The same, polling with the non-blocking test (mbarrier.try_wait may park the thread for a hardware-chosen
-// time; a poller on the critical path of a hand-off sees the phase flip sooner this way, at the price of
-// issue slots).
-__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity) {
-  uint64_t t0 = 0;
-  for (uint32_t i = 0;; ++i) {
-    if (mbar_test_wait(bar, parity)) return true;
-    if ((i & 1023u) == 1023u) {
-      const uint64_t now = global_ns();
-      if (t0 == 0) t0 = now;
-      else if (now - t0 > kWaitLimitNs) return false;
-    }
-  }
-}
 // Bounded pause used on the abort path so bulk copies already in flight can land.
 __device__ __forceinline__ void drain_pause() {
   for (int i = 0; i < 200; ++i) __nanosleep(1000);
