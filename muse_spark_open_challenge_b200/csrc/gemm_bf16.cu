@@ -64,11 +64,6 @@ __device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int
   nt = r / gm;
 }
 
-__device__ __forceinline__ void st_global_v8(void* dst, const uint32_t (&w)[8]) {
-  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst), "r"(w[0]), "r"(w[1]), "r"(w[2]),
-               "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
-}
-
 // SiLU(g) * u = g * u / (1 + exp(-g)) with the fast reciprocal: 2 ulp, far below the bf16 it is rounded to.
 // For g < -88 the denominator is +inf and the quotient 0, the limit.
 __device__ __forceinline__ float silu_mul(float g, float u) {
@@ -290,6 +285,33 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             tmem_ld16(taddr + BN / 2 + c + 32, u[0]);
           }
           store_chunk<BN, OUT, 16>(p, row, nt * (BN / 2) + c + 16, g[1], u[1], wide_ok);
+        }
+      } else if (OUT == MSL_OUT_BF16 && wide_ok && (nt + 1) * BN <= p.n) {
+        // bf16 rows of a tile that lies inside the output: chunks of 64 columns, transposed within quads so
+        // that four lanes write 128 contiguous bytes of one row per instruction (a lane writing 32 bytes of
+        // its own row costs the memory pipe one request per lane and per instruction)
+        const int q = lane & 3, row_base = row - q;
+        __nv_bfloat16* obase = reinterpret_cast<__nv_bfloat16*>(p.c) + static_cast<int64_t>(row_base) * p.ldc + nt * BN + 16 * q;
+        uint32_t a[32], b[32];
+        tmem_ld32(taddr, a);
+        tmem_ld32(taddr + 32, b);
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 64) {
+          tmem_ld_wait();
+          uint32_t u[32], f[32];
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            u[j / 2] = pack_bf16x2(__uint_as_float(a[j]) * p.alpha, __uint_as_float(a[j + 1]) * p.alpha);
+            u[16 + j / 2] = pack_bf16x2(__uint_as_float(b[j]) * p.alpha, __uint_as_float(b[j + 1]) * p.alpha);
+          }
+          quad_transpose_units(u, f);
+          if (c + 64 < BN) {
+            tmem_ld32(taddr + c + 64, a);
+            tmem_ld32(taddr + c + 96, b);
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (row_base + j < p.m) st_global_v8(obase + static_cast<int64_t>(j) * p.ldc + c, &f[8 * j]);
         }
       } else {
         uint32_t v[2][32];

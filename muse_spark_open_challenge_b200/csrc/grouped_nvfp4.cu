@@ -154,7 +154,7 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
 
 template <bool SWIGLU>
 __device__ __forceinline__ void store_rows(const GroupedArgs& p, const TileInfo& ti, uint32_t taddr, int r,
-                                           float alpha, uint64_t* release) {
+                                           float alpha, uint64_t* release, long long* epi = nullptr) {
   // One thread owns row r of the tile: 256 accumulator columns -> 256 (or 128 fused) outputs, in chunks
   // whose TMEM loads are issued one chunk ahead of the arithmetic and the stores.  Offsets that run past
   // the slab (a routing that needs more rows than the buffers hold) store nothing.  `release` (the last
@@ -208,13 +208,22 @@ __device__ __forceinline__ void store_rows(const GroupedArgs& p, const TileInfo&
             static_cast<unsigned short>((j & 1) ? (packed[j / 2] >> 16) : (packed[j / 2] & 0xffffu)));
     }
   };
+#ifdef MSL_GROUPED_PROF
+  long long t_ = clock64();
+#define EPI_MARK(i) do { const long long n_ = clock64(); if (epi) epi[i] += n_ - t_; t_ = n_; } while (0)
+#else
+#define EPI_MARK(i) do {} while (0)
+#endif
   load(0, buf[0]);
 #pragma unroll 1
   for (int c = 0; c < kOutCols; c += 2 * CH) {
     tmem_ld_wait();
+    EPI_MARK(0);
     load(c + CH, buf[1]);                                    // kOutCols is a multiple of 2 CH
     emit(c, buf[0]);
+    EPI_MARK(1);
     tmem_ld_wait();
+    EPI_MARK(0);
     if (c + 2 * CH < kOutCols) {
       load(c + 2 * CH, buf[0]);
     } else if (release != nullptr) {
@@ -223,6 +232,46 @@ __device__ __forceinline__ void store_rows(const GroupedArgs& p, const TileInfo&
       if ((threadIdx.x & 31) == 0) mbar_arrive(release);
     }
     emit(c + CH, buf[1]);
+    EPI_MARK(1);
+  }
+}
+
+// The plain bf16 output (down projection) when a whole 256-column tile lies inside the output and base and
+// pitch allow 32-byte stores: chunks of 64 columns, transposed within quads so that four lanes write 128
+// contiguous bytes of one row per instruction.  (With a lane writing 32 bytes of its own row, the 128 KB of a
+// 256-row tile left the SM at 14 bytes per cycle and took 9.2 k cycles.)  Called by whole warps.
+__device__ __forceinline__ void store_rows_quads(const GroupedArgs& p, const TileInfo& ti, uint32_t taddr, int r,
+                                                 float alpha, uint64_t* release) {
+  const int q = r & 3, r_base = r & ~3;
+  __nv_bfloat16* obase = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<int64_t>(ti.row0 + r_base) * p.ld_out +
+                         ti.nt * kGN + 16 * q;
+  bool ok_row[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) ok_row[j] = r_base + j < ti.rows && static_cast<int64_t>(ti.row0) + r_base + j < p.slab_rows;
+  uint32_t a[32], b[32];
+  tmem_ld32(taddr, a);
+  tmem_ld32(taddr + 32, b);
+#pragma unroll 1
+  for (int c = 0; c < kGN; c += 64) {
+    tmem_ld_wait();
+    uint32_t u[32], f[32];
+#pragma unroll
+    for (int j = 0; j < 32; j += 2) {
+      u[j / 2] = pack_bf16x2(__uint_as_float(a[j]) * alpha, __uint_as_float(a[j + 1]) * alpha);
+      u[16 + j / 2] = pack_bf16x2(__uint_as_float(b[j]) * alpha, __uint_as_float(b[j + 1]) * alpha);
+    }
+    quad_transpose_units(u, f);
+    if (c + 64 < kGN) {
+      tmem_ld32(taddr + c + 64, a);
+      tmem_ld32(taddr + c + 96, b);
+    } else if (release != nullptr) {
+      tc_fence_before();
+      __syncwarp();
+      if ((threadIdx.x & 31) == 0) mbar_arrive(release);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (ok_row[j]) st_global_v8(obase + static_cast<int64_t>(j) * p.ld_out + c, &f[8 * j]);
   }
 }
 
@@ -375,6 +424,9 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
     const int quarter = warp & 3;
     uint32_t tile_i = 0;
     bool ok = true;
+#ifdef MSL_GROUPED_PROF
+    long long epi_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#endif
     for (int g = worker; g < total_tiles && ok; g += n_workers, ++tile_i) {
       const TileInfo ti = decode_tile(g, mt_prefix, p.offsets, p.experts, n_tiles, S::kTileM);
       const uint32_t acc = WIDE ? 0u : (tile_i & 1), acc_ph = WIDE ? (tile_i & 1) : ((tile_i >> 1) & 1);
@@ -386,8 +438,17 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
         const uint32_t taddr = tmem_base + (acc + sub) * kGN + (static_cast<uint32_t>(quarter * 32) << 16);
         const int r = sub * kSubM + quarter * 32 + lane;
         uint64_t* release = sub == nsub - 1 ? &tmem_empty[acc] : nullptr;
+        const bool quads = !p.swiglu && (ti.nt + 1) * kGN <= p.n_out &&
+                           ((reinterpret_cast<uintptr_t>(p.out) | static_cast<uintptr_t>(p.ld_out * 2)) & 31) == 0;
+#ifdef MSL_GROUPED_PROF
+        if (p.swiglu) store_rows<true>(p, ti, taddr, r, alpha, release, epi_acc);
+        else if (quads) store_rows_quads(p, ti, taddr, r, alpha, release);
+        else store_rows<false>(p, ti, taddr, r, alpha, release, epi_acc);
+#else
         if (p.swiglu) store_rows<true>(p, ti, taddr, r, alpha, release);
+        else if (quads) store_rows_quads(p, ti, taddr, r, alpha, release);
         else store_rows<false>(p, ti, taddr, r, alpha, release);
+#endif
       }
       if (nsub == 0) {                                       // an empty tile: nothing was read, hand the set back
         tc_fence_before();
@@ -395,6 +456,9 @@ grouped_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_x, GroupedArgs p) {
         if (lane == 0) mbar_arrive(&tmem_empty[acc]);
       }
     }
+#ifdef MSL_GROUPED_PROF
+    if (threadIdx.x == 64) { epi_acc[7] = tile_i; for (int i_ = 0; i_ < 8; ++i_) atomicAdd(&g_grouped_prof[24 + i_], (unsigned long long)epi_acc[i_]); }
+#endif
     if (!ok && lane == 0) { *abort_flag = 1; report_error(p.status, MSL_ERR_DEVICE_TIMEOUT); }
   } else {
     // ------------------------------------------------------------ weight producers (warps 6-13)

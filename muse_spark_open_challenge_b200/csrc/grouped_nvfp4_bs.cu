@@ -272,6 +272,37 @@ grouped_nvfp4_bs_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_c
                 static_cast<unsigned short>((j & 1) ? (packed[j / 2] >> 16) : (packed[j / 2] & 0xffffu)));
         }
       };
+      if (!p.swiglu && wide_ok && (ti.nt + 1) * kBsN <= p.n_out) {
+        // plain bf16 rows of a tile inside the output: 64-column chunks transposed within quads, so that four
+        // lanes write 128 contiguous bytes of one row per instruction
+        const int q = r & 3, r_base = r & ~3;
+        __nv_bfloat16* obase = reinterpret_cast<__nv_bfloat16*>(p.out) +
+                               (static_cast<int64_t>(ti.row0) + r_base) * p.ld_out + ti.nt * kBsN + 16 * q;
+        tmem_ld32(taddr, a[0]);
+        tmem_ld32(taddr + 32, b[0]);
+#pragma unroll 1
+        for (int c = 0; c < kBsN; c += 64) {
+          tmem_ld_wait();
+          uint32_t u[32], f[32];
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            // every lane scales with ITS row's factor before the exchange
+            u[j / 2] = pack_bf16x2(__uint_as_float(a[0][j]) * alpha, __uint_as_float(a[0][j + 1]) * alpha);
+            u[16 + j / 2] = pack_bf16x2(__uint_as_float(b[0][j]) * alpha, __uint_as_float(b[0][j + 1]) * alpha);
+          }
+          quad_transpose_units(u, f);
+          if (c + 64 < kBsN) {
+            tmem_ld32(taddr + c + 64, a[0]);
+            tmem_ld32(taddr + c + 96, b[0]);
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int rj = r_base + j;
+            if (rj < ti.rows && static_cast<int64_t>(ti.row0) + rj < p.slab_rows)
+              st_global_v8(obase + static_cast<int64_t>(j) * p.ld_out + c, &f[8 * j]);
+          }
+        }
+      } else {
       load(0, a[0], b[0]);
 #pragma unroll 1
       for (int c = 0; c < out_cols; c += 64) {               // out_cols is 96 or 192
@@ -284,6 +315,7 @@ grouped_nvfp4_bs_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_c
           if (c + 64 < out_cols) load(c + 64, a[0], b[0]);
           emit(c + 32, a[1], b[1]);
         }
+      }
       }
       tc_fence_before();
       __syncwarp();

@@ -227,6 +227,38 @@ __device__ __forceinline__ void tc_mma_f8_ts_if(uint32_t on, uint32_t d_tmem, ui
       : "memory");
 }
 
+// 4 x 4 transpose of 32-byte units among the four lanes of a quad (lanes 4k .. 4k + 3).  Lane q gives the
+// four units u[8 j .. 8 j + 7] (j = 0..3) of ITS row and ends with unit q of the quad's four rows in
+// f[8 j .. 8 j + 7] (row j of the quad).  With a lane per row, four lanes can then write 128 contiguous bytes
+// of one row in one instruction (a store whose 32 lanes touch 32 different lines costs the memory pipe one
+// request per lane).  Two rounds of 16 shuffles; must be called by the whole warp.
+__device__ __forceinline__ void quad_transpose_units(const uint32_t (&u)[32], uint32_t (&f)[32]) {
+  const bool hi = (threadIdx.x & 2) != 0, odd = (threadIdx.x & 1) != 0;
+  uint32_t w[32];                        // w[(2 s + t) * 8 + k]: unit (q & 2) + t of row (q & 1) + 2 s
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {         // lanes 0, 1 give their units 2, 3 for the partner's units 0, 1; lanes 2, 3 the reverse
+    const uint32_t send = hi ? u[i] : u[16 + i];
+    const uint32_t recv = __shfl_xor_sync(0xffffffffu, send, 2);
+    w[i] = hi ? recv : u[i];
+    w[16 + i] = hi ? u[16 + i] : recv;
+  }
+#pragma unroll
+  for (int s = 0; s < 2; ++s) {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {        // keep the unit with this lane's number, give the other to the neighbour
+      const uint32_t keep = odd ? w[(2 * s + 1) * 8 + k] : w[(2 * s) * 8 + k];
+      const uint32_t send = odd ? w[(2 * s) * 8 + k] : w[(2 * s + 1) * 8 + k];
+      const uint32_t recv = __shfl_xor_sync(0xffffffffu, send, 1);
+      f[(2 * s) * 8 + k] = odd ? recv : keep;
+      f[(2 * s + 1) * 8 + k] = odd ? keep : recv;
+    }
+  }
+}
+__device__ __forceinline__ void st_global_v8(void* dst, const uint32_t* w) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst), "r"(w[0]), "r"(w[1]), "r"(w[2]),
+               "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
+}
+
 // Instruction descriptor (32 bit) for kind::f16 / kind::f8f6f4, dense, fp32 accumulator:
 //   [4,6) D format (1 = f32)   [7,10) A format   [10,13) B format   [15] A major   [16] B major
 //   [17,23) N >> 3             [24,29) M >> 4          (major: 0 = K-contiguous, 1 = M/N-contiguous)
