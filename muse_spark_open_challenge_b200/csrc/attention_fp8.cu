@@ -61,7 +61,10 @@
 // the reference maximum); at head_dim 64, where TMEM has room, P in columns of its own with Q K^T(j+1)
 // issued as soon as S(j) is in registers (the wait for S shrinks from 800 to 470 cycles, the exponential
 // pass grows by as much: 0.54 against 0.50 ms); no turns but a quarter of the exponentials as a cubic
-// (0.582 ms, and 0.503 ms at head_dim 64: the same as the turns).
+// (0.582 ms, and 0.503 ms at head_dim 64: the same as the turns); an epilogue in which quads of lanes
+// exchange 4 x 4 blocks by shuffles so that gate rows are read and output rows written 128 contiguous
+// bytes at a time, as the GEMM epilogues do (0.581 against 0.573 ms at head_dim 128, 0.496 against
+// 0.502 ms at 64: the 128 shuffles per 64 columns cost what the wider requests save).
 #include "msl_common.cuh"
 #include "msl_host.h"
 
