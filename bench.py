@@ -375,7 +375,8 @@ def run_native(args):
                  "ok": ok, "message": msg, "local_routes": int(st["offsets"][-1].item()),
                  "update_vs_fp32": rep.get("update_vs_fp32"), "hidden_vs_fp8q": rep.get("hidden_vs_fp8q")}
         del data, data_cpu, w_cpu
-    for batch, ctx, new, sliding, h200_us, h100_us in NATIVE_SHAPES:
+    chosen = NATIVE_SHAPES if not args.native_shapes else [NATIVE_SHAPES[int(i)] for i in args.native_shapes.split(",")]
+    for batch, ctx, new, sliding, h200_us, h100_us in chosen:
         shape = dataclasses.replace(synth.NATIVE, window=2048 if sliding else 0, rope_theta=5e5 if sliding else 0.0)
         data = synth.make_input(shape, [new] * batch, [ctx] * batch, seed=7, page=args.page, kv_scale=1.0, local_start=0,
                                 device=dev, fill_cache=True)
@@ -639,6 +640,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--layers", type=int, default=4, help="layers of --workload stack")
     ap.add_argument("--page", type=int, default=1, help="page size of --workload native (the reference's runs use 1)")
+    ap.add_argument("--native-shapes", default="", help="--workload native: comma-separated indices of the scored "
+                    "shapes to run (default: all eight)")
     ap.add_argument("--check", action="store_true", help="--workload native: also judge one 4096-token case by the "
                                                           "CPU oracle")
     ap.add_argument("--workload", default="layer", choices=["layer", "attn", "moe", "native", "long", "stack", "peaks"],

@@ -391,6 +391,58 @@ splitk_reduce_kernel(const float* __restrict__ part, int splits, int m, int n, f
 
 using namespace msl;
 
+// Choice of tile geometry and K slices from the sizes alone: a cost model in SM cycles.  A 128 x 256 tile takes
+// about 880 cycles per 64-wide K step (its 48 KB per step arrive at the 55-60 bytes per clock one SM takes
+// from L2; the four MMAs would need 512), a 256 x 256 tile about 1100 (64 KB, 1024 cycles of MMA), a 128 x
+// 128 tile about 570; a work item costs a pipeline fill of about 1500 cycles; the epilogue (5000 cycles, 8000
+// for 256 rows, 3000 for 128 columns) overlaps the next item's main loop only where there are two accumulator
+// sets; the reduction over K slices reads its planes out of L2 at about 4 TB/s behind a launch of about 3 us.
+// The step times hold where many row tiles share each weight tile.  Products of 753 rows on weights that come
+// from HBM (three to six row tiles) move 7.5-10 TB/s from L2 to the SMs whatever the geometry, and a 256 x 256
+// step then takes 1560-2300 cycles; the plans chosen here (QKV 5 slices of 256-row tiles, pooler 3, unpooler
+// and output projection 256-row tiles unsliced) ran 41, 56, 52 and 19 us against 41, 58, 58 and 20 us under the
+// rule they replace (256-row tiles only when they alone fill every SM, slices only below half a wave).
+struct GemmPlan {
+  int splits;
+  bool wide;
+  double cycles;
+};
+
+static double gemm_cost(int m, int n, int k_blocks, int bn, bool wide, int splits, int sms) {
+  const int tile_m = wide ? 2 * kBM : kBM;
+  const int64_t items = static_cast<int64_t>((m + tile_m - 1) / tile_m) * ((n + bn - 1) / bn) * splits;
+  const double per_cta = static_cast<double>((items + sms - 1) / sms);
+  const double stage = wide ? 1100.0 : (bn == 256 ? 880.0 : 570.0);
+  const double epilogue = wide ? 8000.0 : (bn == 256 ? 5000.0 : 3000.0);
+  const int kb = (k_blocks + splits - 1) / splits;
+  double cycles = per_cta * (kb * stage + 1500.0) + (wide ? per_cta : 1.0) * epilogue;
+  if (splits > 1) cycles += 1900.0 * (3.0 + static_cast<double>(splits) * m * n * 4.0 / 4.0e6);
+  return cycles;
+}
+
+// Best geometry for a given number of K slices (`splits` > 0), or best of both (`splits` == 0, at most
+// `max_splits` slices).  A slower-by-model plan with fewer slices wins unless slicing saves 5 %.
+static GemmPlan gemm_plan(int m, int n, int k, int segs, int out_mode, int splits, int max_splits) {
+  const bool narrow_n = (out_mode != MSL_OUT_SWIGLU_BF16) && (n <= 128 || (n % 256 != 0 && n % 128 == 0));
+  const int bn = narrow_n ? 128 : 256;
+  const int k_blocks = ((k + kBK - 1) / kBK) * segs;
+  const int sms = sm_count();
+  const bool may_wide = !narrow_n && m > kBM && option(MSL_OPT_GEMM_WIDE) != 0;
+  GemmPlan best{1, false, 0.0};
+  bool have = false;
+  const int lo = splits > 0 ? splits : 1, hi = splits > 0 ? splits : std::max(1, max_splits);
+  for (int s = lo; s <= hi; ++s) {
+    for (int w = 0; w <= (may_wide ? 1 : 0); ++w) {
+      const double c = gemm_cost(m, n, k_blocks, bn, w != 0, s, sms);
+      if (!have || c < best.cycles * (s > best.splits ? 0.95 : 1.0)) {
+        best = GemmPlan{s, w != 0, c};
+        have = true;
+      }
+    }
+  }
+  return best;
+}
+
 static int gemm_entry(const void* a, int64_t lda, const void* b, int64_t ldb, void* c, int64_t ldc, int m, int n, int k,
                       int segs, int a_seg_stride, int b_seg_stride, int out_mode, float alpha, int splits,
                       void* workspace, int* status, void* stream) {
@@ -424,7 +476,9 @@ static int gemm_entry(const void* a, int64_t lda, const void* b, int64_t ldb, vo
     rc = make_tmap_2d(&tb, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, b_cols, n, ldb * 2, kBK, narrow_n ? 128 : 256,
                       CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
-    rc = narrow_n ? launch_gemm<128, 6, MSL_OUT_F32>(ta, tb, part, st) : launch_gemm<256, 4, MSL_OUT_F32>(ta, tb, part, st);
+    if (narrow_n) rc = launch_gemm<128, 6, MSL_OUT_F32>(ta, tb, part, st);
+    else if (gemm_plan(m, n, k, segs, out_mode, splits, splits).wide) rc = launch_gemm<256, 3, MSL_OUT_F32, 2>(ta, tb, part, st);
+    else rc = launch_gemm<256, 4, MSL_OUT_F32>(ta, tb, part, st);
     if (rc) return rc;
     const int64_t quads = static_cast<int64_t>(m) * (n / 4);
     const int blocks = static_cast<int>(std::min<int64_t>((quads + 255) / 256, 8 * static_cast<int64_t>(sm_count())));
@@ -438,9 +492,8 @@ static int gemm_entry(const void* a, int64_t lda, const void* b, int64_t ldb, vo
   rc = make_tmap_2d(&tb, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, b_cols, n, ldb * 2, kBK, bn,
                     CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc) return rc;
-  // 256 x 256 tiles once there are enough rows to fill them and enough tiles to fill the GPU.
-  const bool wide = !narrow && m >= 512 && static_cast<int64_t>((m + 255) / 256) * ((n + 255) / 256) >= sm_count() &&
-                    option(MSL_OPT_GEMM_WIDE) != 0;
+  // 256 x 256 tiles where the cost model above prefers them.
+  const bool wide = gemm_plan(m, n, k, segs, out_mode, 1, 1).wide;
   switch (out_mode) {
     case MSL_OUT_BF16:
       if (wide) return launch_gemm<256, 3, MSL_OUT_BF16, 2>(ta, tb, args, st);
@@ -472,12 +525,9 @@ extern "C" int msl_gemm_splitk_plan(int m, int n, int k, int segs, int out_mode)
   // Slicing K changes the order of the fp32 sums, so a product's low bits then depend on how many rows
   // it has; with the option off every product runs in one pass, for hosts that need batch-invariant bits.
   if (option(MSL_OPT_GEMM_SPLITK) == 0) return 1;
-  const bool narrow_n = n <= 128 || (n % 256 != 0 && n % 128 == 0);
-  const int64_t tiles = static_cast<int64_t>((m + kBM - 1) / kBM) * ((n + (narrow_n ? 127 : 255)) / (narrow_n ? 128 : 256));
   const int k_blocks = ((k + kBK - 1) / kBK) * segs;
-  const int sms = sm_count();
-  if (tiles * 2 > sms || k_blocks < 16) return 1;            // enough tiles, or too little K to slice
-  return static_cast<int>(std::max<int64_t>(1, std::min<int64_t>({sms / tiles, k_blocks / 8, 16})));
+  if (k_blocks < 16) return 1;                               // too little K to slice
+  return gemm_plan(m, n, k, segs, out_mode, 0, std::min(k_blocks / 8, 16)).splits;
 }
 
 extern "C" int msl_gemm_bf16_splitk(const void* a, int64_t lda, const void* b, int64_t ldb, void* c, int64_t ldc,

@@ -683,8 +683,18 @@ extern "C" int msl_grouped_gemm_nvfp4(const void* x, int64_t slab_rows, const vo
   GroupedArgs a{static_cast<const uint8_t*>(codes), static_cast<const uint8_t*>(scales), global_scales, offsets, out,
                 ld_out, slab_rows, experts, n_padded, k, weight_experts, n_out, swiglu, status};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // 256-row tiles when the groups are large enough on average to fill them.
-  const bool use_wide = slab_rows >= 256LL * experts && option(MSL_OPT_GROUPED_WIDE) != 0;
+  // 256-row tiles unless the groups are tiny on average.  Both geometries advance at the pace of the weight
+  // producers when a tile has a single 128-row sub-tile (about 1150 cycles per K step), so a 256-row tile never
+  // costs more per step than a 128-row one, and a skewed routing (the row counts live on the device, the host
+  // sees the slab's size only) gives the busiest groups half as many tiles: 1367 rows on 14 of 32 groups, two
+  // of them with a third of the rows each, take 4 instead of 5 rounds of tiles (203 + 107 against 222 + 133 us
+  // for the two products).  What the 128-row geometry keeps is its second accumulator set (the epilogue, a
+  // tenth of a tile at K = 4096, hides under the next tile), which pays when no group exceeds 128 rows.
+  // (Letting single-sub-tile tiles of the 256-row geometry take the two halves of the accumulator columns in
+  // turn recovers that overlap, 180 against 183 us on those 1367 rows, but measured 1 % slower wherever full
+  // tiles dominate: not kept.  Three producer groups, 576 threads with 4 weight and 3 activation slots, were
+  // slower on every shape tried: the 112 registers left per thread spill in the epilogue.)
+  const bool use_wide = slab_rows >= 32LL * experts && option(MSL_OPT_GROUPED_WIDE) != 0;
   return use_wide ? launch_grouped<kWide>(tx, a, slab_rows, experts, n_padded, st)
                   : launch_grouped<kNarrow>(tx, a, slab_rows, experts, n_padded, st);
 }
