@@ -52,8 +52,8 @@ const char* msl_status_string(int code);
 enum {
   MSL_OPT_GEMM_SPLITK = 0,  /* MSL_GEMM_SPLITK: msl_gemm_splitk_plan may recommend slicing K (default 1).  Off:
                                every product runs in one pass and its low bits do not depend on its row count */
-  MSL_OPT_GEMM_WIDE = 1,    /* MSL_GEMM_WIDE: 256 x 256 tiles in the dense GEMM when the problem fills them (1) */
-  MSL_OPT_GROUPED_WIDE = 2, /* MSL_GROUPED_WIDE: 256-row tiles in the grouped GEMM when groups average >= 256 rows (1) */
+  MSL_OPT_GEMM_WIDE = 1,    /* MSL_GEMM_WIDE: the dense GEMM may choose 256 x 256 tiles (1) */
+  MSL_OPT_GROUPED_WIDE = 2, /* MSL_GROUPED_WIDE: 256-row tiles in the grouped GEMM unless the slab has under 32 rows per group (1) */
   MSL_OPT_COUNT = 3
 };
 int msl_set_option(int option, int value);
