@@ -84,6 +84,27 @@ def test_split_kv_plan_counts_waves(lib):
     assert plan(1, 1, 32, 8, 8, 64, 0) == 1 and plan(0, 1, 32, 8, 64, 64, 0) == 1 and plan(1, 1, 32, 5, 64, 64, 0) == 1
 
 
+def test_split_k_plan_follows_the_cost_model(lib):
+    """The K slices of a dense product come from sizes alone (148 SMs assumed without a GPU): rounds of work
+    items x K steps per item, plus the reduction pass, for 128- and 256-row tiles; slicing must save 5 %."""
+    plan = lib.msl_gemm_splitk_plan
+    # the 753-token products of the native shard: QKV and pooler as K slices of 256-row tiles
+    assert plan(753, 2304, 8192, 1, 0) == 5 and plan(753, 4096, 8192, 1, 0) == 3
+    # unpooler and output projection: 96 tiles of 256 rows in one round, nothing to gain from slices
+    assert plan(753, 8192, 4096, 1, 0) == 1 and plan(753, 8192, 1024, 1, 0) == 1
+    # six tiles with 256 K steps (the two-segment router): the most slices allowed
+    assert plan(753, 256, 8192, 2, 1) == 16
+    # prefill-sized products fill the GPU; the fused SiLU output cannot be sliced; short K is not sliced
+    assert plan(16384, 10240, 4096, 1, 0) == 1 and plan(3012, 4096, 8192, 1, 0) == 1
+    assert plan(753, 256, 8192, 2, 2) == 1 and plan(8, 2304, 512, 1, 0) == 1
+    # with slicing switched off every product runs in one pass
+    old = lib.msl_get_option(0)
+    try:
+        assert lib.msl_set_option(0, 0) == 0 and plan(753, 2304, 8192, 1, 0) == 1
+    finally:
+        lib.msl_set_option(0, old)
+
+
 def test_missing_library_fails_loudly(tmp_path):
     from muse_spark_open_challenge_b200 import _lib
     with pytest.raises(_lib.MslError):
