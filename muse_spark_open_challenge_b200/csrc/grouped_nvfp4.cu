@@ -693,7 +693,10 @@ extern "C" int msl_grouped_gemm_nvfp4(const void* x, int64_t slab_rows, const vo
   // (Letting single-sub-tile tiles of the 256-row geometry take the two halves of the accumulator columns in
   // turn recovers that overlap, 180 against 183 us on those 1367 rows, but measured 1 % slower wherever full
   // tiles dominate: not kept.  Three producer groups, 576 threads with 4 weight and 3 activation slots, were
-  // slower on every shape tried: the 112 registers left per thread spill in the epilogue.)
+  // slower on every shape tried: the 112 registers left per thread spill in the epilogue.  Asking L2 for a
+  // step's packed weights eight steps ahead (cp.async.bulk.prefetch.L2 from the TMA lane) gave those 1367 rows
+  // 566 against 574 us per layer, their weights coming from HBM with no other reader, and cost products whose
+  // groups have many row tiles 1-3 %: not kept.)
   const bool use_wide = slab_rows >= 32LL * experts && option(MSL_OPT_GROUPED_WIDE) != 0;
   return use_wide ? launch_grouped<kWide>(tx, a, slab_rows, experts, n_padded, st)
                   : launch_grouped<kNarrow>(tx, a, slab_rows, experts, n_padded, st);
