@@ -25,7 +25,8 @@ def rel_l2(a, b):
 
 # ------------------------------------------------------------------------------ dense GEMM
 @pytest.mark.parametrize("m,n,k", [(128, 256, 64), (256, 512, 512), (300, 1280, 512), (1, 256, 128), (777, 128, 256),
-                                   (130, 16, 512), (4096, 4096, 1024), (2500, 10240, 512)])
+                                   (130, 16, 512), (4096, 4096, 1024), (2500, 10240, 512),
+                                   (753, 8192, 1024)])      # 96 tiles of 256 rows, the last row tile ragged
 def test_gemm_bf16_matches_fp32_matmul(ops, m, n, k):
     g = torch.Generator(device="cuda").manual_seed(m * 7 + n)
     a = torch.randn((m, k), generator=g, device="cuda").to(torch.bfloat16)
@@ -43,7 +44,8 @@ def test_gemm_bf16_matches_fp32_matmul(ops, m, n, k):
 
 
 @pytest.mark.parametrize("m,n,k,segs,splits", [(753, 2304, 8192, 1, 2), (8, 2304, 4096, 1, 16), (100, 256, 2048, 2, 7),
-                                               (24, 64, 1024, 1, 16), (300, 1280, 1024, 1, 3)])
+                                               (24, 64, 1024, 1, 16), (300, 1280, 1024, 1, 3),
+                                               (753, 2304, 8192, 1, 5), (753, 4096, 8192, 1, 3)])   # 256-row tiles
 def test_gemm_split_k(ops, m, n, k, segs, splits):
     """K cut into slices on separate CTAs, summed in a fixed order: same bound as the one-pass product,
     repeatable bit for bit, for bf16 and fp32 outputs and for the two-segment (router) form."""
