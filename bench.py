@@ -192,12 +192,32 @@ def mma_peak(kind, n, iters=20000):
     return best
 
 
+def unit_peak(op, warps, iters=4000):
+    """SM cycles per warp instruction and scheduler of one scalar-pipe instruction (msl_unit_peak): op 0 ex2,
+    1 FP8 pair conversion, 2 fma, 3 max, 4 two ex2 + one conversion; `warps` warps in the one CTA per SM."""
+    from muse_spark_open_challenge_b200 import _lib
+    lib = _lib.lib()
+    span = torch.zeros(2, dtype=torch.int64, device="cuda")       # [longest CTA's span, collected results]
+    stream = torch.cuda.current_stream().cuda_stream
+    _lib.check(lib.msl_unit_peak(op, warps, 200, span.data_ptr(), stream), "msl_unit_peak")      # warm-up
+    span.zero_()
+    _lib.check(lib.msl_unit_peak(op, warps, iters, span.data_ptr(), stream), "msl_unit_peak")
+    torch.cuda.synchronize()
+    return int(span[0].item()) / (iters * 16 * warps / 4.0)
+
+
 def run_peaks(args):
-    """The measured instruction ceilings used as roofline denominators where the pool's peak file has none."""
+    """The measured instruction ceilings used as roofline denominators where the pool's peak file has none, and
+    the issue rates of the scalar-pipe instructions that bound the attention kernel's softmax."""
     rows = {f"{name} M128xN{n}": round(mma_peak(kind, n), 1)
             for kind, name in ((0, "bf16 K16"), (1, "e4m3 K32"), (2, "nvfp4 block-scaled K64")) for n in (128, 192, 256)}
+    units = {f"{name}, {w // 4} warp(s) per scheduler": round(unit_peak(op, w), 2)
+             for op, name in ((0, "ex2.approx.ftz.f32"), (1, "cvt.rn.satfinite.e4m3x2.f32"), (2, "fma.rn.f32"),
+                              (3, "max.f32"), (4, "2 x ex2 + 1 x cvt e4m3x2 (per group of three)")) for w in (4, 8, 16)}
     print(json.dumps({"metric": "tensor-core instruction ceilings (resident operands, no loads, no epilogue)",
-                      "unit": "TFLOP/s", "n_gpus": 1, "rows": rows, "gpu_launches": 36}))
+                      "unit": "TFLOP/s", "n_gpus": 1, "rows": rows,
+                      "scalar_units": {"unit": "SM cycles per warp instruction and scheduler", "rows": units},
+                      "gpu_launches": 36 + 30}))
 
 
 def run_attention_op(args):

@@ -330,6 +330,13 @@ int msl_attention_fp8_split(const void* q8, const void* k_cache, const void* v_c
  * fractions; the reference's own model takes the vendor's dense figures (reference.py:681-697). */
 int msl_mma_peak(int kind, int n, int iters, int* status, void* stream);
 
+/* Measured issue rate of one scalar-pipe instruction (op 0: ex2.approx.ftz.f32, 1: cvt.rn.satfinite.e4m3x2.f32,
+ * 2: fma.rn.f32, 3: max.f32, 4: two ex2 and one such conversion per instance): one CTA of `warps` warps (1..16) per SM, each warp `iters` rounds of 16 independent
+ * instances; the longest CTA's span in SM cycles is left in max_cycles[0] by an atomic maximum (two 64-bit device
+ * words zeroed by the caller; the second collects the instances' results).  Cycles per warp instruction and scheduler = span / (iters * 16 * warps / 4).  The exponentials
+ * and the FP8 conversion of the attention kernel's softmax share one such unit; the reference has no such probe. */
+int msl_unit_peak(int op, int warps, int iters, unsigned long long* max_cycles, void* stream);
+
 /* ---- The whole layer for hosts that do not run Python.  These three calls stand where the reference's
  * harness calls `state = prepare(weights)` once and `kernel_fn(data, state)` per step
  * (muse_prefill_layer/submission.py:1013-1070, 1073-1140; tools/prefill/judge.py:94,113,124): the same

@@ -52,6 +52,7 @@ SIGNATURES = {
     "msl_nvfp4_bs_quantize": (_i, [_p, _i64, _i64, _i, _p, _i, _p, _p, _p, _p]),
     "msl_grouped_gemm_nvfp4_bs": (_i, [_p, _p, _p, _i64, _p, _p, _p, _p, _p, _i64, _i, _i, _i, _i, _i, _i, _p, _p]),
     "msl_mma_peak": (_i, [_i, _i, _i, _p, _p]),
+    "msl_unit_peak": (_i, [_i, _i, _i, _p, _p]),
     "msl_layer_prepared_bytes": (_i64, [_p]),
     "msl_layer_workspace_bytes": (_i64, [_p]),
     "msl_layer_prepare": (_i, [_p, _p, _p, _i64, _p, _p]),

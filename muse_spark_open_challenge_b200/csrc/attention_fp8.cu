@@ -43,10 +43,11 @@
 // 128-key tile and softmax warp): waiting for S 1200, reading it 115, maximum 450, waiting for the turn
 // 400-600, exponentials + P 1450, rescale 220 (one tile in two has one), stores + arrivals 110: about
 // 3900 cycles, of which the tensor pipe works about 1000.  The unit that sets the floor is the one that
-// runs ex2 and the FP8 conversion: microbenchmarks on this GPU give 8 cycles per ex2.approx warp
-// instruction and scheduler whatever the number of warps (ex2 on f16x2 pairs 16: no gain) and 4 per FP8
-// pair conversion, so a tile costs each scheduler 2 warps x (128 x 8 + 64 x 4) = 2560 cycles there,
-// 2.4 x its tensor time; the kernel runs at 69 % of that floor.  Other facts measured on the way: max
+// runs ex2: microbenchmarks on this GPU (msl_unit_peak) give 8 cycles per ex2.approx warp instruction and
+// scheduler whatever the number of warps (ex2 on f16x2 pairs 16: no gain); the FP8 pair conversion takes 4
+// alone and hides under the exponentials (two ex2 and one conversion: 16.0), so a tile costs each scheduler
+// 2 warps x 128 x 8 = 2048 cycles there, twice its tensor time; the kernel runs at 53-55 % of that floor, the
+// rest being the chain maximum -> exponentials -> P -> MMA of each sub-tile.  Other facts measured on the way: max
 // with two or three inputs takes 2 cycles; a tcgen05.mma never takes less than about 57 cycles (M128 with
 // N <= 64 runs as long as with N = 128), so smaller S tiles cost tensor time without saving any; a warp
 // whose unrolled code outgrows the instruction cache loses half its speed, which is why two warps in

@@ -67,9 +67,75 @@ __global__ void __launch_bounds__(128, 1) mma_peak_kernel(int n, int iters, int*
   if (threadIdx.x < 32) tmem_dealloc(base, 512);
 }
 
+// Issue rate of one scalar-pipe instruction, the other ceiling the attention kernel lives under: every warp of
+// the one CTA per SM runs `iters` rounds of 16 independent instances; the longest CTA's clock64 span goes to
+// max_cycles[0]; max_cycles[1] collects every warp's results.  OP 0: ex2.approx.ftz.f32 (x <- -ex2(x) stays within [-1, -0.5]); 1: cvt.rn.satfinite.e4m3x2.f32
+// (one FP8 pair from two floats); 2: fma.rn.f32; 3: max.f32; 4: two ex2 and one conversion per instance.
+template <int OP>
+__global__ void __launch_bounds__(512, 1) unit_peak_kernel(int iters, unsigned long long* max_cycles) {
+  constexpr int kChains = 16;
+  uint32_t r[kChains];
+#pragma unroll
+  for (int i = 0; i < kChains; ++i) r[i] = 0xbf000000u + ((threadIdx.x * 7u + i) & 0xffffu);   // floats just below -0.5
+  __syncthreads();
+  const long long t0 = clock64();
+  for (int it = 0; it < iters; ++it) {
+#pragma unroll
+    for (int i = 0; i < kChains; ++i) {
+      float a = __uint_as_float(r[i]);
+      const float b = __uint_as_float(r[(i + 1) % kChains]);
+      if constexpr (OP == 0) {
+        asm volatile("ex2.approx.ftz.f32 %0, %0;" : "+f"(a));
+        r[i] = __float_as_uint(-a);
+      } else if constexpr (OP == 1) {
+        uint16_t h;
+        asm volatile("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(h) : "f"(a), "f"(b));
+        r[i] = h;                       // fed back as it is: an OR to keep the value normal would cost the ALU pipe 2 cycles
+      } else if constexpr (OP == 4) {
+        // the softmax mix: two exponentials per converted pair.  The second takes its input from the first
+        // (two instances with the same source register would be merged by the assembler)
+        asm volatile("ex2.approx.ftz.f32 %0, %0;" : "+f"(a));
+        float b2 = a - 1.0f;
+        asm volatile("ex2.approx.ftz.f32 %0, %0;" : "+f"(b2));
+        uint16_t h;
+        asm volatile("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(h) : "f"(a), "f"(b2));
+        r[i] = h;
+      } else if constexpr (OP == 2) {
+        asm volatile("fma.rn.f32 %0, %0, %1, %2;" : "+f"(a) : "f"(0.999f), "f"(-0.0005f));
+        r[i] = __float_as_uint(a);
+      } else {
+        asm volatile("max.f32 %0, %0, %1;" : "+f"(a) : "f"(b));
+        r[i] = __float_as_uint(a);
+      }
+    }
+  }
+  uint32_t acc = 0;
+#pragma unroll
+  for (int i = 0; i < kChains; ++i) acc ^= r[i];
+  const long long t1 = clock64();
+  // every thread's result is observable (word 1), so that no instance of the loop is dead code
+  for (int o = 16; o > 0; o >>= 1) acc ^= __shfl_xor_sync(0xffffffffu, acc, o);
+  if ((threadIdx.x & 31) == 0) atomicXor(max_cycles + 1, static_cast<unsigned long long>(acc));
+  if (threadIdx.x == 0) atomicMax(max_cycles, static_cast<unsigned long long>(t1 - t0));
+}
+
 }  // namespace msl
 
 using namespace msl;
+
+extern "C" int msl_unit_peak(int op, int warps, int iters, unsigned long long* max_cycles, void* stream) {
+  if (op < 0 || op > 4 || warps < 1 || warps > 16 || iters <= 0 || iters > (1 << 20) || !max_cycles) return MSL_ERR_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int grid = sm_count();
+  switch (op) {
+    case 0: unit_peak_kernel<0><<<grid, warps * 32, 0, st>>>(iters, max_cycles); break;
+    case 1: unit_peak_kernel<1><<<grid, warps * 32, 0, st>>>(iters, max_cycles); break;
+    case 2: unit_peak_kernel<2><<<grid, warps * 32, 0, st>>>(iters, max_cycles); break;
+    case 4: unit_peak_kernel<4><<<grid, warps * 32, 0, st>>>(iters, max_cycles); break;
+    default: unit_peak_kernel<3><<<grid, warps * 32, 0, st>>>(iters, max_cycles); break;
+  }
+  return cudaGetLastError() == cudaSuccess ? MSL_OK : MSL_ERR_CUDA;
+}
 
 extern "C" int msl_mma_peak(int kind, int n, int iters, int* status, void* stream) {
   if (kind < 0 || kind > 2 || iters <= 0 || iters > (1 << 22) || n < 16 || n > 256 || (n & 15)) return MSL_ERR_ARG;
